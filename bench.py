@@ -1,0 +1,287 @@
+"""Benchmark of the Kokoro iSTFTNet generator path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--t T]
+
+Metric: audio-seconds per second of the generator alone (24 kHz, f32), whole job over N GPUs. One step = one
+generator forward of one utterance per GPU (default T = 2080 input frames = the 26 s paragraph case: 624000
+samples, 1.279 TFLOP of conv work). N > 1 (torchrun, one rank per GPU): independent utterances, one per rank, no
+data-path collective -> weak scaling; time = max over ranks.
+
+`value`   : inputs already resident in HBM, one CUDA-graph replay per step, timed with CUDA events.
+`e2e`     : the same metric through Generator.synthesize() with HOST buffers: pinned host -> device copies of
+            x / har / s, the replay, and the device -> host copy of the waveform inside the timed region.
+`roofline`: the fused conv kernels (the dominant kernels), timed live per launch with CUDA events in an extra
+            eager pass; achieved = algorithmic conv FLOPs (2 Co Ci K Lo per launch) / summed launch time, against
+            the 3xTF32 tensor roofline = measured bf16 peak / 2 (TF32 rate) / 3 (three TF32 products per f32 one).
+`cpu_baseline` / --impl reference: the CPU oracle (torch f32, the basic-op graph the reference's eager PyTorch
+            modules run) on the host cores, on a bounded sample (a shorter utterance of the same model).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from lokinfer_b200 import synth  # noqa: E402
+
+METRIC = "kokoro_generator_audio_seconds_per_second"
+UNIT = "audio-s/s"
+SAMPLE_RATE = 24000.0
+
+
+def conv_flops_per_t() -> float:
+    """Algorithmic conv FLOPs per unit of T (2 * MACs): ups + noise convs + resblocks + conv_post."""
+    macs = 0
+    macs += 512 * 256 * 20 * 1  # ups.0: 2 Ci Co K Lin / 2 per input column
+    macs += 22 * 256 * 12 * 10  # noise_convs.0 over L0 = 10 T
+    macs += 6 * 256 * 256 * 7 * 10  # noise_res.0
+    macs += 6 * 256 * 256 * (3 + 7 + 11) * 10  # resblocks.0-2
+    macs += 256 * 128 * 12 * 10  # ups.1 over Lin = 10 T
+    macs += 22 * 128 * 1 * 60  # noise_convs.1 over L1 = 60 T (+1)
+    macs += 6 * 128 * 128 * 11 * 60  # noise_res.1
+    macs += 6 * 128 * 128 * (3 + 7 + 11) * 60  # resblocks.3-5
+    macs += 128 * 22 * 7 * 60  # conv_post
+    return 2.0 * macs
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for j, n in enumerate(names) if any(len(r) > 3 + j and r[3 + j].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_generator_rate(t_sample: int, reps: int, warmup: int, threads: int | None):
+    """audio-s/s of the CPU oracle (f32, basic-op graph) for an utterance of t_sample frames."""
+    from oracle import kokoro_oracle as O
+
+    if threads:
+        torch.set_num_threads(threads)
+    cores = torch.get_num_threads()
+    sd = synth.generator_weights(0)
+    sd_t = {k: O.T(v) for k, v in sd.items()}
+    inp = synth.generator_inputs(t_sample, 1)
+    a = [O.T(inp[k]) for k in ("x", "har", "s")]
+    times = []
+    for i in range(warmup + reps):
+        t0 = time.perf_counter()
+        O.generator(sd_t, *a, fused=False)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    sec = float(np.median(times))
+    return 300.0 * t_sample / SAMPLE_RATE / sec, sec, cores
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    t_sample = min(args.t, 520)
+    rate, sec, cores = cpu_generator_rate(t_sample, args.steps, args.warmup, None)
+    sample = (f"CPU oracle (torch f32, basic-op graph = what the reference's eager PyTorch modules run), one "
+              f"utterance of T={t_sample} ({300 * t_sample / SAMPLE_RATE:.1f} s audio) per step, median of {args.steps}")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"kokoro_generator_T{args.t}", "sample_T": t_sample},
+        "cpu_baseline": {"value": rate, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's NEON/Accelerate kernels do not build on this host; the oracle port stands in",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank: int, local_rank: int, world: int):
+    import torch.distributed as dist
+
+    from lokinfer_b200 import Generator, ops
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    t = args.t
+    sh = synth.shapes(t)
+    audio_s = sh["S"] / SAMPLE_RATE
+    gen = Generator(synth.generator_weights(0), dev)
+    inp = synth.generator_inputs(t, 1 + rank)  # each rank synthesises its own utterance
+    host = [torch.from_numpy(inp[k]).pin_memory() for k in ("x", "har", "s")]
+    audio_host = torch.empty(sh["S"], dtype=torch.float32).pin_memory()
+
+    # count launches of one forward and capture the graph
+    with ops.Profile(time_kernels=False) as cnt:
+        gen.forward(*[h.to(dev) for h in host])
+    launches_per_step = cnt.count
+    bufs = gen.capture(t)
+    for k, h in zip(("x", "har", "s"), host):
+        bufs[k].copy_(h)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps, warmup):
+        for _ in range(warmup):
+            step_fn()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            step_fn()
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms_dev = timed(lambda: bufs["graph"].replay(), args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    ms_e2e = timed(lambda: gen.synthesize(host[0], host[1], host[2], audio_host), args.steps, max(1, args.warmup // 2))
+
+    value = world * audio_s * args.steps / (ms_dev * 1e-3)
+    e2e = world * audio_s * args.steps / (ms_e2e * 1e-3)
+    h2d = sum(h.numel() * 4 for h in host)
+    d2h = audio_host.numel() * 4
+
+    roofline, cpu_base, kernels = None, None, None
+    if rank == 0:
+        # per-launch timing of the fused conv kernels (eager pass, CUDA event pair around every launch)
+        with ops.Profile() as prof:
+            for _ in range(2):
+                gen.forward(bufs["x"], bufs["har"], bufs["s"])
+        rows = prof.rows()
+        half = len(rows) // 2
+        rows = rows[half:]  # second pass only (first one warms caches)
+        agg = {}
+        conv_ms, conv_flops = 0.0, 0.0
+        for name, ints, ms in rows:
+            a = agg.setdefault(name, [0, 0.0])
+            a[0] += 1
+            a[1] += ms
+            if name.startswith("conv1d_snake") or name.startswith("conv1d_leaky") or name.startswith("conv1d_affine"):
+                ci, l, co, _, k = ints[0], ints[1], ints[2], ints[3], ints[4]
+                if name == "conv1d_leaky_mean3_f32_cuda":
+                    co, k = ints[6], ints[8]
+                conv_ms += ms
+                conv_flops += 2.0 * co * ci * k * l  # "same" padding: Lo = L
+        pk = peaks()
+        peak = pk["bf16_tflops"] / 2.0 / 3.0
+        achieved = conv_flops / (conv_ms * 1e-3) / 1e12
+        total_ms = sum(v[1] for v in agg.values())
+        kernels = {n: {"launches": v[0], "ms": round(v[1], 4), "share": round(v[1] / total_ms, 4)}
+                   for n, v in sorted(agg.items(), key=lambda kv: -kv[1][1])}
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "traffic": None, "kernel": "conv1d_{snake,leaky}[_res]_f32_cuda (all fused conv launches of one "
+                    "forward)", "peak_source": f"{pk['source']}: bf16 {pk['bf16_tflops']} TF/s / 2 (TF32) / 3 (3xTF32)",
+                    "conv_ms_per_step": conv_ms, "conv_flops_per_step": conv_flops}
+        if world == 1 and not args.no_cpu:
+            t_sample = min(t, 520)
+            rate, sec, cores = cpu_generator_rate(t_sample, 3, 1, None)
+            cpu_base = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
+                        "sample": f"CPU oracle (torch f32, basic-op graph), one utterance of T={t_sample} "
+                                  f"({300 * t_sample / SAMPLE_RATE:.1f} s audio), median of 3 after 1 warm-up, "
+                                  f"{sec * 1e3:.0f} ms each"}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"kokoro_generator_T{t}", "audio_seconds_per_utterance": audio_s,
+                       "utterances_per_step": world, "L0": sh["L0"], "L1": sh["L1"], "samples": sh["S"],
+                       "sharding": "one utterance per GPU, no communication" if world > 1 else "single GPU",
+                       "l2": "working set per step (~2 GB of activations) is larger than the 126 MB L2",
+                       "conv_gflop_per_utterance": conv_flops_per_t() * t / 1e9},
+            "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": roofline, "clocks": clocks, "kernels": kernels,
+        }
+        if cpu_base:
+            line["cpu_baseline"] = cpu_base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--t", type=int, default=2080, help="generator input frames per utterance (2080 = 26 s, 320 = 4 s)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        print(f"bench.py: --gpus {args.gpus} needs torchrun with {args.gpus} ranks; running 1 rank", file=sys.stderr)
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,135 @@
+/* lkc: C-ABI of the B200 (sm_100a) kernel library for lokinfer's Kokoro iSTFTNet generator path.
+ *
+ * Every entry point mirrors one kernel of the reference's registry and takes the reference's own argument
+ * packing (include/lokinfer/runtime/kernel.h:3-39, struct KernelArgs), so a registry adapter on the reference
+ * side is a one-line forward:
+ *
+ *   ptrs   : operands in order, then outs in order (device pointers; f32 unless said otherwise)
+ *   ints   : every operand's shape dims, then every out's shape dims, then the integer attrs in
+ *            attribute-name order
+ *   floats : float attrs in attribute-name order
+ *   state  : result of the matching *_prepare call, or NULL
+ *
+ * Layout: frame-rate tensors are channel-first [C, L], row-major, like the reference CPU path.
+ * Ownership: the caller owns every buffer; no entry point allocates or frees device memory, and all work is
+ * queued on the caller's stream (a cudaStream_t passed as void*) without a host synchronisation.
+ * Errors: every function returns 0 on success and non-zero on failure; lkc_last_error() then returns a
+ * message (thread-local, valid until the next failing call on the thread). Nothing throws or aborts.
+ * The stats tensors are f32[C, ceil(L / 128), 2] = per-(channel, 128-sample chunk) (mean, M2).
+ */
+#ifndef LKC_H_
+#define LKC_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define LKC_API __attribute__((visibility("default")))
+#else
+#define LKC_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct LkcArgs {
+  void* const* ptrs;
+  const int64_t* ints;
+  const double* floats;
+  const void* state;
+  uint32_t numPtrs;
+  uint32_t numInts;
+} LkcArgs;
+
+typedef int (*LkcRunFn)(const LkcArgs* args, void* stream);
+
+/* Registry, as registerKernel / findKernel / registeredKernels (include/lokinfer/runtime/kernel.h:60-74,
+ * src/runtime/registry.cpp). Names are "<op>_f32_cuda"; the `_cuda` token plays the role of the reference's
+ * `_gpu` device token (src/ir/ir.cpp:67-77). */
+LKC_API int lkc_kernel_count(void);
+LKC_API const char* lkc_kernel_name(int index); /* sorted */
+LKC_API LkcRunFn lkc_find_kernel(const char* name); /* NULL if unknown */
+LKC_API const char* lkc_last_error(void);
+/* Library build info: "sm_100a" and the compile-time feature list. */
+LKC_API const char* lkc_build_info(void);
+
+/* ---- basic (unfused) layer ------------------------------------------------------------------------------ */
+
+/* conv1d_f32_cpu (kernels/cpu/kokoro_conv.cpp:32-69, adapter :276-280).
+ * ptrs x[Ci,L] w[Co,Ci,K] b[Co] | out[Co,Lo]; ints x(2) w(3) b(1) out(2) dilation padding stride. */
+LKC_API int lkc_conv1d_f32_cuda(const LkcArgs* a, void* stream);
+/* conv1d_nobias_f32_cpu (kokoro_conv.cpp:282-286). ptrs x w | out; ints x(2) w(3) out(2) dilation padding stride. */
+LKC_API int lkc_conv1d_nobias_f32_cuda(const LkcArgs* a, void* stream);
+/* conv_transpose1d_f32_cpu (kokoro_conv.cpp:71-95, adapter :288-292).
+ * ptrs x[Ci,L] w[Ci,Co,K] b[Co] | out[Co,Lo]; ints x(2) w(3) b(1) out(2) output_padding padding stride. */
+LKC_API int lkc_conv_transpose1d_f32_cuda(const LkcArgs* a, void* stream);
+/* adain1d_f32_cpu (kernels/cpu/kokoro_norm.cpp:49-58, adapter :82-85). ptrs x[C,L] gb[2C] | out; ints x(2) gb(1)
+ * out(2); floats eps. */
+LKC_API int lkc_adain1d_f32_cuda(const LkcArgs* a, void* stream);
+/* snake_f32_cpu (kernels/cpu/kokoro_misc.cpp:197-214). ptrs x[C,L] alpha[C] | out; ints x(2) alpha(1) out(2). */
+LKC_API int lkc_snake_f32_cuda(const LkcArgs* a, void* stream);
+/* leaky_relu_f32_cpu (kokoro_misc.cpp:172-180). ptrs x | out (any rank r); ints x(r) out(r); floats slope. */
+LKC_API int lkc_leaky_relu_f32_cuda(const LkcArgs* a, void* stream);
+/* add_f32_cpu (kernels/cpu/elementwise.cpp:58). ptrs a b | out; ints a(r) b(r) out(r). */
+LKC_API int lkc_add_f32_cuda(const LkcArgs* a, void* stream);
+/* add3_scale_f32_cpu (kokoro_misc.cpp:189-195): ((a + b) + c) * scale. ptrs a b c | out; floats scale. */
+LKC_API int lkc_add3_scale_f32_cuda(const LkcArgs* a, void* stream);
+/* scale_f32_cpu (kokoro_misc.cpp:182-187). ptrs x | out; floats scale. */
+LKC_API int lkc_scale_f32_cuda(const LkcArgs* a, void* stream);
+/* pad_reflect1d_f32_cpu (kokoro_conv.cpp:249-258, adapter :318-320). ptrs x[C,L] | out[C,left+L+right];
+ * ints x(2) out(2) left right. */
+LKC_API int lkc_pad_reflect1d_f32_cuda(const LkcArgs* a, void* stream);
+/* gemm_bias_f32_cpu_accelerate as used for the style bank (models/kokoro/model.py:135-144): out = x @ wt + b.
+ * ptrs x[M,K] wt[K,N] b[N] | out[M,N]; ints x(2) wt(2) b(1) out(2). */
+LKC_API int lkc_gemm_bias_f32_cuda(const LkcArgs* a, void* stream);
+
+/* ---- fused layer ---------------------------------------------------------------------------------------- */
+
+/* channel_stats_f32_cpu (kernels/cpu/kokoro_conv_fused.cpp:631-639, adapter :775-777).
+ * ptrs x[C,L] | stats[C,ceil(L/128),2]; ints x(2) stats(3). */
+LKC_API int lkc_channel_stats_f32_cuda(const LkcArgs* a, void* stream);
+/* adain_affine_f32_cpu (kokoro_conv_fused.cpp:641-664, adapter :780-783).
+ * ptrs stats[C,S,2] gb[2C] | affine[3,C]; ints stats(3) gb(1) affine(2) length; floats eps. */
+LKC_API int lkc_adain_affine_f32_cuda(const LkcArgs* a, void* stream);
+
+/* conv1d_{snake,leaky,affine}[_res]_f32_cpu (kokoro_conv_fused.cpp:117-150, adapter :678-708):
+ *   out = (conv1d(act((x - mean) * scale + beta), w) + b [+ res]) [* oscale], stride 1, zero padding applied
+ *   after act; stats = chunk stats of out.
+ * ptrs x[Ci,L] w[Co,Ci,K] b[Co] affine[3,Ci] [alpha[Ci]] [res[Co,Lo]] | out[Co,Lo] stats[Co,S,2]
+ * ints x(2) w(3) b(1) affine(2) [alpha(1)] [res(2)] out(2) stats(3) dilation padding tile
+ * floats (name order) [oscale (leaky_res only)] [slope (leaky only)]. `tile` is accepted and ignored.
+ * state: NULL, or the LkcConvState returned by lkc_conv1d_prepare_f32_cuda for this weight (tensor-core path). */
+LKC_API int lkc_conv1d_snake_f32_cuda(const LkcArgs* a, void* stream);
+LKC_API int lkc_conv1d_snake_res_f32_cuda(const LkcArgs* a, void* stream);
+LKC_API int lkc_conv1d_leaky_f32_cuda(const LkcArgs* a, void* stream);
+LKC_API int lkc_conv1d_leaky_res_f32_cuda(const LkcArgs* a, void* stream);
+LKC_API int lkc_conv1d_affine_f32_cuda(const LkcArgs* a, void* stream);
+/* conv1d_leaky_wino_mean3_f32_cpu's contract as a direct conv (kokoro_conv_fused.cpp:744-772): the input is
+ * ((x + x2) + x3) * in_scale.
+ * ptrs x x2 x3 [Ci,L] w[Co,Ci,K] b[Co] affine[3,Ci] | out stats
+ * ints x(2) x2(2) x3(2) w(3) b(1) affine(2) out(2) stats(3) dilation padding tile; floats in_scale slope. */
+LKC_API int lkc_conv1d_leaky_mean3_f32_cuda(const LkcArgs* a, void* stream);
+
+/* conv_transpose1d_poly[_mean3]_f32_cpu (kernels/cpu/kokoro_conv.cpp:139-229, adapters :294-309):
+ *   out = reflect_pad_left(conv_transpose1d(leaky(xin, slope), w, b, stride, padding), pad_left) + res,
+ *   xin = x or ((x + x2) + x3) * in_scale; needs K = taps * stride and 2 padding = (taps - 1) stride.
+ * wp is this library's polyphase weight pack f32[Ci, stride, taps, Co] made by lkc_convt_poly_pack_f32_cuda
+ * (the counterpart of ops.convt_poly_weights_cpu, python/lokinfer/ops/kokoro.py:289-314).
+ * ptrs x[Ci,L] wp b[Co] res[Co,L*s+pad_left] | out;  ints x(2) wp(4) b(1) res(2) out(2) pad_left padding stride
+ * taps; floats slope.   mean3: ptrs x x2 x3 wp b res | out; ints x(2) x2(2) x3(2) wp(4) b(1) res(2) out(2)
+ * pad_left padding stride taps; floats in_scale slope. */
+LKC_API int lkc_conv_transpose1d_poly_f32_cuda(const LkcArgs* a, void* stream);
+LKC_API int lkc_conv_transpose1d_poly_mean3_f32_cuda(const LkcArgs* a, void* stream);
+/* Weight pack for the two ops above, run once on constants. ptrs w[Ci,Co,K] | wp[Ci,stride,taps,Co] with
+ * wp[c][r][tt][co] = w[c][co][(r + padding) % stride + (taps - 1 - tt) * stride];
+ * ints w(3) wp(4) padding stride. */
+LKC_API int lkc_convt_poly_pack_f32_cuda(const LkcArgs* a, void* stream);
+
+/* istft_logits_f32_cpu (kernels/cpu/kokoro_signal.cpp:275-359, adapter :388-391).
+ * ptrs x[n_fft+2,L] | out[hop*(L-1)]; ints x(2) out(1) hop n_fft. Fails when n_fft/2+1 > 64, like the reference. */
+LKC_API int lkc_istft_logits_f32_cuda(const LkcArgs* a, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LKC_H_ */

@@ -1,0 +1,65 @@
+// Internal helpers shared by the lkc kernel sources: error reporting and argument decoding.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+
+#include "lkc.h"
+
+namespace lkc {
+
+// Records a failure message for lkc_last_error() and returns 1.
+int fail(const char* msg);
+int failCuda(const char* what, cudaError_t e);
+
+inline const float* F(const LkcArgs* a, int i) { return static_cast<const float*>(a->ptrs[i]); }
+inline float* O(const LkcArgs* a, int i) { return static_cast<float*>(a->ptrs[i]); }
+inline cudaStream_t S(void* stream) { return static_cast<cudaStream_t>(stream); }
+
+// Checks the launch that was just issued (no synchronisation).
+inline int launched(const char* what) {
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return failCuda(what, e);
+  }
+  return 0;
+}
+
+#define LKC_REQUIRE(cond, msg) \
+  do {                         \
+    if (!(cond)) return ::lkc::fail(msg); \
+  } while (0)
+
+constexpr int64_t kStatChunk = 128;
+inline int64_t statChunks(int64_t l) { return (l + kStatChunk - 1) / kStatChunk; }
+inline int64_t ceilDiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+enum class Act : int { None = 0, Snake = 1, Leaky = 2 };
+
+// Operands of the fused conv family (one struct for the CUDA-core and the tensor-core kernels).
+struct ConvFusedParams {
+  const float* x = nullptr;
+  const float* x2 = nullptr;  // mean3 prologue: input = ((x + x2) + x3) * inScale
+  const float* x3 = nullptr;
+  const float* w = nullptr;  // [co, ci, k]
+  const float* bias = nullptr;
+  const float* affine = nullptr;  // [3, ci] rows mean, scale, beta; null = identity
+  const float* alpha = nullptr;
+  const float* residual = nullptr;
+  float* out = nullptr;
+  float* stats = nullptr;  // may be null
+  int64_t ci = 0, l = 0, co = 0, k = 0, dilation = 1, padding = 0, lo = 0;
+  Act act = Act::None;
+  float slope = 0.f, outScale = 1.f, inScale = 1.f;
+  const void* state = nullptr;
+};
+
+// One fused conv, routed to the tensor-core kernel when the shape qualifies, else to the CUDA-core kernel (api.cu).
+int convFused(const ConvFusedParams& p, cudaStream_t s);
+// CUDA-core implicit-GEMM conv for any shape (conv_simt.cu). stride > 1 only for the plain conv1d.
+int convSimt(const ConvFusedParams& p, int64_t stride, cudaStream_t s);
+
+}  // namespace lkc

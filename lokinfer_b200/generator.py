@@ -1,0 +1,171 @@
+"""The Kokoro iSTFTNet generator wired from `ops.*_cuda`: the `cuda`-device twin of the generator part of the
+reference graph builder (models/kokoro/model.py:735-781) with its building blocks adain_resblock1_fused (:235-247),
+adain_resblock1 (:250-260) and the style bank (:67-81, 135-144). The graph structure is the reference's; only the
+kernel-name suffix differs.
+
+Generator(sd) uploads a state dict once (weights become device constants, the ConvTranspose weights are packed once,
+the AdaIN `fc` layers are concatenated into one style-bank GEMV). forward() runs one utterance on torch's current
+stream. capture(t) records the fused graph for one input length into a CUDA graph with static input/output
+buffers, so a replay costs one launch.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import ops
+from .synth import shapes
+
+DILATIONS = (1, 3, 5)
+RES_KERNELS = (3, 7, 11)
+
+
+class Generator:
+    def __init__(self, sd: dict, device="cuda"):
+        self.device = torch.device(device)
+        self.w = {k: ops.to_cuda(np.ascontiguousarray(v, dtype=np.float32), self.device) for k, v in sd.items()}
+        for k in list(self.w):
+            if ".alpha" in k:  # Snake alpha (1, C, 1) -> (C,)   (model.py:_flat_alpha)
+                self.w[k] = self.w[k].reshape(-1).contiguous()
+        # Style bank: every `<name>.fc` as one [128, total] weight + bias, names sorted (model.py:67-81).
+        names = sorted(k[: -len(".weight")] for k in self.w if k.endswith(".fc.weight"))
+        self.bank_wt = torch.cat([self.w[n + ".weight"].t() for n in names], dim=1).contiguous()
+        self.bank_b = torch.cat([self.w[n + ".bias"] for n in names]).contiguous()
+        self.bank_off, o = {}, 0
+        for n in names:
+            self.bank_off[n] = (o, self.w[n + ".bias"].shape[0])
+            o += self.bank_off[n][1]
+        # Polyphase packs of the two upsamplers (model.py:788-793), run once on constants.
+        self.ups_wp = None
+        if "ups.0.weight" in self.w:  # a state dict of resblocks only is enough for adain_resblock1*
+            self.ups_wp = [ops.convt_poly_weights_cuda(self.w["ups.0.weight"], 10, 5),
+                           ops.convt_poly_weights_cuda(self.w["ups.1.weight"], 6, 3)]
+        self.ident128 = torch.stack([torch.zeros(128), torch.ones(128), torch.zeros(128)]).to(self.device).contiguous()
+        self.conv_state = {}  # per-weight prepared state of the tensor-core conv (filled by prepare())
+        self._graphs = {}
+
+    # ------------------------------------------------------------------ building blocks
+
+    def style(self, s):
+        """fc(style) of every AdaIN as views into one style-bank GEMV (model.py:135-144): name -> f32[2C]."""
+        bank = ops.gemm_bias_f32_cuda(s.reshape(1, -1), self.bank_wt, self.bank_b).reshape(-1)
+        return lambda name: bank[self.bank_off[name][0]: self.bank_off[name][0] + self.bank_off[name][1]]
+
+    def _snake_conv(self, x, af, alpha_key, conv, k, d, residual=None):
+        w = self.w
+        return ops.conv1d_snake_f32_cuda(x, w[conv + ".weight"], w[conv + ".bias"], af, w[alpha_key],
+                                         residual=residual, padding=d * (k - 1) // 2, dilation=d,
+                                         state=self.conv_state.get(conv))
+
+    def adain_resblock1_fused(self, x, gb, prefix, k, x_stats=None):
+        n = x.shape[1]
+        st = ops.channel_stats_f32_cuda(x) if x_stats is None else x_stats
+        for j, d in enumerate(DILATIONS):
+            af = ops.adain_affine_f32_cuda(st, gb(f"{prefix}.adain1.{j}.fc"), length=n)
+            xt, st1 = self._snake_conv(x, af, f"{prefix}.alpha1.{j}", f"{prefix}.convs1.{j}", k, d)
+            af = ops.adain_affine_f32_cuda(st1, gb(f"{prefix}.adain2.{j}.fc"), length=n)
+            x, st = self._snake_conv(xt, af, f"{prefix}.alpha2.{j}", f"{prefix}.convs2.{j}", k, 1, residual=x)
+        return x, st
+
+    def adain_resblock1(self, x, gb, prefix, k):
+        w = self.w
+        for j, d in enumerate(DILATIONS):
+            xt = ops.adain1d_f32_cuda(x, gb(f"{prefix}.adain1.{j}.fc"))
+            xt = ops.snake_f32_cuda(xt, w[f"{prefix}.alpha1.{j}"])
+            xt = ops.conv1d_f32_cuda(xt, w[f"{prefix}.convs1.{j}.weight"], w[f"{prefix}.convs1.{j}.bias"],
+                                     padding=d * (k - 1) // 2, dilation=d)
+            xt = ops.adain1d_f32_cuda(xt, gb(f"{prefix}.adain2.{j}.fc"))
+            xt = ops.snake_f32_cuda(xt, w[f"{prefix}.alpha2.{j}"])
+            xt = ops.conv1d_f32_cuda(xt, w[f"{prefix}.convs2.{j}.weight"], w[f"{prefix}.convs2.{j}.bias"],
+                                     padding=(k - 1) // 2)
+            x = ops.add_f32_cuda(xt, x)
+        return x
+
+    # ------------------------------------------------------------------ the graph
+
+    def forward(self, x, har, s, fused=True, outputs=("audio",)):
+        """x f32[512, T], har f32[22, 60 T + 1], s f32[128] (cuda tensors) -> the named outputs
+        ("audio" f32[300 T], "post" f32[22, 60 T + 1])."""
+        w = self.w
+        ops.check(x.dim() == 2 and x.shape[0] == 512, "x must be f32[512, T]")
+        sh = shapes(int(x.shape[1]))
+        ops.check(tuple(har.shape) == (22, sh["L1"]), f"har must be f32[22, {sh['L1']}]")
+        gb = self.style(s)
+        st = {}
+        rb = None
+        for i, (k_up, u, k_noise) in enumerate(((20, 10, 7), (12, 6, 11))):
+            if i == 0:
+                xs = ops.conv1d_f32_cuda(har, w["noise_convs.0.weight"], w["noise_convs.0.bias"], stride=6, padding=3)
+            else:
+                xs = ops.conv1d_f32_cuda(har, w["noise_convs.1.weight"], w["noise_convs.1.bias"])
+            if fused:
+                xs, _ = self.adain_resblock1_fused(xs, gb, f"noise_res.{i}", k_noise)
+                x = ops.conv_transpose1d_poly_f32_cuda(
+                    x if i == 0 else rb[0], self.ups_wp[i], w[f"ups.{i}.bias"], xs, stride=u, padding=(k_up - u) // 2,
+                    taps=k_up // u, slope=0.1, pad_left=1 if i == 1 else 0,
+                    mean3=None if i == 0 else (rb[1], rb[2], 1.0 / 3.0))
+                xst = ops.channel_stats_f32_cuda(x)
+                rb = [self.adain_resblock1_fused(x, gb, f"resblocks.{3 * i + j}", kk, xst)[0]
+                      for j, kk in enumerate(RES_KERNELS)]
+            else:
+                xs = self.adain_resblock1(xs, gb, f"noise_res.{i}", k_noise)
+                x = ops.leaky_relu_f32_cuda(x, slope=0.1)
+                x = ops.conv_transpose1d_f32_cuda(x, w[f"ups.{i}.weight"], w[f"ups.{i}.bias"], stride=u,
+                                                  padding=(k_up - u) // 2, output_padding=0)
+                if i == 1:
+                    x = ops.pad_reflect1d_f32_cuda(x, left=1, right=0)
+                x = ops.add_f32_cuda(x, xs)
+                rb = [self.adain_resblock1(x, gb, f"resblocks.{3 * i + j}", kk) for j, kk in enumerate(RES_KERNELS)]
+                x = ops.add3_scale_f32_cuda(rb[0], rb[1], rb[2], scale=1.0 / 3.0)
+            st[f"stage{i}"] = rb if fused else x
+        if fused:
+            post, _ = ops.conv1d_leaky_mean3_f32_cuda(rb[0], rb[1], rb[2], w["conv_post.weight"], w["conv_post.bias"],
+                                                      self.ident128, in_scale=1.0 / 3.0, slope=0.01, padding=3,
+                                                      state=self.conv_state.get("conv_post"))
+        else:
+            x = ops.leaky_relu_f32_cuda(x, slope=0.01)
+            post = ops.conv1d_f32_cuda(x, w["conv_post.weight"], w["conv_post.bias"], padding=3)
+        st["post"] = post
+        st["audio"] = ops.istft_logits_f32_cuda(post, n_fft=20, hop=5)
+        res = tuple(st[o] for o in outputs)
+        return res[0] if len(res) == 1 else res
+
+    # ------------------------------------------------------------------ CUDA graph replay
+
+    def capture(self, t: int):
+        """Records forward(fused=True) for input length t into a CUDA graph (once per t). Returns a dict with the
+        static buffers `x`, `har`, `s`, `audio` and the `graph`; fill the inputs, then graph.replay()."""
+        if t in self._graphs:
+            return self._graphs[t]
+        sh = shapes(t)
+        dev = self.device
+        bufs = {"x": torch.zeros(512, t, device=dev), "har": torch.zeros(22, sh["L1"], device=dev),
+                "s": torch.zeros(128, device=dev)}
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm-up outside capture: lazy module loading, function attributes
+                self.forward(bufs["x"], bufs["har"], bufs["s"])
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            bufs["audio"] = self.forward(bufs["x"], bufs["har"], bufs["s"])
+        bufs["graph"] = g
+        self._graphs[t] = bufs
+        return bufs
+
+    def synthesize(self, x_host, har_host, s_host, audio_host=None):
+        """End-to-end call with HOST buffers (pinned torch tensors for async copies): host -> device copies, one
+        graph replay, device -> host copy of the waveform. Returns the host waveform tensor."""
+        t = int(x_host.shape[1])
+        b = self.capture(t)
+        b["x"].copy_(x_host, non_blocking=True)
+        b["har"].copy_(har_host, non_blocking=True)
+        b["s"].copy_(s_host, non_blocking=True)
+        b["graph"].replay()
+        if audio_host is None:
+            audio_host = torch.empty(b["audio"].shape, dtype=torch.float32, pin_memory=True)
+        audio_host.copy_(b["audio"], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return audio_host

@@ -1,0 +1,426 @@
+"""`ops.*` surface of the Kokoro generator path on the `cuda` device.
+
+Each function mirrors one op of the reference's Python front end (python/lokinfer/ops/kokoro.py; elementwise ops
+python/lokinfer/ops/elementwise.py) with the same positional operands, keyword attributes, defaults, shape rules
+and error messages, under the name `<op>_f32_cuda` instead of `<op>_f32_cpu`. Operands are contiguous float32
+torch tensors on a CUDA device; results are new tensors (the wrapper plays the runtime's role of allocating the
+outs, src/runtime/executable.cpp:583-654) and every launch goes to torch's current stream through the C-ABI in
+include/lkc.h. Shape errors raise OpError before anything is launched (python/lokinfer/ops/_def.py:12-19).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+STAT_CHUNK = 128  # python/lokinfer/ops/kokoro.py:470
+
+
+class OpError(ValueError):
+    pass
+
+
+def check(cond: bool, msg: str = "invalid operands") -> None:
+    if not cond:
+        raise OpError(msg)
+
+
+def _float(v, name):
+    check(isinstance(v, (int, float)) and not isinstance(v, bool), f"{name} must be a number")
+    return float(v)
+
+
+def _int(v, name):
+    check(isinstance(v, int) and not isinstance(v, bool), f"{name} must be an int")
+    return int(v)
+
+
+def _f32(*xs, rank=None):
+    for x in xs:
+        check(isinstance(x, torch.Tensor) and x.dtype == torch.float32, "expected f32 tensor operands")
+        check(x.is_contiguous(), "expected contiguous tensors")
+        if rank is not None:
+            check(x.dim() == rank, f"expected rank-{rank} operands, got {tuple(x.shape)}")
+
+
+def ceildiv(a, b):
+    return -(-a // b)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Profile:
+    """Per-kernel recorder (the reference's Executable::setProfile / LOKINFER_PROFILE, runtime.h:69-74): while one is
+    active every kernel launch is bracketed by a CUDA event pair on the launching stream and counted. Zero cost
+    when off. rows() -> [(kernel name, ints, milliseconds)] after a synchronize."""
+
+    def __init__(self, time_kernels=True):
+        self.time_kernels = time_kernels
+        self.calls = []  # (name, ints, start event, end event)
+        self.count = 0
+
+    def __enter__(self):
+        global _profile
+        self._prev, _profile = _profile, self
+        return self
+
+    def __exit__(self, *exc):
+        global _profile
+        _profile = self._prev
+
+    def rows(self):
+        torch.cuda.synchronize()
+        return [(n, i, a.elapsed_time(b)) for n, i, a, b in self.calls]
+
+
+_profile = None
+
+
+def _run(name, operands, outs, attrs_int=(), attrs_float=(), state=None):
+    ts = list(operands) + list(outs)
+    check(all(t.is_cuda and t.device == ts[0].device for t in ts),
+          f"{name}: operands must live on one cuda device (use to_cuda); there is no CPU path")
+    ints = [d for t in ts for d in t.shape] + list(attrs_int)
+    with torch.cuda.device(ts[0].device):
+        prof = _profile
+        if prof is None:
+            _lib.run(name, [t.data_ptr() for t in ts], ints, attrs_float, state, _stream())
+            return
+        prof.count += 1
+        if not prof.time_kernels:
+            _lib.run(name, [t.data_ptr() for t in ts], ints, attrs_float, state, _stream())
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        _lib.run(name, [t.data_ptr() for t in ts], ints, attrs_float, state, _stream())
+        b.record()
+        prof.calls.append((name, ints, a, b))
+
+
+def _new(like, shape):
+    # Shape rules run on any device (so they can be exercised without a GPU); storage is only made on cuda.
+    return torch.empty(shape, dtype=torch.float32, device=like.device if like.is_cuda else "meta")
+
+
+def to_cuda(a, device="cuda"):
+    """Host array / tensor -> contiguous f32 tensor on the cuda device (the `sync cpu_to_cuda` copy)."""
+    t = torch.as_tensor(a, dtype=torch.float32)
+    return t.to(device).contiguous()
+
+
+def to_cpu(t):
+    return t.detach().cpu()
+
+
+# --- elementwise ---------------------------------------------------------------------------------------------
+
+def leaky_relu_f32_cuda(x, slope):
+    """F.leaky_relu(x, slope), any shape."""
+    _f32(x)
+    out = _new(x, x.shape)
+    _run("leaky_relu_f32_cuda", [x], [out], attrs_float=[_float(slope, "slope")])
+    return out
+
+
+def scale_f32_cuda(x, scale):
+    """x * scale, any shape."""
+    _f32(x)
+    out = _new(x, x.shape)
+    _run("scale_f32_cuda", [x], [out], attrs_float=[_float(scale, "scale")])
+    return out
+
+
+def add_f32_cuda(a, b):
+    """a + b, same shapes."""
+    _f32(a, b)
+    check(a.shape == b.shape, f"shape mismatch: {tuple(a.shape)}, {tuple(b.shape)}")
+    out = _new(a, a.shape)
+    _run("add_f32_cuda", [a, b], [out])
+    return out
+
+
+def add3_scale_f32_cuda(a, b, c, scale):
+    """(a + b + c) * scale, any shape."""
+    _f32(a, b, c)
+    check(a.shape == b.shape and a.shape == c.shape,
+          f"shape mismatch: {tuple(a.shape)}, {tuple(b.shape)}, {tuple(c.shape)}")
+    out = _new(a, a.shape)
+    _run("add3_scale_f32_cuda", [a, b, c], [out], attrs_float=[_float(scale, "scale")])
+    return out
+
+
+def gemm_bias_f32_cuda(x, wt, b):
+    """x @ wt + b: x f32[M, K], wt f32[K, N], b f32[N] -> f32[M, N] (the style-bank GEMV)."""
+    _f32(x, wt, rank=2)
+    _f32(b, rank=1)
+    check(wt.shape[0] == x.shape[1] and b.shape[0] == wt.shape[1], "gemm_bias: x[M,K] wt[K,N] b[N]")
+    out = _new(x, (x.shape[0], wt.shape[1]))
+    _run("gemm_bias_f32_cuda", [x, wt, b], [out])
+    return out
+
+
+# --- frame-rate ([C, L]) ------------------------------------------------------------------------------------
+
+def _conv_out(l, k, stride, padding, dilation):
+    return (l + 2 * padding - dilation * (k - 1) - 1) // stride + 1
+
+
+def _conv_rule(x, w, *, dilation, padding, stride):
+    _f32(x, rank=2)
+    _f32(w, rank=3)
+    check(w.shape[1] == x.shape[0], f"w must be [Co, Ci, K]: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    check(stride >= 1 and dilation >= 1 and padding >= 0, "invalid stride/padding/dilation")
+    lo = _conv_out(x.shape[1], w.shape[2], stride, padding, dilation)
+    check(lo >= 1, "empty conv output")
+    return (w.shape[0], lo)
+
+
+def conv1d_f32_cuda(x, w, b, stride=1, padding=0, dilation=1):
+    """F.conv1d: x f32[Ci, L], w f32[Co, Ci, K], b f32[Co] -> f32[Co, Lo]."""
+    stride, padding, dilation = _int(stride, "stride"), _int(padding, "padding"), _int(dilation, "dilation")
+    shape = _conv_rule(x, w, dilation=dilation, padding=padding, stride=stride)
+    _f32(b, rank=1)
+    check(b.shape[0] == w.shape[0], "bias must be f32[Co]")
+    out = _new(x, shape)
+    _run("conv1d_f32_cuda", [x, w, b], [out], attrs_int=[dilation, padding, stride])
+    return out
+
+
+def conv1d_nobias_f32_cuda(x, w, stride=1, padding=0, dilation=1):
+    """F.conv1d without bias."""
+    stride, padding, dilation = _int(stride, "stride"), _int(padding, "padding"), _int(dilation, "dilation")
+    shape = _conv_rule(x, w, dilation=dilation, padding=padding, stride=stride)
+    out = _new(x, shape)
+    _run("conv1d_nobias_f32_cuda", [x, w], [out], attrs_int=[dilation, padding, stride])
+    return out
+
+
+def _convt_out(l, k, stride, padding, output_padding):
+    return (l - 1) * stride - 2 * padding + k + output_padding
+
+
+def conv_transpose1d_f32_cuda(x, w, b, stride=1, padding=0, output_padding=0):
+    """F.conv_transpose1d: x f32[Ci, L], w f32[Ci, Co, K], b f32[Co] -> f32[Co, (L-1)s - 2p + K + op]."""
+    stride, padding = _int(stride, "stride"), _int(padding, "padding")
+    output_padding = _int(output_padding, "output_padding")
+    _f32(x, rank=2)
+    _f32(w, rank=3)
+    _f32(b, rank=1)
+    check(w.shape[0] == x.shape[0], f"w must be [Ci, Co, K]: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    check(b.shape[0] == w.shape[1], "bias must be f32[Co]")
+    check(stride >= 1 and padding >= 0 and 0 <= output_padding < stride, "invalid stride/padding/output_padding")
+    lo = _convt_out(x.shape[1], w.shape[2], stride, padding, output_padding)
+    check(lo >= 1, "empty conv_transpose output")
+    out = _new(x, (w.shape[1], lo))
+    _run("conv_transpose1d_f32_cuda", [x, w, b], [out], attrs_int=[output_padding, padding, stride])
+    return out
+
+
+def convt_poly_weights_cuda(w, stride: int, padding: int):
+    """torch ConvTranspose1d weight f32[Ci, Co, K] (K = taps*s, 2p = (taps-1)*s) -> the polyphase pack of
+    conv_transpose1d_poly_f32_cuda: f32[Ci, s, taps, Co], entry [c, r, tt, co] = w[c, co, (r + p) % s + (taps-1-tt)*s]
+    (the counterpart of convt_poly_weights_cpu, python/lokinfer/ops/kokoro.py:289-314; run once on constants)."""
+    _f32(w, rank=3)
+    s, p = _int(stride, "stride"), _int(padding, "padding")
+    ci, co, k = w.shape
+    taps = k // s
+    check(taps * s == k and 2 * p == (taps - 1) * s and 0 <= p < s, "needs K = taps*s and 2p = (taps-1)*s")
+    wp = _new(w, (ci, s, taps, co))
+    _run("convt_poly_pack_f32_cuda", [w], [wp], attrs_int=[p, s])
+    return wp
+
+
+def conv_transpose1d_poly_f32_cuda(x, wp, b, res, stride, padding, taps, slope, pad_left=0, mean3=None):
+    """reflect_pad_left(conv_transpose1d(leaky_relu(x, slope), w, b, stride, padding), pad_left) + res, polyphase
+    (wp = convt_poly_weights_cuda(w, stride, padding), K = taps * stride): x f32[Ci, L] -> f32[Co, L*s + pad_left].
+    mean3 = (x2, x3, scale): the input is ((x + x2) + x3) * scale."""
+    pad_left, padding, stride = _int(pad_left, "pad_left"), _int(padding, "padding"), _int(stride, "stride")
+    taps, slope = _int(taps, "taps"), _float(slope, "slope")
+    _f32(x, res, rank=2)
+    _f32(wp, rank=4)
+    _f32(b, rank=1)
+    check(wp.shape[0] == x.shape[0] and wp.shape[1] == stride and wp.shape[2] == taps and wp.shape[3] == b.shape[0],
+          "wp must come from convt_poly_weights_cuda")
+    check(2 * padding == (taps - 1) * stride and 0 <= padding < stride, "needs 2p = (taps-1)*s")
+    check(pad_left in (0, 1), "pad_left must be 0 or 1")
+    lo = x.shape[1] * stride + pad_left
+    check(res.shape[0] == b.shape[0] and res.shape[1] == lo, "residual must be f32[Co, L*s + pad_left]")
+    out = _new(x, (b.shape[0], lo))
+    at = [pad_left, padding, stride, taps]
+    if mean3 is not None:
+        x2, x3, sc = mean3
+        _f32(x2, x3, rank=2)
+        check(x2.shape == x.shape and x3.shape == x.shape, "x2 / x3 must match x")
+        _run("conv_transpose1d_poly_mean3_f32_cuda", [x, x2, x3, wp, b, res], [out], attrs_int=at,
+             attrs_float=[_float(sc, "in_scale"), slope])
+    else:
+        _run("conv_transpose1d_poly_f32_cuda", [x, wp, b, res], [out], attrs_int=at, attrs_float=[slope])
+    return out
+
+
+def adain1d_f32_cuda(x, gb, eps=1e-5):
+    """(1 + gb[:C, None]) * instance_norm(x) + gb[C:, None] (biased var) over x f32[C, L]."""
+    _f32(x, rank=2)
+    _f32(gb, rank=1)
+    check(gb.shape[0] == x.shape[0] * 2, "gb must be f32[2C]")
+    out = _new(x, x.shape)
+    _run("adain1d_f32_cuda", [x, gb], [out], attrs_float=[_float(eps, "eps")])
+    return out
+
+
+def snake_f32_cuda(x, alpha):
+    """x + (1/alpha) * sin(alpha * x)^2, alpha f32[C] per channel of x f32[C, L]."""
+    _f32(x, rank=2)
+    _f32(alpha, rank=1)
+    check(alpha.shape[0] == x.shape[0], "alpha must be f32[C]")
+    out = _new(x, x.shape)
+    _run("snake_f32_cuda", [x, alpha], [out])
+    return out
+
+
+def pad_reflect1d_f32_cuda(x, left, right):
+    """F.pad(x, (left, right), mode='reflect') over f32[C, L] (left, right < L)."""
+    left, right = _int(left, "left"), _int(right, "right")
+    _f32(x, rank=2)
+    check(left >= 0 and right >= 0, "negative padding")
+    check(x.shape[1] >= max(left, right) + 1, "reflect padding must be < L")
+    out = _new(x, (x.shape[0], x.shape[1] + left + right))
+    _run("pad_reflect1d_f32_cuda", [x], [out], attrs_int=[left, right])
+    return out
+
+
+def istft_logits_f32_cuda(x, n_fft=20, hop=5):
+    """torch.istft(exp(x[:K]) * e^{i sin(x[K:])}, periodic hann, center), K = n_fft/2+1:
+    f32[n_fft+2, L] -> f32[hop*(L-1)]."""
+    n_fft, hop = _int(n_fft, "n_fft"), _int(hop, "hop")
+    _f32(x, rank=2)
+    check(n_fft >= 2 and n_fft % 2 == 0 and hop >= 1, "n_fft must be even, hop >= 1")
+    check(n_fft <= 126, "n_fft must be <= 126 (the kernel keeps n_fft/2 + 1 <= 64 bins on the stack)")
+    check(x.shape[0] == n_fft + 2, f"x must be f32[n_fft+2, L], got {tuple(x.shape)}")
+    check(x.shape[1] >= 2, "need at least 2 frames")
+    out = _new(x, ((x.shape[1] - 1) * hop,))
+    _run("istft_logits_f32_cuda", [x], [out], attrs_int=[hop, n_fft])
+    return out
+
+
+# --- fused frame-rate conv -----------------------------------------------------------------------------------
+
+def conv_tile(ci: int, k: int) -> int:
+    """The reference's default time tile (python/lokinfer/ops/kokoro.py:474-479). The CUDA kernels pick their own
+    tiling; the attribute is packed for ABI compatibility and ignored."""
+    t = (3 << 20) // (4 * ci * k) // STAT_CHUNK * STAT_CHUNK
+    return max(STAT_CHUNK, min(768, t))
+
+
+def _fused_rule(x, w, b, affine, extra, *, dilation, padding, tile):
+    shape = _conv_rule(x, w, dilation=dilation, padding=padding, stride=1)
+    _f32(b, *extra, rank=1)
+    _f32(affine, rank=2)
+    check(b.shape[0] == w.shape[0], "bias must be f32[Co]")
+    check(affine.shape[0] == 3 and affine.shape[1] == x.shape[0], "affine must be f32[3, Ci]")
+    check(tile >= STAT_CHUNK and tile % STAT_CHUNK == 0, f"tile must be a positive multiple of {STAT_CHUNK}")
+    return shape, (shape[0], ceildiv(shape[1], STAT_CHUNK), 2)
+
+
+def _fused_attrs(x, w, padding, dilation, tile):
+    if tile is None:
+        tile = conv_tile(int(x.shape[0]), int(w.shape[2]))
+    return dict(padding=_int(padding, "padding"), dilation=_int(dilation, "dilation"), tile=_int(tile, "tile"))
+
+
+def _state_of(w, state):
+    return None if state is None else state.handle
+
+
+def conv1d_snake_f32_cuda(x, w, b, affine, alpha, residual=None, padding=0, dilation=1, tile=None, state=None):
+    """conv1d(snake((x - mean) * scale + beta, alpha), w) + b [+ residual] -> (out f32[Co, Lo], stats f32[Co, T, 2]).
+    affine = f32[3, Ci] rows (mean, scale, beta), e.g. from adain_affine_f32_cuda."""
+    at = _fused_attrs(x, w, padding, dilation, tile)
+    _f32(alpha, rank=1) if isinstance(alpha, torch.Tensor) else check(False, "alpha must be f32[Ci]")
+    check(alpha.shape[0] == x.shape[0], "alpha must be f32[Ci]")
+    oshape, sshape = _fused_rule(x, w, b, affine, [alpha], **at)
+    out, stats = _new(x, oshape), _new(x, sshape)
+    ai = [at["dilation"], at["padding"], at["tile"]]
+    if residual is None:
+        _run("conv1d_snake_f32_cuda", [x, w, b, affine, alpha], [out, stats], attrs_int=ai, state=_state_of(w, state))
+    else:
+        _f32(residual, rank=2)
+        check(tuple(residual.shape) == tuple(oshape), "residual must match the output")
+        _run("conv1d_snake_res_f32_cuda", [x, w, b, affine, alpha, residual], [out, stats], attrs_int=ai,
+             state=_state_of(w, state))
+    return out, stats
+
+
+def conv1d_leaky_f32_cuda(x, w, b, affine, slope=0.1, residual=None, out_scale=1.0, padding=0, dilation=1,
+                          tile=None, state=None):
+    """(conv1d(leaky_relu((x - mean) * scale + beta, slope), w) + b [+ residual]) * out_scale -> (out, stats)."""
+    at = _fused_attrs(x, w, padding, dilation, tile)
+    slope, out_scale = _float(slope, "slope"), _float(out_scale, "out_scale")
+    oshape, sshape = _fused_rule(x, w, b, affine, [], **at)
+    out, stats = _new(x, oshape), _new(x, sshape)
+    ai = [at["dilation"], at["padding"], at["tile"]]
+    if residual is None:
+        check(out_scale == 1.0, "out_scale needs a residual")
+        _run("conv1d_leaky_f32_cuda", [x, w, b, affine], [out, stats], attrs_int=ai, attrs_float=[slope],
+             state=_state_of(w, state))
+    else:
+        _f32(residual, rank=2)
+        check(tuple(residual.shape) == tuple(oshape), "residual must match the output")
+        _run("conv1d_leaky_res_f32_cuda", [x, w, b, affine, residual], [out, stats], attrs_int=ai,
+             attrs_float=[out_scale, slope], state=_state_of(w, state))
+    return out, stats
+
+
+def conv1d_affine_f32_cuda(x, w, b, affine, padding=0, dilation=1, tile=None, state=None):
+    """conv1d((x - mean) * scale + beta, w) + b -> (out, stats)."""
+    at = _fused_attrs(x, w, padding, dilation, tile)
+    oshape, sshape = _fused_rule(x, w, b, affine, [], **at)
+    out, stats = _new(x, oshape), _new(x, sshape)
+    _run("conv1d_affine_f32_cuda", [x, w, b, affine], [out, stats],
+         attrs_int=[at["dilation"], at["padding"], at["tile"]], state=_state_of(w, state))
+    return out, stats
+
+
+def conv1d_leaky_mean3_f32_cuda(x, x2, x3, w, b, affine, in_scale, slope, padding=0, dilation=1, tile=None,
+                                state=None):
+    """conv1d_leaky_f32_cuda on ((x + x2) + x3) * in_scale (add3_scale fused into the input window: the generator's
+    resblock mean feeding conv_post; the contract of conv1d_leaky_wino_mean3_f32_cpu,
+    python/lokinfer/ops/kokoro.py:641-653, as a direct conv) -> (out, stats)."""
+    at = _fused_attrs(x, w, padding, dilation, tile)
+    _f32(x2, x3, rank=2)
+    check(x2.shape == x.shape and x3.shape == x.shape, "x2 / x3 must match x")
+    oshape, sshape = _fused_rule(x, w, b, affine, [], **at)
+    out, stats = _new(x, oshape), _new(x, sshape)
+    _run("conv1d_leaky_mean3_f32_cuda", [x, x2, x3, w, b, affine], [out, stats],
+         attrs_int=[at["dilation"], at["padding"], at["tile"]],
+         attrs_float=[_float(in_scale, "in_scale"), _float(slope, "slope")], state=_state_of(w, state))
+    return out, stats
+
+
+def channel_stats_f32_cuda(x):
+    """Per-(channel, 128-sample chunk) (mean, M2) of x f32[C, L] -> f32[C, ceil(L / 128), 2]."""
+    _f32(x, rank=2)
+    check(x.shape[1] >= 1, "empty sequence")
+    stats = _new(x, (x.shape[0], ceildiv(x.shape[1], STAT_CHUNK), 2))
+    _run("channel_stats_f32_cuda", [x], [stats])
+    return stats
+
+
+def adain_affine_f32_cuda(stats, gb, length, eps=1e-5):
+    """AdaIN from chunk stats over `length` samples -> affine f32[3, C] = (mean, (1 + g) / std, b)."""
+    _f32(stats, rank=3)
+    _f32(gb, rank=1)
+    length = _int(length, "length")
+    c = stats.shape[0]
+    check(gb.shape[0] == 2 * c, "gb must be f32[2C]")
+    check(stats.shape[1] == ceildiv(length, STAT_CHUNK), "stats chunks don't match length")
+    affine = _new(stats, (3, c))
+    _run("adain_affine_f32_cuda", [stats, gb], [affine], attrs_int=[length], attrs_float=[_float(eps, "eps")])
+    return affine
+
+
+def registered_kernels():
+    """Kernel names in the library registry; every op above resolves its kernel by name through it."""
+    return _lib.registered_kernels()

@@ -1,0 +1,319 @@
+"""CPU oracle for the Kokoro iSTFTNet generator path. TEST INFRASTRUCTURE ONLY.
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline / reference arm may import this module; the
+product package never does. It is a torch/numpy restatement (public torch ops only) of the reference's f32 CPU
+kernels and graph for this path, each function citing the reference file:line it follows.
+
+Pinning: the reference's own implementation cannot be built or imported on an x86-64 Linux host (Apple-only
+headers, aarch64 intrinsics, a nanobind extension for Python >= 3.14) and the repo stores no golden vectors for
+this path; its kernel tests are seeded recipes that compare each op with a torch float64 composition
+(tests/kernels/test_kokoro_conv_fused.py, tests/kernels/test_kokoro_kernels.py). This oracle is pinned per op
+and per AdaINResBlock1 iteration against those same recipes (tests/test_oracle.py). Whole-generator parity is
+UNPINNED: the reference checks it against the third-party `kokoro==0.7.16` PyTorch modules, which are absent.
+
+Every function takes/returns torch CPU tensors and works in the dtype of its inputs (float32 = the reference's
+precision, float64 = golden).
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+STAT_CHUNK = 128  # include/lokinfer/kernels/cpu_kokoro.h:96 (kStatChunk)
+DILATIONS = (1, 3, 5)
+RES_KERNELS = (3, 7, 11)
+
+
+def T(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(np.asarray(a))).to(dtype)
+
+
+# ----------------------------------------------------------------------------- shape rules (integers, exact)
+
+def conv_out_len(l, k, stride, padding, dilation):
+    """python/lokinfer/ops/kokoro.py:223-224."""
+    return (l + 2 * padding - dilation * (k - 1) - 1) // stride + 1
+
+
+def convt_out_len(l, k, stride, padding, output_padding=0):
+    """python/lokinfer/ops/kokoro.py:264-265."""
+    return (l - 1) * stride - 2 * padding + k + output_padding
+
+
+def stat_chunks(l):
+    """kernels/cpu/kokoro_conv_fused.cpp:78."""
+    return (l + STAT_CHUNK - 1) // STAT_CHUNK
+
+
+def istft_len(l, hop=5):
+    """python/lokinfer/ops/kokoro.py:459."""
+    return (l - 1) * hop
+
+
+# ----------------------------------------------------------------------------- basic ops (the unfused layer)
+
+def conv1d(x, w, b=None, stride=1, padding=0, dilation=1):
+    """F.conv1d over x [Ci, L] (kernels/cpu/kokoro_conv.cpp:32-69)."""
+    return F.conv1d(x[None], w, b, stride=stride, padding=padding, dilation=dilation)[0]
+
+
+def conv_transpose1d(x, w, b=None, stride=1, padding=0, output_padding=0):
+    """F.conv_transpose1d over x [Ci, L], w [Ci, Co, K] (kernels/cpu/kokoro_conv.cpp:71-95)."""
+    return F.conv_transpose1d(x[None], w, b, stride=stride, padding=padding, output_padding=output_padding)[0]
+
+
+def leaky_relu(x, slope):
+    """kernels/cpu/kokoro_misc.cpp:172-180."""
+    return F.leaky_relu(x, slope)
+
+
+def snake(x, alpha):
+    """x + (1/alpha) sin(alpha x)^2, alpha [C] (kernels/cpu/kokoro_misc.cpp:197-214)."""
+    a = alpha.reshape(-1, 1)
+    return x + (1.0 / a) * torch.sin(a * x) ** 2
+
+
+def add(a, b):
+    return a + b
+
+
+def add3_scale(a, b, c, scale):
+    """((a + b) + c) * scale (kernels/cpu/kokoro_misc.cpp:189-195)."""
+    return ((a + b) + c) * scale
+
+
+def pad_reflect1d(x, left, right):
+    """F.pad(mode='reflect') (kernels/cpu/kokoro_conv.cpp:249-258)."""
+    return F.pad(x[None], (left, right), mode="reflect")[0]
+
+
+def instance_norm(x, eps=1e-5):
+    m = x.mean(dim=-1, keepdim=True)
+    return (x - m) / torch.sqrt(((x - m) ** 2).mean(dim=-1, keepdim=True) + eps)
+
+
+def adain1d(x, gb, eps=1e-5):
+    """(1 + gb[:C]) * instance_norm(x) + gb[C:], biased variance (kernels/cpu/kokoro_norm.cpp:49-58)."""
+    c = x.shape[0]
+    return (1 + gb[:c, None]) * instance_norm(x, eps) + gb[c:, None]
+
+
+# ----------------------------------------------------------------------------- fused-layer ops
+
+def channel_stats(x):
+    """Per-(channel, 128-sample chunk) (mean, M2 = sum (v - mean)^2): [C, L] -> [C, ceil(L/128), 2]
+    (kernels/cpu/kokoro_conv_fused.cpp:41-46, 631-639). Sums are taken in double and rounded to the working dtype,
+    as the reference's blocked sums are; the deviation pass uses the rounded mean."""
+    c, l = x.shape
+    n = stat_chunks(l)
+    out = torch.empty(c, n, 2, dtype=x.dtype)
+
+    def seg_stats(seg):  # seg [c, m, len]
+        mean = (seg.double().sum(dim=-1) / seg.shape[-1]).to(x.dtype)
+        dev = seg - mean[..., None]
+        return mean, (dev * dev).double().sum(dim=-1).to(x.dtype)
+
+    full = l // STAT_CHUNK
+    if full:
+        out[:, :full, 0], out[:, :full, 1] = seg_stats(x[:, :full * STAT_CHUNK].reshape(c, full, STAT_CHUNK))
+    if full < n:
+        m, q = seg_stats(x[:, None, full * STAT_CHUNK:])
+        out[:, full, 0], out[:, full, 1] = m[:, 0], q[:, 0]
+    return out
+
+
+def adain_affine(stats, gb, length, eps=1e-5):
+    """Chan combine of the chunk partials in double, then affine rows (mean, (1 + g) / sqrt(var + eps), b):
+    -> [3, C] (kernels/cpu/kokoro_conv_fused.cpp:641-664). var is biased and rounded to the working dtype before
+    the rsqrt, as in the reference."""
+    c, n, _ = stats.shape
+    assert n == stat_chunks(length)
+    dt = stats.dtype
+    cnt = torch.full((n,), float(STAT_CHUNK), dtype=torch.float64)
+    cnt[-1] = length - (n - 1) * STAT_CHUNK
+    m = stats[:, :, 0].double()
+    mean = (m * cnt).sum(dim=1) / length
+    m2 = stats[:, :, 1].double().sum(dim=1) + (cnt * (m - mean[:, None]) ** 2).sum(dim=1)
+    var = (m2 / length).to(dt)
+    mean = mean.to(dt)
+    scale = (1 + gb[:c]) * (1.0 / torch.sqrt(var + torch.tensor(eps, dtype=dt)))
+    return torch.stack([mean, scale, gb[c:].clone()])
+
+
+def conv1d_fused(x, w, b, affine, act="none", alpha=None, slope=0.0, residual=None, out_scale=1.0, padding=0,
+                 dilation=1, mean3=None):
+    """(conv1d(act((x - mean) * scale + beta), w) + b [+ residual]) * out_scale and the output's chunk stats
+    (kernels/cpu/kokoro_conv_fused.cpp:117-150; zero padding is applied after the activation, :127-135).
+    mean3 = (x2, x3, in_scale): the input is ((x + x2) + x3) * in_scale first (cpu_kokoro.h:113-115)."""
+    if mean3 is not None:
+        x = add3_scale(x, mean3[0], mean3[1], mean3[2])
+    xa = (x - affine[0][:, None]) * affine[1][:, None] + affine[2][:, None]
+    if act == "snake":
+        xa = snake(xa, alpha)
+    elif act == "leaky":
+        xa = F.leaky_relu(xa, slope)
+    else:
+        assert act == "none"
+    out = conv1d(xa, w, b, padding=padding, dilation=dilation)
+    if residual is not None:
+        out = out + residual
+        if out_scale != 1.0:
+            out = out * out_scale
+    return out, channel_stats(out)
+
+
+def conv_transpose1d_poly(x, w, b, res, stride, padding, slope, pad_left=0, mean3=None):
+    """reflect_pad_left(conv_transpose1d(leaky(xin, slope), w, b, stride, padding), pad_left) + res with
+    xin = x or ((x + x2) + x3) * in_scale (kernels/cpu/kokoro_conv.cpp:139-229; out[:, 0] = unpadded[:, 1] at :226).
+    w is the torch ConvTranspose1d weight [Ci, Co, K], K = taps * stride, 2 p = (taps - 1) * stride."""
+    k = w.shape[2]
+    taps = k // stride
+    assert taps * stride == k and 2 * padding == (taps - 1) * stride and 0 <= padding < stride
+    if mean3 is not None:
+        x = add3_scale(x, mean3[0], mean3[1], mean3[2])
+    y = conv_transpose1d(F.leaky_relu(x, slope), w, b, stride=stride, padding=padding)
+    assert y.shape[1] == x.shape[1] * stride
+    if pad_left:
+        y = torch.cat([y[:, 1:2], y], dim=1)
+    return y + res
+
+
+def hann_periodic(n, dtype):
+    """kernels/cpu/kokoro_signal.cpp:33-36: computed in double, rounded to the working dtype."""
+    i = torch.arange(n, dtype=torch.float64)
+    return (0.5 - 0.5 * torch.cos(2.0 * math.pi * i / n)).to(dtype)
+
+
+def istft_logits(x, n_fft=20, hop=5):
+    """Explicit restatement of kernels/cpu/kokoro_signal.cpp:275-359: X_k = exp(x[k]) e^{i sin(x[K+k])},
+    windowed inverse real DFT per frame, overlap-add as a gather per output sample with frames in ascending
+    order, divided by the window-square envelope: [n_fft+2, L] -> [hop (L-1)]."""
+    bins, pad = n_fft // 2 + 1, n_fft // 2
+    l = x.shape[1]
+    dt = x.dtype
+    win = hann_periodic(n_fft, dt)
+    k = torch.arange(bins, dtype=torch.float64)[:, None]
+    m = torch.arange(n_fft, dtype=torch.float64)[None, :]
+    ang = 2.0 * math.pi * torch.remainder(k * m, n_fft) / n_fft
+    edge = ((k == 0) | (2 * k == n_fft)).double()
+    cw = (2.0 - edge) * win.double()[None, :] / n_fft
+    tab_re = (cw * torch.cos(ang)).to(dt)  # [bins, n_fft]
+    tab_im = ((1.0 - edge) * (-cw) * torch.sin(ang)).to(dt)
+    mag = torch.exp(x[:bins])
+    ph = torch.sin(x[bins:])
+    re, im = mag * torch.cos(ph), mag * torch.sin(ph)  # [bins, L]
+    fr = tab_re.t() @ re + tab_im.t() @ im  # [n_fft, L] frame-minor like the kernel's fr[m][t]
+    length = hop * (l - 1)
+    i = torch.arange(length)
+    p = pad + i
+    t_hi = torch.clamp(p // hop, max=l - 1)
+    t_lo = torch.where(p >= n_fft, (p - n_fft) // hop + 1, torch.zeros_like(p))
+    y = torch.zeros(length, dtype=dt)
+    env = torch.zeros(length, dtype=dt)
+    w2 = win * win
+    span = n_fft // hop
+    for j in range(span):  # ascending t = t_lo + j
+        t = t_lo + j
+        ok = t <= t_hi
+        tt = torch.where(ok, t, t_lo)
+        mm = p - tt * hop
+        y = y + torch.where(ok, fr[mm, tt], torch.zeros((), dtype=dt))
+        env = env + torch.where(ok, w2[mm], torch.zeros((), dtype=dt))
+    return y / env
+
+
+def istft_logits_torch(x, n_fft=20, hop=5):
+    """The documented equivalent (python/lokinfer/ops/kokoro.py:462-465):
+    torch.istft(exp(x[:K]) e^{i sin(x[K:])}, periodic hann, center)."""
+    bins = n_fft // 2 + 1
+    mag, ph = torch.exp(x[:bins]), torch.sin(x[bins:])
+    spec = torch.complex(mag * torch.cos(ph), mag * torch.sin(ph))
+    win = torch.hann_window(n_fft, periodic=True, dtype=x.dtype)
+    return torch.istft(spec[None], n_fft, hop_length=hop, win_length=n_fft, window=win, center=True)[0]
+
+
+# ----------------------------------------------------------------------------- graph (models/kokoro/model.py)
+
+def style_bank(sd, s, names=None):
+    """gb = Linear(128 -> 2C)(s) for every `<name>.fc` (models/kokoro/model.py:67-81, 135-144)."""
+    names = names or sorted(k[: -len(".weight")] for k in sd if k.endswith(".fc.weight"))
+    return {n: sd[n + ".weight"] @ s + sd[n + ".bias"] for n in names}
+
+
+def adain_resblock1(x, gbs, sd, prefix, k):
+    """Basic AdaINResBlock1 (models/kokoro/model.py:250-260)."""
+    for j, d in enumerate(DILATIONS):
+        xt = adain1d(x, gbs[f"{prefix}.adain1.{j}.fc"])
+        xt = snake(xt, sd[f"{prefix}.alpha1.{j}"].reshape(-1))
+        xt = conv1d(xt, sd[f"{prefix}.convs1.{j}.weight"], sd[f"{prefix}.convs1.{j}.bias"], padding=d * (k - 1) // 2,
+                    dilation=d)
+        xt = adain1d(xt, gbs[f"{prefix}.adain2.{j}.fc"])
+        xt = snake(xt, sd[f"{prefix}.alpha2.{j}"].reshape(-1))
+        xt = conv1d(xt, sd[f"{prefix}.convs2.{j}.weight"], sd[f"{prefix}.convs2.{j}.bias"], padding=(k - 1) // 2)
+        x = xt + x
+    return x
+
+
+def adain_resblock1_fused(x, gbs, sd, prefix, k, x_stats=None):
+    """Fused AdaINResBlock1 (models/kokoro/model.py:235-247): per dilation adain_affine -> conv1d_snake ->
+    adain_affine -> conv1d_snake(+x); every conv emits the chunk stats of its output. Returns (x, stats)."""
+    n = x.shape[1]
+    st = channel_stats(x) if x_stats is None else x_stats
+    for j, d in enumerate(DILATIONS):
+        af = adain_affine(st, gbs[f"{prefix}.adain1.{j}.fc"], n)
+        xt, st1 = conv1d_fused(x, sd[f"{prefix}.convs1.{j}.weight"], sd[f"{prefix}.convs1.{j}.bias"], af, "snake",
+                               alpha=sd[f"{prefix}.alpha1.{j}"].reshape(-1), padding=d * (k - 1) // 2, dilation=d)
+        af = adain_affine(st1, gbs[f"{prefix}.adain2.{j}.fc"], n)
+        x, st = conv1d_fused(xt, sd[f"{prefix}.convs2.{j}.weight"], sd[f"{prefix}.convs2.{j}.bias"], af, "snake",
+                             alpha=sd[f"{prefix}.alpha2.{j}"].reshape(-1), padding=(k - 1) // 2, residual=x)
+    return x, st
+
+
+def generator(sd, x, har, s, fused=True, stages=False):
+    """The generator part of the reference graph (models/kokoro/model.py:735-781): x [512, T] decoder features,
+    har [22, 60 T + 1] harmonic-source STFT, s [128] style -> audio [300 T]. fused=False is the basic-kernel
+    graph (:750-764, 779-780). stages=True also returns named intermediates."""
+    dt = x.dtype
+    sd = {k: (v if torch.is_tensor(v) else T(v)).to(dt) for k, v in sd.items()}
+    gbs = style_bank(sd, s)
+    st = {}
+    rb = None
+    for i, (k_up, u, k_noise) in enumerate(((20, 10, 7), (12, 6, 11))):
+        if i == 0:
+            xs = conv1d(har, sd["noise_convs.0.weight"], sd["noise_convs.0.bias"], stride=6, padding=3)
+        else:
+            xs = conv1d(har, sd["noise_convs.1.weight"], sd["noise_convs.1.bias"])
+        if fused:
+            xs, _ = adain_resblock1_fused(xs, gbs, sd, f"noise_res.{i}", k_noise)
+            x = conv_transpose1d_poly(x if i == 0 else rb[0], sd[f"ups.{i}.weight"], sd[f"ups.{i}.bias"], xs, stride=u,
+                                      padding=(k_up - u) // 2, slope=0.1, pad_left=1 if i == 1 else 0,
+                                      mean3=None if i == 0 else (rb[1], rb[2], 1.0 / 3.0))
+            xst = channel_stats(x)
+            rb = [adain_resblock1_fused(x, gbs, sd, f"resblocks.{3 * i + j}", kk, xst)[0]
+                  for j, kk in enumerate(RES_KERNELS)]
+        else:
+            xs = adain_resblock1(xs, gbs, sd, f"noise_res.{i}", k_noise)
+            x = leaky_relu(x, 0.1)
+            x = conv_transpose1d(x, sd[f"ups.{i}.weight"], sd[f"ups.{i}.bias"], stride=u, padding=(k_up - u) // 2)
+            if i == 1:
+                x = pad_reflect1d(x, 1, 0)
+            x = x + xs
+            rb = [adain_resblock1(x, gbs, sd, f"resblocks.{3 * i + j}", kk) for j, kk in enumerate(RES_KERNELS)]
+            x = add3_scale(rb[0], rb[1], rb[2], 1.0 / 3.0)
+        st[f"stage{i}"] = x if not fused else rb
+    if fused:
+        c = rb[0].shape[0]
+        ident = torch.stack([torch.zeros(c), torch.ones(c), torch.zeros(c)]).to(dt)
+        post, _ = conv1d_fused(rb[0], sd["conv_post.weight"], sd["conv_post.bias"], ident, "leaky", slope=0.01,
+                               padding=3, mean3=(rb[1], rb[2], 1.0 / 3.0))
+    else:
+        post = conv1d(leaky_relu(x, 0.01), sd["conv_post.weight"], sd["conv_post.bias"], padding=3)
+    audio = istft_logits(post)
+    if stages:
+        st["post"] = post
+        st["audio"] = audio
+        return st
+    return audio

@@ -1,0 +1,95 @@
+"""Whole-path parity: one AdaINResBlock1, the full generator (fused and basic graphs) against the CPU oracle and the
+committed golden fixture, CUDA-graph replay, and size-independent properties at the full 26 s size."""
+import numpy as np
+import pytest
+import torch
+
+from lokinfer_b200 import synth
+from oracle import kokoro_oracle as O
+from util import REL_L2, WAVE_MAXABS, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gen(cuda):
+    from lokinfer_b200 import Generator
+    return Generator(synth.generator_weights(0), cuda)
+
+
+def _inputs(cuda, t, seed=1):
+    from lokinfer_b200 import ops
+    inp = synth.generator_inputs(t, seed)
+    return inp, [ops.to_cuda(inp[k], cuda) for k in ("x", "har", "s")]
+
+
+@pytest.mark.parametrize("c,l,k", [(16, 300, 7), (128, 1201, 3), (128, 2000, 11), (256, 640, 7)])
+def test_resblock(cuda, c, l, k):
+    """Config 0 at reduced length: one AdaINResBlock1 (kernel k, dilations 1/3/5) through the fused ops."""
+    from lokinfer_b200 import Generator, ops
+    sd, x, s = synth.resblock_case(c, l, k, 100 + c + k)
+    g = Generator(sd, cuda)
+    out, st = g.adain_resblock1_fused(ops.to_cuda(x, cuda), g.style(ops.to_cuda(s, cuda)), "rb", k)
+    sd32 = {n: O.T(v) for n, v in sd.items()}
+    ref, rst = O.adain_resblock1_fused(O.T(x), O.style_bank(sd32, O.T(s)), sd32, "rb", k)
+    sd64 = {n: O.T(v, torch.float64) for n, v in sd.items()}
+    ref64, _ = O.adain_resblock1_fused(O.T(x, torch.float64), O.style_bank(sd64, O.T(s, torch.float64)), sd64, "rb", k)
+    got = out.cpu().numpy()
+    # six chained convs: the per-op bar compounds; the float64 golden is the arbiter
+    assert rel_l2(got, ref.numpy()) <= 6 * REL_L2
+    assert rel_l2(got, ref64.numpy()) <= 2 * rel_l2(ref.numpy(), ref64.numpy()) + 1e-6
+    np.testing.assert_allclose(st.cpu().numpy()[..., 0], rst.numpy()[..., 0], atol=1e-4, rtol=1e-4)
+
+
+def test_generator_golden(cuda, gen):
+    from pathlib import Path
+    gold = np.load(Path(__file__).resolve().parent / "golden" / "kokoro_golden.npz")
+    _, d = _inputs(cuda, 4)
+    post, audio = gen.forward(*d, outputs=("post", "audio"))
+    assert tuple(audio.shape) == (1200,) and tuple(post.shape) == (22, 241)
+    assert np.abs(audio.cpu().numpy() - gold["gen_audio_f32"]).max() <= WAVE_MAXABS
+    assert np.abs(audio.cpu().numpy() - gold["gen_audio_f64"]).max() <= WAVE_MAXABS
+    assert rel_l2(post.cpu().numpy(), gold["gen_post_f64"]) <= 1e-4
+
+
+@pytest.mark.parametrize("t", [1, 7, 16])
+@pytest.mark.parametrize("fused", [True, False])
+def test_generator_vs_oracle(cuda, gen, t, fused):
+    inp, d = _inputs(cuda, t, seed=3 + t)
+    audio = gen.forward(*d, fused=fused).cpu().numpy()
+    sd = synth.generator_weights(0)
+    ref32 = O.generator(sd, O.T(inp["x"]), O.T(inp["har"]), O.T(inp["s"]), fused=fused).numpy()
+    dt = torch.float64
+    ref64 = O.generator(sd, O.T(inp["x"], dt), O.T(inp["har"], dt), O.T(inp["s"], dt), fused=fused).numpy()
+    sh = synth.shapes(t)
+    assert audio.shape == (sh["S"],) == ref32.shape
+    assert np.abs(audio - ref32).max() <= WAVE_MAXABS
+    assert np.abs(audio - ref64).max() <= WAVE_MAXABS
+
+
+def test_graph_replay_matches_eager(cuda, gen):
+    inp, d = _inputs(cuda, 9, seed=21)
+    eager = gen.forward(*d).cpu().numpy()
+    host = [torch.from_numpy(inp[k]).pin_memory() for k in ("x", "har", "s")]
+    a1 = gen.synthesize(*host).numpy().copy()
+    a2 = gen.synthesize(*host).numpy().copy()
+    np.testing.assert_array_equal(a1, eager)
+    np.testing.assert_array_equal(a1, a2)
+
+
+def test_full_size_properties(cuda, gen):
+    """The 26 s case (T = 2080: L0 = 20800, L1 = 124801, 624000 samples), too large for the CPU oracle in a test:
+    exact shapes, run-to-run determinism, agreement of the fused graph with the basic-kernel graph (two independent
+    kernel sets), and the iSTFT tail against torch.istft on the same logits."""
+    t = 2080
+    sh = synth.shapes(t)
+    _, d = _inputs(cuda, t, seed=5)
+    post, audio = gen.forward(*d, outputs=("post", "audio"))
+    assert tuple(post.shape) == (22, sh["L1"]) == (22, 124801) and tuple(audio.shape) == (624000,)
+    audio2 = gen.forward(*d)
+    assert torch.equal(audio, audio2)
+    assert torch.isfinite(audio).all()
+    basic = gen.forward(*d, fused=False)
+    assert (audio - basic).abs().max().item() <= 2 * WAVE_MAXABS
+    ref = O.istft_logits_torch(post)  # torch's own CUDA iSTFT
+    assert (audio - ref).abs().max().item() <= 1e-5 * ref.abs().max().item()

@@ -1,0 +1,253 @@
+"""Parity of every CUDA op (called through the C-ABI via lokinfer_b200.ops) against the CPU oracle on the same seeded
+inputs. Bars: rel-L2 <= 1e-5 per op against the float32 oracle; the reference's own float64 tolerances
+(tests/kernels/test_kokoro_conv_fused.py:1-7) against the float64 oracle; integer shape logic exact."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from lokinfer_b200 import synth
+from oracle import kokoro_oracle as O
+from util import REL_L2, check_stats, rel_l2, t32, t64
+
+pytestmark = pytest.mark.gpu
+
+GOLD = None
+
+
+def gold():
+    global GOLD
+    if GOLD is None:
+        from pathlib import Path
+        GOLD = np.load(Path(__file__).resolve().parent / "golden" / "kokoro_golden.npz")
+    return GOLD
+
+
+def dev(cuda, *arrs):
+    from lokinfer_b200 import ops
+    return [ops.to_cuda(a, cuda) for a in arrs]
+
+
+# (Ci, Co, L, K, dilation): the reference's cases (test_kokoro_conv_fused.py:44-51) + K*d > L, exact chunk multiples,
+# Kokoro stage shapes at reduced length.
+CONV_CASES = [(8, 8, 50, 3, 1), (16, 12, 700, 7, 3), (12, 16, 97, 11, 5), (128, 128, 5000, 11, 5),
+              (64, 64, 3000, 3, 1), (8, 8, 1, 3, 1), (8, 8, 20, 11, 5), (32, 32, 256, 7, 1), (32, 32, 257, 7, 1),
+              (128, 128, 1201, 3, 1), (128, 128, 1201, 7, 3), (256, 256, 640, 11, 5), (256, 256, 333, 3, 5),
+              (128, 22, 961, 7, 1), (22, 128, 961, 1, 1)]
+
+
+@pytest.mark.parametrize("ci,co,l,k,d", CONV_CASES)
+@pytest.mark.parametrize("variant", ["snake", "snake_res", "leaky", "leaky_res", "affine"])
+def test_conv1d_fused(cuda, ci, co, l, k, d, variant):
+    from lokinfer_b200 import ops
+    x, w, b, affine, alpha, res = synth.conv_case(ci, co, l, k, ci * 31 + l + k)
+    pad = d * (k - 1) // 2
+    lo = l + 2 * pad - d * (k - 1)
+    res = res[:, :lo]
+    dx, dw, db, daf, dal, dres = dev(cuda, x, w, b, affine, alpha, np.ascontiguousarray(res))
+    kw = dict(padding=pad, dilation=d)
+
+    def oracle(dt):
+        a = [O.T(v, dt) for v in (x, w, b, affine, alpha, res)]
+        if variant.startswith("snake"):
+            return O.conv1d_fused(a[0], a[1], a[2], a[3], "snake", alpha=a[4],
+                                  residual=a[5] if variant == "snake_res" else None, **kw)
+        if variant.startswith("leaky"):
+            rk = dict(residual=a[5], out_scale=0.7071067811865476) if variant == "leaky_res" else {}
+            return O.conv1d_fused(a[0], a[1], a[2], a[3], "leaky", slope=0.2, **kw, **rk)
+        return O.conv1d_fused(a[0], a[1], a[2], a[3], "none", **kw)
+
+    if variant.startswith("snake"):
+        out, stats = ops.conv1d_snake_f32_cuda(dx, dw, db, daf, dal, residual=dres if variant == "snake_res" else None,
+                                               **kw)
+    elif variant.startswith("leaky"):
+        rk = dict(residual=dres, out_scale=0.7071067811865476) if variant == "leaky_res" else {}
+        out, stats = ops.conv1d_leaky_f32_cuda(dx, dw, db, daf, slope=0.2, **kw, **rk)
+    else:
+        out, stats = ops.conv1d_affine_f32_cuda(dx, dw, db, daf, **kw)
+    out, stats = out.cpu().numpy(), stats.cpu().numpy()
+    ref32, st32 = oracle(torch.float32)
+    ref64, _ = oracle(torch.float64)
+    assert out.shape == tuple(ref32.shape) == (co, lo) and stats.shape == tuple(st32.shape)
+    assert rel_l2(out, ref32.numpy()) <= REL_L2
+    np.testing.assert_allclose(out, ref64.numpy(), atol=1e-4, rtol=1e-4)
+    # f32 error against the float64 golden stays within 2x the f32 oracle's own error (+ a floor of one ulp-scale)
+    e_gpu, e_cpu = rel_l2(out, ref64.numpy()), rel_l2(ref32.numpy(), ref64.numpy())
+    assert e_gpu <= 2 * e_cpu + 2e-7
+    check_stats(stats, out)
+    np.testing.assert_allclose(stats[..., 0], st32.numpy()[..., 0], atol=2e-5, rtol=2e-5)
+
+
+def test_conv1d_fused_golden(cuda):
+    from lokinfer_b200 import ops
+    import importlib.util, pathlib
+    spec = importlib.util.spec_from_file_location("make_golden", pathlib.Path(__file__).parent / "golden" / "make_golden.py")
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    c = mg.CONV
+    x, w, b, affine, alpha, res = synth.conv_case(c["ci"], c["co"], c["l"], c["k"], c["seed"])
+    d = dev(cuda, x, w, b, affine, alpha, res)
+    out, stats = ops.conv1d_snake_f32_cuda(*d[:5], residual=d[5], padding=c["d"] * (c["k"] - 1) // 2, dilation=c["d"])
+    assert rel_l2(out.cpu().numpy(), gold()["conv_out_f32"]) <= REL_L2
+    np.testing.assert_allclose(out.cpu().numpy(), gold()["conv_out_f64"], atol=1e-4, rtol=1e-4)
+    check_stats(stats.cpu().numpy(), out.cpu().numpy())
+    # polyphase convT and iSTFT fixtures
+    cx, cw, cb, cres = mg.convt_inputs()
+    ct = mg.CONVT
+    p = (ct["k"] - ct["s"]) // 2
+    dx, dw, db, dres = dev(cuda, cx, cw, cb, cres)
+    wp = ops.convt_poly_weights_cuda(dw, ct["s"], p)
+    got = ops.conv_transpose1d_poly_f32_cuda(dx, wp, db, dres, stride=ct["s"], padding=p, taps=ct["k"] // ct["s"],
+                                             slope=0.1, pad_left=ct["pl"]).cpu().numpy()
+    assert rel_l2(got, gold()["convt_f32"]) <= REL_L2
+    (dxi,) = dev(cuda, mg.istft_input())
+    y = ops.istft_logits_f32_cuda(dxi).cpu().numpy()
+    assert np.abs(y - gold()["istft_f64"]).max() <= 1e-5 * np.abs(gold()["istft_f64"]).max()
+
+
+@pytest.mark.parametrize("c,l", [(4, 1), (16, 700), (128, 5000), (256, 3200), (128, 19201), (3, 128), (3, 129)])
+def test_channel_stats_and_adain_affine(cuda, c, l):
+    from lokinfer_b200 import ops
+    r = np.random.default_rng(c + l)
+    x = (r.standard_normal((c, l)) * 3 + 5).astype(np.float32)
+    gb = (r.standard_normal(2 * c) * 0.5).astype(np.float32)
+    dx, dgb = dev(cuda, x, gb)
+    stats = ops.channel_stats_f32_cuda(dx)
+    assert tuple(stats.shape) == (c, O.stat_chunks(l), 2)
+    check_stats(stats.cpu().numpy(), x)
+    af = ops.adain_affine_f32_cuda(stats, dgb, length=l).cpu().numpy()
+    ref_af = O.adain_affine(O.channel_stats(t32(x)), t32(gb), l).numpy()
+    np.testing.assert_allclose(af, ref_af, atol=2e-5, rtol=2e-5)
+    got = (x - af[0][:, None]) * af[1][:, None] + af[2][:, None]
+    ref = O.adain1d(t64(x), t64(gb)).numpy()
+    np.testing.assert_allclose(got, ref, atol=2e-5 * max(1, np.abs(ref).max()), rtol=1e-4)
+
+
+CONVT_CASES = [(8, 32, 5, 4, 2, 0), (16, 40, 37, 8, 4, 1), (512, 256, 26, 20, 10, 0), (512, 256, 294, 20, 10, 0),
+               (256, 128, 2940, 12, 6, 1), (256, 128, 1, 12, 6, 1), (64, 64, 700, 12, 6, 1), (16, 8, 33, 6, 3, 1),
+               (8, 4, 9, 5, 5, 0)]
+
+
+@pytest.mark.parametrize("ci,co,l,k,s,pl", CONVT_CASES)
+@pytest.mark.parametrize("mean3", [False, True])
+def test_conv_transpose1d_poly(cuda, ci, co, l, k, s, pl, mean3):
+    from lokinfer_b200 import ops
+    r = np.random.default_rng(ci + l + k)
+    xs = [(r.standard_normal((ci, l)) * 2).astype(np.float32) for _ in range(3)]
+    w = (r.standard_normal((ci, co, k)) / math.sqrt(ci * k / s)).astype(np.float32)
+    b = r.standard_normal(co).astype(np.float32)
+    p = (k - s) // 2
+    if 2 * p != (k // s - 1) * s:
+        pytest.skip("not a polyphase shape")
+    res = r.standard_normal((co, l * s + pl)).astype(np.float32)
+    d = dev(cuda, *xs, w, b, res)
+    wp = ops.convt_poly_weights_cuda(d[3], s, p)
+    m3 = (d[1], d[2], 1.0 / 3.0) if mean3 else None
+    got = ops.conv_transpose1d_poly_f32_cuda(d[0], wp, d[4], d[5], stride=s, padding=p, taps=k // s, slope=0.1,
+                                             pad_left=pl, mean3=m3).cpu().numpy()
+
+    def oracle(dt):
+        a = [O.T(v, dt) for v in (*xs, w, b, res)]
+        return O.conv_transpose1d_poly(a[0], a[3], a[4], a[5], s, p, 0.1, pad_left=pl,
+                                       mean3=(a[1], a[2], 1.0 / 3.0) if mean3 else None).numpy()
+
+    assert got.shape == (co, l * s + pl)
+    assert rel_l2(got, oracle(torch.float32)) <= REL_L2
+    np.testing.assert_allclose(got, oracle(torch.float64), atol=1e-4, rtol=1e-4)
+    if mean3:  # bit-identical to add3_scale followed by the op (test_kokoro_conv_fused.py:252-264)
+        m = ops.add3_scale_f32_cuda(d[0], d[1], d[2], 1.0 / 3.0)
+        exp = ops.conv_transpose1d_poly_f32_cuda(m, wp, d[4], d[5], stride=s, padding=p, taps=k // s, slope=0.1,
+                                                 pad_left=pl).cpu().numpy()
+        np.testing.assert_array_equal(got, exp)
+
+
+@pytest.mark.parametrize("l", [2, 3, 7, 57, 641, 1201, 19201])
+def test_istft_logits(cuda, l):
+    from lokinfer_b200 import ops
+    x = np.random.default_rng(l).standard_normal((22, l)).astype(np.float32)
+    (dx,) = dev(cuda, x)
+    y = ops.istft_logits_f32_cuda(dx).cpu().numpy()
+    ref64 = O.istft_logits(t64(x)).numpy()
+    ref32 = O.istft_logits(t32(x)).numpy()
+    assert y.shape == (5 * (l - 1),)
+    assert np.abs(y - ref64).max() <= 1e-5 * np.abs(ref64).max()
+    assert rel_l2(y, ref32) <= REL_L2
+
+
+def test_istft_other_sizes(cuda):
+    from lokinfer_b200 import ops
+    for n_fft, hop, l in ((16, 4, 100), (8, 2, 33), (126, 21, 40)):
+        x = (np.random.default_rng(n_fft).standard_normal((n_fft + 2, l)) * 0.5).astype(np.float32)
+        (dx,) = dev(cuda, x)
+        y = ops.istft_logits_f32_cuda(dx, n_fft=n_fft, hop=hop).cpu().numpy()
+        ref = O.istft_logits(t64(x), n_fft, hop).numpy()
+        assert np.abs(y - ref).max() <= 1e-5 * np.abs(ref).max()
+
+
+def test_basic_ops(cuda):
+    """The unfused parity layer: conv1d (all strides incl. noise_convs[0]), conv_transpose1d, adain1d (mean-100 trap),
+    snake, leaky_relu, add, add3_scale, scale, pad_reflect1d (bit-exact data movement), gemm_bias."""
+    from lokinfer_b200 import ops
+    r = np.random.default_rng(5)
+    # conv1d: (Ci, Co, L, K, s, p, d) from test_kokoro_kernels.py:347-368 style sweep
+    for ci, co, l, k, s, p, d in [(22, 32, 1201, 12, 6, 3, 1), (22, 128, 961, 1, 1, 0, 1), (3, 5, 1, 1, 1, 0, 1),
+                                  (4, 6, 10, 3, 2, 1, 2), (16, 16, 127, 7, 1, 9, 3), (8, 8, 5, 7, 1, 3, 1)]:
+        x = r.standard_normal((ci, l)).astype(np.float32)
+        w = (r.standard_normal((co, ci, k)) / math.sqrt(ci * k)).astype(np.float32)
+        b = r.standard_normal(co).astype(np.float32)
+        dx, dw, db = dev(cuda, x, w, b)
+        got = ops.conv1d_f32_cuda(dx, dw, db, stride=s, padding=p, dilation=d).cpu().numpy()
+        ref = O.conv1d(t64(x), t64(w), t64(b), stride=s, padding=p, dilation=d).numpy()
+        assert got.shape == ref.shape
+        np.testing.assert_allclose(got, ref, atol=1e-4, rtol=1e-4)
+        assert rel_l2(got, O.conv1d(t32(x), t32(w), t32(b), stride=s, padding=p, dilation=d).numpy()) <= REL_L2
+        got = ops.conv1d_nobias_f32_cuda(dx, dw, stride=s, padding=p, dilation=d).cpu().numpy()
+        np.testing.assert_allclose(got, ref - b[:, None], atol=1e-4, rtol=1e-4)
+    for ci, co, l, k, s, p, op in [(16, 12, 37, 8, 4, 2, 0), (512, 256, 26, 20, 10, 5, 0), (4, 3, 5, 3, 2, 0, 1)]:
+        x = r.standard_normal((ci, l)).astype(np.float32)
+        w = (r.standard_normal((ci, co, k)) / math.sqrt(ci * k / s)).astype(np.float32)
+        b = r.standard_normal(co).astype(np.float32)
+        dx, dw, db = dev(cuda, x, w, b)
+        got = ops.conv_transpose1d_f32_cuda(dx, dw, db, stride=s, padding=p, output_padding=op).cpu().numpy()
+        ref = O.conv_transpose1d(t64(x), t64(w), t64(b), stride=s, padding=p, output_padding=op).numpy()
+        assert got.shape == ref.shape
+        np.testing.assert_allclose(got, ref, atol=1e-4, rtol=1e-4)
+    x = (r.standard_normal((4, 135001)) + 100).astype(np.float32)
+    gb = (r.standard_normal(8) * 0.5).astype(np.float32)
+    dx, dgb = dev(cuda, x, gb)
+    np.testing.assert_allclose(ops.adain1d_f32_cuda(dx, dgb).cpu().numpy(), O.adain1d(t64(x), t64(gb)).numpy(),
+                               atol=2e-4, rtol=1e-4)
+    x = (r.standard_normal((6, 257)) * 2).astype(np.float32)
+    al = r.uniform(0.2, 3.0, 6).astype(np.float32)
+    dx, dal = dev(cuda, x, al)
+    np.testing.assert_allclose(ops.snake_f32_cuda(dx, dal).cpu().numpy(), O.snake(t64(x), t64(al)).numpy(), atol=1e-6,
+                               rtol=1e-6)
+    np.testing.assert_array_equal(ops.leaky_relu_f32_cuda(dx, 0.1).cpu().numpy(), O.leaky_relu(t32(x), 0.1).numpy())
+    a, b, c = (r.standard_normal((5, 33)).astype(np.float32) for _ in range(3))
+    da, dbb, dc = dev(cuda, a, b, c)
+    np.testing.assert_array_equal(ops.add_f32_cuda(da, dbb).cpu().numpy(), a + b)
+    np.testing.assert_array_equal(ops.add3_scale_f32_cuda(da, dbb, dc, 1 / 3).cpu().numpy(),
+                                  ((a + b) + c) * np.float32(1 / 3))
+    np.testing.assert_array_equal(ops.scale_f32_cuda(da, 0.5).cpu().numpy(), a * np.float32(0.5))
+    for left, right in ((1, 0), (0, 3), (4, 4)):
+        np.testing.assert_array_equal(ops.pad_reflect1d_f32_cuda(da, left, right).cpu().numpy(),
+                                      O.pad_reflect1d(t32(a), left, right).numpy())
+    s = r.standard_normal((1, 128)).astype(np.float32)
+    wt = (r.standard_normal((128, 1000)) / math.sqrt(128)).astype(np.float32)
+    bb = r.standard_normal(1000).astype(np.float32)
+    ds, dwt, dbv = dev(cuda, s, wt, bb)
+    np.testing.assert_allclose(ops.gemm_bias_f32_cuda(ds, dwt, dbv).cpu().numpy(), s.astype(np.float64) @ wt + bb,
+                               atol=1e-5, rtol=1e-5)
+
+
+def test_errors_come_back_as_exceptions(cuda):
+    """Entry points report failures through their return code and lkc_last_error(); nothing aborts."""
+    from lokinfer_b200 import _lib, ops
+    x = torch.zeros(22, 8, device=cuda)
+    with pytest.raises(_lib.LkcError, match="istft_logits_f32_cuda"):
+        out = torch.empty(7, device=cuda)  # wrong out length, bypassing the Python rule
+        _lib.run("istft_logits_f32_cuda", [x.data_ptr(), out.data_ptr()], [22, 8, 7, 5, 20], (), None,
+                 torch.cuda.current_stream().cuda_stream)
+    # the context is still usable
+    assert ops.istft_logits_f32_cuda(x).shape == (35,)
