@@ -231,7 +231,7 @@ def istft_logits_torch(x, n_fft=20, hop=5):
     bins = n_fft // 2 + 1
     mag, ph = torch.exp(x[:bins]), torch.sin(x[bins:])
     spec = torch.complex(mag * torch.cos(ph), mag * torch.sin(ph))
-    win = torch.hann_window(n_fft, periodic=True, dtype=x.dtype)
+    win = torch.hann_window(n_fft, periodic=True, dtype=x.dtype, device=x.device)
     return torch.istft(spec[None], n_fft, hop_length=hop, win_length=n_fft, window=win, center=True)[0]
 
 
