@@ -110,6 +110,25 @@ LKC_API int lkc_conv1d_affine_f32_cuda(const LkcArgs* a, void* stream);
  * ints x(2) x2(2) x3(2) w(3) b(1) affine(2) out(2) stats(3) dilation padding tile; floats in_scale slope. */
 LKC_API int lkc_conv1d_leaky_mean3_f32_cuda(const LkcArgs* a, void* stream);
 
+/* Tensor-core path of the fused conv family (tcgen05, TMEM accumulators, 3xTF32): the counterpart of the
+ * reference's prepare / destroy hooks (PrepareFn / DestroyFn, include/lokinfer/runtime/kernel.h:56-58) and of its
+ * build-time weight packing (models/kokoro/model.py:60-65). Run once per constant weight:
+ *   n = lkc_conv1d_tc_pack_floats(Co, Ci, K)       floats of the pack; 0 = shape not eligible (needs Co % 128 == 0,
+ *                                                  Ci % 16 == 0, K <= 64), the CUDA-core kernel serves it
+ *   lkc_conv1d_tc_pack_f32_cuda: ptrs w[Co,Ci,K] | wp[n]; ints w(3) wp(1)     hi / lo TF32 split in the UMMA layout
+ *   st = lkc_conv1d_state_create(wp, Co, Ci, K)    host-side handle; pass it as LkcArgs.state of the conv1d_* calls
+ * A conv call with a state whose shape is eligible ((K - 1) * dilation <= 64, no mean3 input) runs on the tensor
+ * cores; anything else runs on the CUDA-core kernel with identical semantics. lkc_conv1d_tc_status reads (and
+ * optionally clears) the device status word the kernel sets if one of its bounded waits gave up (0 = ok); it
+ * synchronises the device. lkc_set_conv_path(1) forces the CUDA-core kernel (A/B testing), 0 restores the default. */
+typedef struct LkcConvState LkcConvState;
+LKC_API int64_t lkc_conv1d_tc_pack_floats(int64_t co, int64_t ci, int64_t k);
+LKC_API int lkc_conv1d_tc_pack_f32_cuda(const LkcArgs* a, void* stream);
+LKC_API LkcConvState* lkc_conv1d_state_create(const void* wp, int64_t co, int64_t ci, int64_t k);
+LKC_API void lkc_conv1d_state_destroy(LkcConvState* st);
+LKC_API int lkc_conv1d_tc_status(int* status, int reset);
+LKC_API int lkc_set_conv_path(int mode);
+
 /* conv_transpose1d_poly[_mean3]_f32_cpu (kernels/cpu/kokoro_conv.cpp:139-229, adapters :294-309):
  *   out = reflect_pad_left(conv_transpose1d(leaky(xin, slope), w, b, stride, padding), pad_left) + res,
  *   xin = x or ((x + x2) + x3) * in_scale; needs K = taps * stride and 2 padding = (taps - 1) stride.

@@ -47,6 +47,16 @@ def lib():
         l.lkc_find_kernel.argtypes = [ctypes.c_char_p]
         l.lkc_last_error.restype = ctypes.c_char_p
         l.lkc_build_info.restype = ctypes.c_char_p
+        l.lkc_conv1d_tc_pack_floats.restype = ctypes.c_int64
+        l.lkc_conv1d_tc_pack_floats.argtypes = [ctypes.c_int64] * 3
+        l.lkc_conv1d_state_create.restype = ctypes.c_void_p
+        l.lkc_conv1d_state_create.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64]
+        l.lkc_conv1d_state_destroy.restype = None
+        l.lkc_conv1d_state_destroy.argtypes = [ctypes.c_void_p]
+        l.lkc_conv1d_tc_status.restype = ctypes.c_int
+        l.lkc_conv1d_tc_status.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+        l.lkc_set_conv_path.restype = ctypes.c_int
+        l.lkc_set_conv_path.argtypes = [ctypes.c_int]
         _lib = l
     return _lib
 

@@ -1,6 +1,7 @@
 // C-ABI entry points of the conv family, the kernel registry and error reporting.
 #include <algorithm>
 #include <cstring>
+#include <new>
 
 #include "lkc_common.h"
 
@@ -103,7 +104,19 @@ struct Entry {
 }  // namespace
 
 // Routes one fused conv to the tensor-core kernel when the shape qualifies, else to the CUDA-core kernel.
-int convFused(const ConvFusedParams& p, cudaStream_t s) { return convSimt(p, 1, s); }
+namespace {
+int gConvPath = 0;  // 0 = tensor cores when eligible, 1 = CUDA-core kernel only
+}
+
+int convFused(const ConvFusedParams& p, cudaStream_t s) {
+  if (gConvPath == 0 && convTcEligible(p)) {
+    const ConvState* st = static_cast<const ConvState*>(p.state);
+    LKC_REQUIRE(st->wp && st->co == p.co && st->ci == p.ci && st->k == p.k,
+                "conv1d fused: the prepared state does not match the weight shape");
+    return convTc(p, st->wp, s);
+  }
+  return convSimt(p, 1, s);
+}
 
 }  // namespace lkc
 
@@ -153,6 +166,44 @@ extern "C" LKC_API int lkc_conv1d_leaky_mean3_f32_cuda(const LkcArgs* a, void* s
 extern "C" LKC_API int lkc_conv1d_f32_cuda(const LkcArgs* a, void* s) { return runConv1d(a, s, true); }
 extern "C" LKC_API int lkc_conv1d_nobias_f32_cuda(const LkcArgs* a, void* s) { return runConv1d(a, s, false); }
 
+// ints: w(Co, Ci, K) wp(n)
+extern "C" LKC_API int lkc_conv1d_tc_pack_f32_cuda(const LkcArgs* a, void* stream) {
+  LKC_REQUIRE(a && a->numPtrs == 2 && a->numInts == 4, "conv1d_tc_pack_f32_cuda: expected w | wp");
+  const int64_t co = a->ints[0], ci = a->ints[1], k = a->ints[2];
+  LKC_REQUIRE(co > 0 && ci > 0 && co % 128 == 0 && ci % 16 == 0 && k >= 1 && k <= 64,
+              "conv1d_tc_pack_f32_cuda: needs Co % 128 == 0, Ci % 16 == 0, 1 <= K <= 64");
+  LKC_REQUIRE(a->ints[3] == convTcPackFloats(co, ci, k), "conv1d_tc_pack_f32_cuda: wp must hold lkc_conv1d_tc_pack_floats");
+  return convTcPack(F(a, 0), O(a, 1), co, ci, k, S(stream));
+}
+
+extern "C" LKC_API int64_t lkc_conv1d_tc_pack_floats(int64_t co, int64_t ci, int64_t k) {
+  if (co <= 0 || ci <= 0 || co % 128 != 0 || ci % 16 != 0 || k < 1 || k > 64) return 0;
+  return convTcPackFloats(co, ci, k);
+}
+
+extern "C" LKC_API LkcConvState* lkc_conv1d_state_create(const void* wp, int64_t co, int64_t ci, int64_t k) {
+  if (!wp || lkc_conv1d_tc_pack_floats(co, ci, k) == 0) {
+    fail("conv1d_state_create: shape not eligible for the tensor-core path or null pack");
+    return nullptr;
+  }
+  ConvState* st = new (std::nothrow) ConvState{static_cast<const float*>(wp), co, ci, k};
+  if (!st) fail("conv1d_state_create: out of host memory");
+  return reinterpret_cast<LkcConvState*>(st);
+}
+
+extern "C" LKC_API void lkc_conv1d_state_destroy(LkcConvState* st) { delete reinterpret_cast<ConvState*>(st); }
+
+extern "C" LKC_API int lkc_conv1d_tc_status(int* status, int reset) {
+  LKC_REQUIRE(status, "conv1d_tc_status: null out pointer");
+  return convTcStatus(status, reset != 0);
+}
+
+extern "C" LKC_API int lkc_set_conv_path(int mode) {
+  LKC_REQUIRE(mode == 0 || mode == 1, "set_conv_path: mode must be 0 (auto) or 1 (CUDA cores only)");
+  gConvPath = mode;
+  return 0;
+}
+
 namespace {
 // Sorted by name.
 const Entry kEntries[] = {
@@ -169,6 +220,7 @@ const Entry kEntries[] = {
     {"conv1d_nobias_f32_cuda", lkc_conv1d_nobias_f32_cuda},
     {"conv1d_snake_f32_cuda", lkc_conv1d_snake_f32_cuda},
     {"conv1d_snake_res_f32_cuda", lkc_conv1d_snake_res_f32_cuda},
+    {"conv1d_tc_pack_f32_cuda", lkc_conv1d_tc_pack_f32_cuda},
     {"conv_transpose1d_f32_cuda", lkc_conv_transpose1d_f32_cuda},
     {"conv_transpose1d_poly_f32_cuda", lkc_conv_transpose1d_poly_f32_cuda},
     {"conv_transpose1d_poly_mean3_f32_cuda", lkc_conv_transpose1d_poly_mean3_f32_cuda},
@@ -192,4 +244,4 @@ extern "C" LKC_API LkcRunFn lkc_find_kernel(const char* name) {
   return nullptr;
 }
 extern "C" LKC_API const char* lkc_last_error(void) { return gError; }
-extern "C" LKC_API const char* lkc_build_info(void) { return "lkc sm_100a: cuda-core conv/convT/stats/istft"; }
+extern "C" LKC_API const char* lkc_build_info(void) { return "lkc sm_100a: tcgen05 3xTF32 fused conv + cuda-core conv/convT/stats/istft"; }

@@ -1,0 +1,730 @@
+// Tensor-core fused conv1d for sm_100a: implicit GEMM on tcgen05 with TMEM accumulators, 3xTF32.
+//
+//   out[co, t] = sum_{ci, kk} W[co, ci, kk] * A[ci, t + kk d - pad],  A = act((x - mean) * scale + beta), zero outside
+//   [0, L); epilogue + bias [+ residual] [* oscale] and the per-(channel, 128-column chunk) (mean, M2).
+//
+// GEMM view: D[128 co, 256 t] += Wtap[128 co, 16 ci] * Ashift[16 ci, 256 t] for every 16-channel chunk and tap.
+// f32 accuracy comes from the 3xTF32 split: v = hi + lo with hi = tf32(v) (round to nearest) and lo = v - hi (exact
+// in f32); out = sum Whi Ahi + (sum Wlo Ahi + Whi Alo) (the lo*lo term, 2^-22 relative, is dropped).
+//
+// The tensor core adds into its f32 accumulator with truncation, so a long accumulation chain drifts towards zero by
+// about 1.5e-8 of the result per MMA (measured: the error grows linearly with the chain length). Two accumulators
+// keep that out of the result: Dhi (TMEM columns 0-255) takes only the hi*hi products of ONE 16-channel chunk
+// (2 K taps MMAs), is then drained by the epilogue warps into f32 registers (round-to-nearest adds on the CUDA cores)
+// and restarted; Dlo (columns 256-511) takes every lo product of the tile, where the same drift is scaled by 2^-11.
+//
+// One persistent CTA per SM, 20 warps in 5 warpgroups, warp-specialised (registers rebalanced with setmaxnreg):
+//   warps 0-7   accumulate + epilogue: per chunk tcgen05.ld of Dhi into 128 running sums per thread; per tile + Dlo,
+//               bias / residual / oscale, chunk statistics, and a shared-memory transpose so that global reads
+//               (residual) and writes (out) are contiguous along time
+//   warps 8-15  activation producers: global x -> affine -> Snake / leaky -> hi / lo split -> shared memory in the
+//               K-major no-swizzle UMMA layout [channel group of 4][time row][4 channels]: a tap shift of kk*d time
+//               steps is a +16*kk*d byte offset of the descriptor start address, so one staged window serves all taps
+//   warp 16     weight producer: cp.async.bulk of pre-packed 16 KB blocks (hi | lo of one [128 co x 16 ci] tap slice,
+//               already in the UMMA layout) from global (L2-resident) into a ring of shared-memory stages
+//   warp 17     MMA issuer: one lane issues tcgen05.mma (kind::tf32, M128 N256 K8) and tcgen05.commit; the lo MMAs of
+//               a tap trail its hi MMAs by LAG taps so that the drain of Dhi overlaps tensor-core work
+// All hand-offs are mbarriers. Every wait is bounded: on a timeout the kernel records a status word, drains and
+// returns (TMEM is freed on every path).
+#include "lkc_common.h"
+
+namespace lkc {
+namespace {
+
+constexpr int NT = 256;         // time columns per tile (= UMMA N)
+constexpr int MT = 128;         // output channels per tile (= UMMA M)
+constexpr int KC = 16;          // input channels per staged chunk (one weight stage, two K8 steps)
+constexpr int NB = 3;           // activation buffers
+constexpr int EPI_WARPS = 8, PRO_WARPS = 8;
+constexpr int W_WARP = EPI_WARPS + PRO_WARPS, MMA_WARP = W_WARP + 1;
+constexpr int NWARPS = EPI_WARPS + PRO_WARPS + 4;  // two idle warps complete the fifth warpgroup
+constexpr int NTHREADS = NWARPS * 32;  // 640
+constexpr int LAUNCH_REGS = 96, EPI_REGS = 168, PRO_REGS = 48, CTL_REGS = 40;
+static_assert(NTHREADS * LAUNCH_REGS <= 65536, "launch register budget");
+// setmaxnreg moves registers inside the CTA's own launch allocation (NTHREADS * LAUNCH_REGS); an increase beyond what
+// the decreases release would block forever.
+static_assert(EPI_WARPS * 32 * EPI_REGS + PRO_WARPS * 32 * PRO_REGS + 4 * 32 * CTL_REGS <= NTHREADS * LAUNCH_REGS,
+              "register pool");
+constexpr int LAG = 2;  // taps by which the lo MMAs trail the hi MMAs
+constexpr int W_STAGE_FLOATS = 2 * MT * KC;           // hi + lo
+constexpr int W_STAGE_BYTES = W_STAGE_FLOATS * 4;     // 16384
+constexpr int STAGE_PITCH = 33;                       // floats per row of an epilogue transpose tile
+constexpr int STAGE_FLOATS = 32 * STAGE_PITCH;
+constexpr int MAX_HALO = 64;
+constexpr int MAX_W_STAGES = 4;
+static_assert(LAG + 2 <= MAX_W_STAGES, "the weight ring must hold the lagging taps plus one in flight");
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+constexpr uint64_t WAIT_LIMIT_NS = 200ull * 1000 * 1000;  // 0.2 s: a healthy wait is tens of microseconds
+constexpr int kMaxSmem = 232448;  // 227 KB per CTA on sm_100
+
+struct TcArgs {
+  const float *x, *wp, *bias, *affine, *alpha, *residual;
+  float *out, *stats;
+  int ci, co, k, dilation, padding;
+  int64_t l, lo, nchunks;
+  float slope, outScale;
+  int rows;        // staged time rows per buffer = NT + (k-1)*dilation
+  int wStages;     // weight ring depth
+  int numTTiles, numCoBlk;
+  int* status;
+};
+
+__device__ int gTcStatus = 0;  // 0 = ok; else (role << 8 | code) of the first bounded wait that gave up
+
+// ---------------------------------------------------------------------------------------------- PTX helpers
+
+__device__ __forceinline__ uint32_t smemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbarInit(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbarArriveExpectTx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemAddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbarTryWait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smemAddr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbarTest(uint64_t* bar, uint32_t parity) {  // non-blocking probe
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smemAddr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false after SPIN_LIMIT polls or when another role has already aborted.
+__device__ __forceinline__ uint64_t globalTimerNs() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up (false) after SPIN_LIMIT polls or WAIT_LIMIT_NS of wall time, whichever comes first, or as
+// soon as another role has aborted.
+__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile int* abortFlag) {
+  if (mbarTryWait(bar, parity)) return true;
+  const uint64_t t0 = globalTimerNs();
+  for (uint32_t spins = 0; !mbarTryWait(bar, parity); ++spins) {
+    if (*abortFlag || spins >= SPIN_LIMIT) return false;
+    if ((spins & 63) == 63 && globalTimerNs() - t0 > WAIT_LIMIT_NS) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void fenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fenceBarrierInit() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void bulkCopyG2S(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smemAddr(dst)),
+               "l"(src), "r"(bytes), "r"(smemAddr(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmemAlloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(slot)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmemRelinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmemDealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], kind::tf32, issued by one thread.
+__device__ __forceinline__ void mmaTf32(uint32_t dTmem, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
+      "l"(descA), "l"(descB), "r"(idesc), "r"(accum)
+      : "memory");
+}
+__device__ __forceinline__ void mmaCommit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar))
+               : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i gets lane (base lane + i), registers = columns.
+__device__ __forceinline__ void tmemLoad32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor, K-major, no swizzle: core matrix = 8 rows x 16 bytes stored contiguously (rows at
+// 16-byte pitch), `sbo` = byte distance between 8-row groups, `lbo` = byte distance between the two 16-byte K chunks
+// of one K8 step. Bits: [0,14) address >> 4, [16,30) lbo >> 4, [32,46) sbo >> 4, [46,48) version = 1, [61,64) layout 0.
+__device__ __forceinline__ uint64_t makeDesc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  return uint64_t((addr >> 4) & 0x3FFFu) | (uint64_t((lbo >> 4) & 0x3FFFu) << 16) |
+         (uint64_t((sbo >> 4) & 0x3FFFu) << 32) | (uint64_t(1) << 46);
+}
+// Instruction descriptor: D f32 (bits 4-5 = 1), A and B tf32 (bits 7-9 / 10-12 = 2), both K-major, N >> 3 at bit 17,
+// M >> 4 at bit 24.
+constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(NT >> 3) << 17) | (uint32_t(MT >> 4) << 24);
+
+__device__ __forceinline__ float tf32Round(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+
+// sin(u)^2 for any finite u, absolute error ~1.5e-7: u = n pi/2 + r with |r| <= pi/4 (three-term Cody-Waite),
+// sin^2(u) = sin^2(r) for even n and 1 - sin^2(r) for odd n.
+__device__ __forceinline__ float sinSq(float u) {
+  const float t = fmaf(u, 0.6366197723675814f, 12582912.f);
+  const float n = t - 12582912.f;
+  float r = fmaf(n, -1.5703125f, u);
+  r = fmaf(n, -4.837512969970703125e-4f, r);
+  r = fmaf(n, -7.54978995489188216e-8f, r);
+  const float s2 = r * r;
+  float p = fmaf(s2, 2.7557319e-6f, -1.9841270e-4f);
+  p = fmaf(p, s2, 8.3333333e-3f);
+  p = fmaf(p, s2, -1.6666667e-1f);
+  p = fmaf(p, s2, 1.f);
+  const float s = r * p;
+  const float q = s * s;
+  return (__float_as_int(t) & 1) ? 1.f - q : q;
+}
+
+template <int ACT>
+__device__ __forceinline__ float activate(float v, float mean, float scale, float beta, float alpha, float inv,
+                                          float slope) {
+  v = (v - mean) * scale + beta;
+  if (ACT == 1) v = fmaf(inv, sinSq(alpha * v), v);
+  if (ACT == 2) v = v >= 0.f ? v : v * slope;
+  return v;
+}
+
+template <int N>
+__device__ __forceinline__ void regInc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void regDec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// Position in the flattened (tile, 16-channel chunk, tap) sequence one CTA walks through.
+struct Cursor {
+  int tile, c, kk;
+  uint32_t chunkIt, wIt, tileIt;
+  __device__ __forceinline__ void advance(int k, int nChunks, int stride) {
+    ++wIt;
+    if (++kk == k) {
+      kk = 0;
+      ++chunkIt;
+      if (++c == nChunks) {
+        c = 0;
+        tile += stride;
+        ++tileIt;
+      }
+    }
+  }
+};
+
+template <int ACT>
+__global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
+  extern __shared__ __align__(1024) unsigned char smemRaw[];
+  const int rows = a.rows;
+  const int actBufFloats = 2 * KC * rows;  // hi + lo
+  float* const sAct = reinterpret_cast<float*>(smemRaw);          // NB buffers of [2 (hi, lo)][KC/4][rows][4]
+  float* const sW = sAct + NB * actBufFloats;                     // wStages stages of [2 (hi, lo)][KC/4][MT][4]
+  float* const sStage = sW + a.wStages * W_STAGE_FLOATS;          // EPI_WARPS transpose tiles of [32][STAGE_PITCH]
+  uint64_t* const bFull = reinterpret_cast<uint64_t*>(sStage + EPI_WARPS * STAGE_FLOATS);
+  uint64_t* const bEmpty = bFull + NB;
+  uint64_t* const wFull = bEmpty + NB;
+  uint64_t* const wEmpty = wFull + MAX_W_STAGES;
+  uint64_t* const hiFull = wEmpty + MAX_W_STAGES;
+  uint64_t* const hiEmpty = hiFull + 1;
+  uint64_t* const loFull = hiEmpty + 1;
+  uint64_t* const loEmpty = loFull + 1;
+  uint32_t* const tmemSlot = reinterpret_cast<uint32_t*>(loEmpty + 1);
+  volatile int* const abortFlag = reinterpret_cast<int*>(tmemSlot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int numTiles = a.numTTiles * a.numCoBlk;
+  const int nChunks16 = a.ci / KC;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NB; ++i) mbarInit(&bFull[i], PRO_WARPS), mbarInit(&bEmpty[i], 1);
+    for (int i = 0; i < MAX_W_STAGES; ++i) mbarInit(&wFull[i], 1), mbarInit(&wEmpty[i], 1);
+    mbarInit(hiFull, 1), mbarInit(hiEmpty, EPI_WARPS), mbarInit(loFull, 1), mbarInit(loEmpty, EPI_WARPS);
+    *abortFlag = 0;
+    fenceBarrierInit();
+  }
+  if (warp == MMA_WARP) {  // the MMA warp owns the TMEM allocation
+    tmemAlloc(tmemSlot, 512);
+    tmemRelinquish();
+  }
+  tcFenceBefore();
+  __syncthreads();
+  tcFenceAfter();
+  const uint32_t tmemBase = *tmemSlot;
+  const uint32_t tmemHi = tmemBase, tmemLo = tmemBase + NT;
+
+  auto giveUp = [&](int role, int code) {
+    if (lane == 0) {
+      atomicCAS(a.status, 0, (role << 8) | code);
+      *abortFlag = 1;
+    }
+  };
+
+  if (warp < EPI_WARPS) {
+    // ------------------------------------------------------------------ accumulate + epilogue
+    regInc<EPI_REGS>();
+    const int q = warp & 3, g = warp >> 2;  // TMEM lane quarter, 128-column half of the tile
+    float* tile = sStage + warp * STAGE_FLOATS;
+    const uint32_t laneBase = uint32_t(q * 32) << 16;
+    uint32_t chunkIt = 0, tileIt = 0;
+    bool dead = false;
+    for (int t = blockIdx.x; t < numTiles && !dead; t += gridDim.x, ++tileIt) {
+      const int tt = t / a.numCoBlk, cb = t - tt * a.numCoBlk;
+      float S[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) S[j] = 0.f;
+      for (int c = 0; c < nChunks16; ++c, ++chunkIt) {
+        if (!mbarWait(hiFull, chunkIt & 1, abortFlag)) {
+          giveUp(1, 1);
+          dead = true;
+          break;
+        }
+        tcFenceAfter();
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          float v[32];
+          tmemLoad32(tmemHi + laneBase + g * 128 + b * 32, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) S[b * 32 + j] += v[j];
+        }
+        tcFenceBefore();
+        __syncwarp();
+        if (lane == 0) mbarArrive(hiEmpty);
+      }
+      if (dead) break;
+      if (!mbarWait(loFull, tileIt & 1, abortFlag)) {
+        giveUp(1, 2);
+        break;
+      }
+      tcFenceAfter();
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        float v[32];
+        tmemLoad32(tmemLo + laneBase + g * 128 + b * 32, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) S[b * 32 + j] += v[j];
+      }
+      tcFenceBefore();
+      __syncwarp();
+      if (lane == 0) mbarArrive(loEmpty);
+
+      const int64_t tChunk = int64_t(tt) * NT + g * 128;  // first output column of this warp's 128-column chunk
+      const int coBase = cb * MT + q * 32;
+      const int co = coBase + lane;
+      const float bias = a.bias ? a.bias[co] : 0.f;
+      const int64_t nValid64 = a.lo - tChunk;
+      const int nValid = nValid64 <= 0 ? 0 : (nValid64 < 128 ? int(nValid64) : 128);
+      float pMean[4], pM2[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);  // valid columns here
+        const int64_t tb = tChunk + b * 32;
+        if (a.residual) {
+          // residual tile [32 channels][32 columns] read with lanes along time, transposed through shared memory
+#pragma unroll 8
+          for (int i = 0; i < 32; ++i)
+            tile[i * STAGE_PITCH + lane] = lane < nb ? a.residual[int64_t(coBase + i) * a.lo + tb + lane] : 0.f;
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) S[b * 32 + j] = (S[b * 32 + j] + bias) + tile[lane * STAGE_PITCH + j];
+          if (a.outScale != 1.f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) S[b * 32 + j] *= a.outScale;
+          }
+          __syncwarp();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) S[b * 32 + j] += bias;
+        }
+        // partial statistics of the valid columns (two passes in registers)
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) s += j < nb ? S[b * 32 + j] : 0.f;
+        const float m = nb > 0 ? s / float(nb) : 0.f;
+        float m2 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float d = j < nb ? S[b * 32 + j] - m : 0.f;
+          m2 = fmaf(d, d, m2);
+        }
+        pMean[b] = m, pM2[b] = m2;
+        // transpose back and store with lanes along time
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
+        __syncwarp();
+        if (lane < nb) {
+#pragma unroll 8
+          for (int i = 0; i < 32; ++i) a.out[int64_t(coBase + i) * a.lo + tb + lane] = tile[i * STAGE_PITCH + lane];
+        }
+        __syncwarp();
+      }
+      if (a.stats && nValid > 0) {
+        // exact combine of the four 32-column partials: mean = sum n_b m_b / n, M2 = sum M2_b + sum n_b (m_b - mean)^2
+        float sum = 0.f;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);
+          sum = fmaf(float(nb), pMean[b], sum);
+        }
+        const float mean = sum / float(nValid);
+        float m2 = 0.f;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);
+          const float d = pMean[b] - mean;
+          m2 += pM2[b] + float(nb) * d * d;
+        }
+        float* st = a.stats + (int64_t(co) * a.nchunks + tChunk / 128) * 2;
+        st[0] = mean;
+        st[1] = m2;
+      }
+    }
+  } else if (warp < EPI_WARPS + PRO_WARPS) {
+    // ------------------------------------------------------------------ activation producers
+    regDec<PRO_REGS>();
+    const int pw = warp - EPI_WARPS;
+    const int cg = pw & 3, half = pw >> 2;  // channel group of 4 inside the 16-channel chunk; row half
+    const int rowsHalf = (rows + 1) >> 1;
+    const int r0 = half * rowsHalf, r1 = (r0 + rowsHalf < rows) ? r0 + rowsHalf : rows;
+    uint32_t chunkIt = 0;
+    bool dead = false;
+    for (int t = blockIdx.x; t < numTiles && !dead; t += gridDim.x) {
+      const int tt = t / a.numCoBlk;
+      const int64_t pos0 = int64_t(tt) * NT - a.padding;  // input position of row 0
+      for (int c = 0; c < nChunks16; ++c, ++chunkIt) {
+        const uint32_t buf = chunkIt % NB;
+        if (!mbarWait(&bEmpty[buf], ((chunkIt / NB) & 1) ^ 1, abortFlag)) {
+          giveUp(2, 1);
+          dead = true;
+          break;
+        }
+        float* hi = sAct + buf * actBufFloats + cg * rows * 4;
+        float* lo = hi + KC * rows;
+        const int ch = c * KC + cg * 4;
+        float mean[4], scale[4], beta[4], alpha[4], inv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          mean[e] = a.affine ? a.affine[ch + e] : 0.f;
+          scale[e] = a.affine ? a.affine[a.ci + ch + e] : 1.f;
+          beta[e] = a.affine ? a.affine[2 * a.ci + ch + e] : 0.f;
+          alpha[e] = ACT == 1 ? a.alpha[ch + e] : 0.f;
+          inv[e] = ACT == 1 ? 1.f / alpha[e] : 0.f;
+        }
+        const float* xc = a.x + int64_t(ch) * a.l;
+        for (int rb = r0; rb < r1; rb += 64) {
+          float raw[2][4];
+          bool ok[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int r = rb + u * 32 + lane;
+            const int64_t pos = pos0 + r;
+            ok[u] = r < r1 && pos >= 0 && pos < a.l;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) raw[u][e] = ok[u] ? xc[int64_t(e) * a.l + pos] : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int r = rb + u * 32 + lane;
+            if (r < r1) {
+              float4 h, l;
+              float v[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                v[e] = ok[u] ? activate<ACT>(raw[u][e], mean[e], scale[e], beta[e], alpha[e], inv[e], a.slope) : 0.f;
+              h.x = tf32Round(v[0]), h.y = tf32Round(v[1]), h.z = tf32Round(v[2]), h.w = tf32Round(v[3]);
+              l.x = v[0] - h.x, l.y = v[1] - h.y, l.z = v[2] - h.z, l.w = v[3] - h.w;
+              *reinterpret_cast<float4*>(hi + r * 4) = h;
+              *reinterpret_cast<float4*>(lo + r * 4) = l;
+            }
+          }
+        }
+        fenceProxyAsync();  // generic-proxy stores -> visible to the tensor core (async proxy)
+        __syncwarp();
+        if (lane == 0) mbarArrive(&bFull[buf]);
+      }
+    }
+  } else {
+    regDec<CTL_REGS>();
+    if (warp == W_WARP) {
+      // ---------------------------------------------------------------- weight producer
+      uint32_t wIt = 0;
+      bool dead = false;
+      const int64_t blocksPerCo = int64_t(nChunks16) * a.k;  // 16 KB blocks per 128-channel output block
+      for (int t = blockIdx.x; t < numTiles && !dead; t += gridDim.x) {
+        const int tt = t / a.numCoBlk, cb = t - tt * a.numCoBlk;
+        const float* src = a.wp + int64_t(cb) * blocksPerCo * W_STAGE_FLOATS;
+        for (int64_t blk = 0; blk < blocksPerCo; ++blk, ++wIt) {
+          const uint32_t s = wIt % a.wStages;
+          if (!mbarWait(&wEmpty[s], ((wIt / a.wStages) & 1) ^ 1, abortFlag)) {
+            giveUp(3, 1);
+            dead = true;
+            break;
+          }
+          if (lane == 0) {
+            mbarArriveExpectTx(&wFull[s], W_STAGE_BYTES);
+            bulkCopyG2S(sW + s * W_STAGE_FLOATS, src + blk * W_STAGE_FLOATS, W_STAGE_BYTES, &wFull[s]);
+          }
+          __syncwarp();
+        }
+      }
+      // Every copy this warp issued must have landed before the CTA may exit. On the normal path the MMA warp has
+      // consumed them all; after an abort, wait (bounded) for the stages still in flight.
+      if (*abortFlag) {
+        const uint32_t issued = wIt;
+        for (uint32_t i = issued > uint32_t(a.wStages) ? issued - a.wStages : 0; i < issued; ++i) {
+          const uint64_t t0 = globalTimerNs();
+          uint32_t spins = 0;
+          while (!mbarTryWait(&wFull[i % a.wStages], (i / a.wStages) & 1) && ++spins < SPIN_LIMIT &&
+                 globalTimerNs() - t0 < WAIT_LIMIT_NS) {
+          }
+        }
+      }
+    } else if (warp == MMA_WARP) {
+      // ---------------------------------------------------------------- MMA issuer
+      const uint32_t actBufBytes = actBufFloats * 4, rowsBytes = rows * 16;
+      const uint32_t actBase = smemAddr(sAct), wBase = smemAddr(sW);
+      const int stride = gridDim.x, k = a.k;
+      const int lagTaps = LAG < k * nChunks16 ? LAG : 0;
+      Cursor hi{int(blockIdx.x), 0, 0, 0u, 0u, 0u}, lo = hi;
+      int ahead = 0;  // taps whose hi MMAs are issued and whose lo MMAs are not
+      bool dead = false;
+      while (lo.tile < numTiles && !dead) {
+        // Greedy order: the hi MMAs of the next tap go first while they may run ahead (at most lagTaps + 1 taps) and
+        // their operands are ready; otherwise pending lo MMAs keep the tensor core busy (e.g. while Dhi is drained).
+        bool doHi = hi.tile < numTiles && ahead <= lagTaps;
+        if (doHi && ahead > 0) {
+          const uint32_t buf = hi.chunkIt % NB, s = hi.wIt % a.wStages;
+          doHi = mbarTest(&wFull[s], (hi.wIt / a.wStages) & 1);
+          if (doHi && hi.kk == 0)
+            doHi = mbarTest(&bFull[buf], (hi.chunkIt / NB) & 1) && mbarTest(hiEmpty, (hi.chunkIt & 1) ^ 1);
+        }
+        if (doHi) {
+          // hi*hi MMAs of tap hi.kk into Dhi
+          const uint32_t buf = hi.chunkIt % NB, s = hi.wIt % a.wStages;
+          if (hi.kk == 0) {
+            if (!mbarWait(&bFull[buf], (hi.chunkIt / NB) & 1, abortFlag)) {
+              giveUp(4, 2);
+              dead = true;
+              break;
+            }
+            if (!mbarWait(hiEmpty, (hi.chunkIt & 1) ^ 1, abortFlag)) {  // Dhi drained by the epilogue warps
+              giveUp(4, 1);
+              dead = true;
+              break;
+            }
+          }
+          if (!mbarWait(&wFull[s], (hi.wIt / a.wStages) & 1, abortFlag)) {
+            giveUp(4, 3);
+            dead = true;
+            break;
+          }
+          tcFenceAfter();
+          if (lane == 0) {
+            const uint32_t bHi = actBase + buf * actBufBytes + uint32_t(hi.kk * a.dilation) * 16;
+            const uint32_t aHi = wBase + s * W_STAGE_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < KC / 8; ++ks) {
+              // one K8 step = two 16-byte K chunks: channel groups 2 ks and 2 ks + 1
+              const uint64_t dA = makeDesc(aHi + ks * 2 * (MT * 16), MT * 16, 128);
+              const uint64_t dB = makeDesc(bHi + ks * 2 * rowsBytes, rowsBytes, 128);
+              mmaTf32(tmemHi, dA, dB, kIdesc, (hi.kk == 0 && ks == 0) ? 0u : 1u);
+            }
+            if (hi.kk == k - 1) mmaCommit(hiFull);  // the chunk's chain is complete
+          }
+          __syncwarp();
+          hi.advance(k, nChunks16, stride);
+          ++ahead;
+        } else {
+          // lo MMAs (Wlo Ahi + Whi Alo) of tap lo.kk into Dlo; then the weight stage and, after the last tap of the
+          // chunk, the activation buffer are free
+          const uint32_t buf = lo.chunkIt % NB, s = lo.wIt % a.wStages;
+          if (lo.c == 0 && lo.kk == 0) {
+            if (!mbarWait(loEmpty, (lo.tileIt & 1) ^ 1, abortFlag)) {  // Dlo of the previous tile folded in
+              giveUp(4, 4);
+              dead = true;
+              break;
+            }
+            tcFenceAfter();
+          }
+          if (lane == 0) {
+            const uint32_t bHi = actBase + buf * actBufBytes + uint32_t(lo.kk * a.dilation) * 16;
+            const uint32_t bLo = bHi + (KC / 4) * rowsBytes;  // the lo half follows the KC/4 channel groups of hi
+            const uint32_t aHi = wBase + s * W_STAGE_BYTES, aLo = aHi + W_STAGE_BYTES / 2;
+#pragma unroll
+            for (int ks = 0; ks < KC / 8; ++ks) {
+              const uint64_t dAhi = makeDesc(aHi + ks * 2 * (MT * 16), MT * 16, 128);
+              const uint64_t dAlo = makeDesc(aLo + ks * 2 * (MT * 16), MT * 16, 128);
+              const uint64_t dBhi = makeDesc(bHi + ks * 2 * rowsBytes, rowsBytes, 128);
+              const uint64_t dBlo = makeDesc(bLo + ks * 2 * rowsBytes, rowsBytes, 128);
+              mmaTf32(tmemLo, dAlo, dBhi, kIdesc, (lo.c == 0 && lo.kk == 0 && ks == 0) ? 0u : 1u);
+              mmaTf32(tmemLo, dAhi, dBlo, kIdesc, 1u);
+            }
+            mmaCommit(&wEmpty[s]);
+            if (lo.kk == k - 1) {
+              mmaCommit(&bEmpty[buf]);
+              if (lo.c == nChunks16 - 1) mmaCommit(loFull);
+            }
+          }
+          __syncwarp();
+          lo.advance(k, nChunks16, stride);
+          --ahead;
+        }
+      }
+    }
+  }
+
+  tcFenceBefore();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tcFenceAfter();
+    tmemDealloc(tmemBase, 512);
+  }
+}
+
+__global__ void packWeightsKernel(const float* __restrict__ w, float* __restrict__ wp, int co, int ci, int k) {
+  // wp index = ((((cb * nC16 + c16) * k + kk) * 2 + part) * 4 + kc) * 128 * 4 + col * 4 + e
+  const int nC16 = ci / KC;
+  const int64_t n = int64_t(co / MT) * nC16 * k * W_STAGE_FLOATS;
+  for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < n; idx += int64_t(gridDim.x) * blockDim.x) {
+    int64_t r = idx;
+    const int e = int(r % 4);
+    r /= 4;
+    const int col = int(r % MT);
+    r /= MT;
+    const int kc = int(r % 4);
+    r /= 4;
+    const int part = int(r % 2);
+    r /= 2;
+    const int kk = int(r % k);
+    r /= k;
+    const int c16 = int(r % nC16);
+    const int cb = int(r / nC16);
+    const float v = w[(int64_t(cb * MT + col) * ci + (c16 * KC + kc * 4 + e)) * k + kk];
+    const float h = tf32Round(v);
+    wp[idx] = part == 0 ? h : v - h;
+  }
+}
+
+}  // namespace
+
+bool convTcEligible(const ConvFusedParams& p) {
+  return p.state != nullptr && p.x2 == nullptr && p.ci % KC == 0 && p.co % MT == 0 && p.ci >= KC &&
+         (p.k - 1) * p.dilation <= MAX_HALO && p.k >= 1 && p.k <= 64 && p.lo >= 1 && p.padding <= (1 << 20);
+}
+
+int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k) { return (co / MT) * (ci / KC) * k * W_STAGE_FLOATS; }
+
+int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, cudaStream_t s) {
+  LKC_REQUIRE(co % MT == 0 && ci % KC == 0 && co > 0 && ci > 0 && k >= 1 && k <= 64,
+              "conv1d_tc_pack_f32_cuda: needs Co % 128 == 0, Ci % 16 == 0, 1 <= K <= 64");
+  const int64_t n = convTcPackFloats(co, ci, k);
+  const int blocks = static_cast<int>(ceilDiv(n, 256) > 4096 ? 4096 : ceilDiv(n, 256));
+  packWeightsKernel<<<blocks, 256, 0, s>>>(w, wp, int(co), int(ci), int(k));
+  return launched("conv1d_tc_pack_f32_cuda");
+}
+
+template <int ACT>
+static int launchTc(const TcArgs& a, int grid, size_t smem, cudaStream_t s) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(convTcKernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    if (e != cudaSuccess) return failCuda("conv (tensor-core): cudaFuncSetAttribute", e);
+    configured[dev] = true;
+  }
+  convTcKernel<ACT><<<grid, NTHREADS, smem, s>>>(a);
+  return launched("conv (tensor-core)");
+}
+
+int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
+  TcArgs a;
+  a.x = p.x, a.wp = wp, a.bias = p.bias, a.affine = p.affine, a.alpha = p.alpha, a.residual = p.residual;
+  a.out = p.out, a.stats = p.stats;
+  a.ci = int(p.ci), a.co = int(p.co), a.k = int(p.k), a.dilation = int(p.dilation), a.padding = int(p.padding);
+  a.l = p.l, a.lo = p.lo, a.nchunks = statChunks(p.lo);
+  a.slope = p.slope, a.outScale = p.outScale;
+  a.rows = NT + (a.k - 1) * a.dilation;
+  const int64_t tTiles = ceilDiv(p.lo, NT);
+  LKC_REQUIRE(tTiles * (p.co / MT) < (1 << 30), "conv (tensor-core): too many tiles");
+  a.numTTiles = int(tTiles), a.numCoBlk = int(p.co / MT);
+  const size_t fixed = size_t(EPI_WARPS) * STAGE_FLOATS * 4 + 256;  // transpose tiles + barriers / slots
+  const size_t act = size_t(NB) * 2 * KC * a.rows * 4;
+  LKC_REQUIRE(fixed + act + 2 * W_STAGE_BYTES <= size_t(kMaxSmem), "conv (tensor-core): window too large");
+  int ws = int((size_t(kMaxSmem) - fixed - act) / W_STAGE_BYTES);
+  a.wStages = ws > MAX_W_STAGES ? MAX_W_STAGES : ws;
+  const size_t smem = fixed + act + size_t(a.wStages) * W_STAGE_BYTES;
+  // Per-device constants, looked up once (the first call on a device must not be inside a stream capture).
+  static int* statusPtr[64] = {};
+  static int smCount[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  LKC_REQUIRE(dev >= 0 && dev < 64, "conv (tensor-core): device index out of range");
+  if (!statusPtr[dev]) {
+    int* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), gTcStatus);
+    if (e != cudaSuccess) return failCuda("conv (tensor-core): cudaGetSymbolAddress", e);
+    e = cudaDeviceGetAttribute(&smCount[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return failCuda("conv (tensor-core): cudaDeviceGetAttribute", e);
+    statusPtr[dev] = ptr;
+  }
+  a.status = statusPtr[dev];
+  const int sms = smCount[dev];
+  const int tiles = a.numTTiles * a.numCoBlk;
+  const int grid = tiles < sms ? tiles : sms;
+  switch (p.act) {
+    case Act::None: return launchTc<0>(a, grid, smem, s);
+    case Act::Snake: return launchTc<1>(a, grid, smem, s);
+    case Act::Leaky: return launchTc<2>(a, grid, smem, s);
+  }
+  return fail("conv (tensor-core): bad activation");
+}
+
+int convTcStatus(int* out, bool reset) {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, gTcStatus, sizeof v);
+  if (e != cudaSuccess) return failCuda("conv1d_tc_status", e);
+  if (reset && v != 0) {
+    const int z = 0;
+    e = cudaMemcpyToSymbol(gTcStatus, &z, sizeof z);
+    if (e != cudaSuccess) return failCuda("conv1d_tc_status", e);
+  }
+  *out = v;
+  return 0;
+}
+
+}  // namespace lkc

@@ -62,4 +62,15 @@ int convFused(const ConvFusedParams& p, cudaStream_t s);
 // CUDA-core implicit-GEMM conv for any shape (conv_simt.cu). stride > 1 only for the plain conv1d.
 int convSimt(const ConvFusedParams& p, int64_t stride, cudaStream_t s);
 
+// Tensor-core (tcgen05, 3xTF32) fused conv (conv_tc.cu). `state` of ConvFusedParams is an LkcConvState.
+struct ConvState {
+  const float* wp;  // packed weights (convTcPack)
+  int64_t co, ci, k;
+};
+bool convTcEligible(const ConvFusedParams& p);
+int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k);
+int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, cudaStream_t s);
+int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s);
+int convTcStatus(int* out, bool reset);
+
 }  // namespace lkc

@@ -41,7 +41,13 @@ class Generator:
             self.ups_wp = [ops.convt_poly_weights_cuda(self.w["ups.0.weight"], 10, 5),
                            ops.convt_poly_weights_cuda(self.w["ups.1.weight"], 6, 3)]
         self.ident128 = torch.stack([torch.zeros(128), torch.ones(128), torch.zeros(128)]).to(self.device).contiguous()
-        self.conv_state = {}  # per-weight prepared state of the tensor-core conv (filled by prepare())
+        # Prepared state of every fused-conv weight the tensor-core kernel accepts (packed once, at init).
+        self.conv_state = {}
+        for k in self.w:
+            if k.endswith(".weight") and (".convs1." in k or ".convs2." in k or k == "conv_post.weight"):
+                st = ops.conv1d_prepare_f32_cuda(self.w[k])
+                if st is not None:
+                    self.conv_state[k[: -len(".weight")]] = st
         self._graphs = {}
 
     # ------------------------------------------------------------------ building blocks

@@ -330,8 +330,62 @@ def _fused_attrs(x, w, padding, dilation, tile):
     return dict(padding=_int(padding, "padding"), dilation=_int(dilation, "dilation"), tile=_int(tile, "tile"))
 
 
+class ConvState:
+    """Prepared state of one constant conv weight for the tensor-core kernel: the hi / lo TF32 pack in the UMMA
+    layout plus the host handle passed as `state` (the reference's prepare hook result, kernel.h:56-58)."""
+
+    def __init__(self, handle, wp, shape):
+        self.handle, self.wp, self.shape = handle, wp, shape
+
+    def __del__(self):
+        try:
+            if self.handle:
+                _lib.lib().lkc_conv1d_state_destroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+
+def conv1d_prepare_f32_cuda(w):
+    """Packs a constant conv weight f32[Co, Ci, K] once for the tensor-core path (run at init, like the reference's
+    hoisted weight preparation, docs/passes/hoist-init.md). Returns None when the shape is served by the CUDA-core
+    kernel instead (Co % 128, Ci % 16 or K > 64)."""
+    _f32(w, rank=3)
+    co, ci, k = (int(d) for d in w.shape)
+    n = int(_lib.lib().lkc_conv1d_tc_pack_floats(co, ci, k))
+    if n == 0:
+        return None
+    wp = _new(w, (n,))
+    _run("conv1d_tc_pack_f32_cuda", [w], [wp])
+    handle = _lib.lib().lkc_conv1d_state_create(wp.data_ptr(), co, ci, k)
+    if not handle:
+        raise _lib.LkcError(_lib.last_error())
+    return ConvState(handle, wp, (co, ci, k))
+
+
+def conv_tc_status(reset=True) -> int:
+    """Status word of the tensor-core conv kernel on the current device (0 = every bounded wait completed).
+    Synchronises the device."""
+    import ctypes
+    v = ctypes.c_int(0)
+    if _lib.lib().lkc_conv1d_tc_status(ctypes.byref(v), 1 if reset else 0) != 0:
+        raise _lib.LkcError(_lib.last_error())
+    return int(v.value)
+
+
+def set_conv_path(mode: str) -> None:
+    """"auto" (tensor cores when a prepared state is passed and the shape is eligible) or "simt" (CUDA cores only)."""
+    check(mode in ("auto", "simt"), "mode must be 'auto' or 'simt'")
+    if _lib.lib().lkc_set_conv_path(0 if mode == "auto" else 1) != 0:
+        raise _lib.LkcError(_lib.last_error())
+
+
 def _state_of(w, state):
-    return None if state is None else state.handle
+    if state is None:
+        return None
+    check(isinstance(state, ConvState) and state.shape == tuple(int(d) for d in w.shape),
+          "state must come from conv1d_prepare_f32_cuda of this weight")
+    return state.handle
 
 
 def conv1d_snake_f32_cuda(x, w, b, affine, alpha, residual=None, padding=0, dilation=1, tile=None, state=None):

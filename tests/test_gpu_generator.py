@@ -93,3 +93,12 @@ def test_full_size_properties(cuda, gen):
     assert (audio - basic).abs().max().item() <= 2 * WAVE_MAXABS
     ref = O.istft_logits_torch(post)  # torch's own CUDA iSTFT
     assert (audio - ref).abs().max().item() <= 1e-5 * ref.abs().max().item()
+    from lokinfer_b200 import ops
+    assert ops.conv_tc_status() == 0
+    # the tensor-core and CUDA-core conv kernels give the same waveform
+    ops.set_conv_path("simt")
+    try:
+        simt = gen.forward(*d)
+    finally:
+        ops.set_conv_path("auto")
+    assert (audio - simt).abs().max().item() <= WAVE_MAXABS

@@ -37,26 +37,43 @@ CONV_CASES = [(8, 8, 50, 3, 1), (16, 12, 700, 7, 3), (12, 16, 97, 11, 5), (128, 
               (128, 22, 961, 7, 1), (22, 128, 961, 1, 1)]
 
 
-@pytest.mark.parametrize("ci,co,l,k,d", CONV_CASES)
+# Shapes the tensor-core kernel takes (Co % 128 == 0, Ci % 16 == 0): every Kokoro (C, K, dilation) plus tile edges:
+# one partial tile, exact tile / chunk multiples, one column past a tile, many tiles per CTA, L < halo.
+TC_CASES = [(128, 128, 1201, 3, 1), (128, 128, 1201, 7, 3), (128, 128, 5000, 11, 5), (256, 256, 640, 11, 5),
+            (256, 256, 333, 3, 5), (128, 128, 256, 3, 1), (128, 128, 257, 7, 1), (128, 128, 128, 11, 1),
+            (128, 128, 20, 11, 5), (128, 128, 1, 3, 1), (16, 128, 700, 7, 3), (48, 128, 300, 5, 2),
+            (256, 128, 900, 3, 3), (128, 256, 900, 7, 5), (128, 128, 45000, 3, 1), (256, 256, 20800, 7, 1),
+            (128, 128, 19201, 11, 3)]
+
+
+@pytest.mark.parametrize("ci,co,l,k,d", CONV_CASES + TC_CASES)
 @pytest.mark.parametrize("variant", ["snake", "snake_res", "leaky", "leaky_res", "affine"])
 def test_conv1d_fused(cuda, ci, co, l, k, d, variant):
+    """Both kernels behind the fused-conv entry points: with a prepared state eligible shapes run on tcgen05, the
+    rest (and every shape without a state) on the CUDA-core kernel; each is held to the same bars."""
     from lokinfer_b200 import ops
+    if (ci, co, l, k, d) in TC_CASES and l > 6000 and variant not in ("snake", "snake_res"):
+        pytest.skip("large shapes: snake variants only (CPU oracle time)")
     x, w, b, affine, alpha, res = synth.conv_case(ci, co, l, k, ci * 31 + l + k)
     pad = d * (k - 1) // 2
     lo = l + 2 * pad - d * (k - 1)
     res = res[:, :lo]
     dx, dw, db, daf, dal, dres = dev(cuda, x, w, b, affine, alpha, np.ascontiguousarray(res))
-    kw = dict(padding=pad, dilation=d)
+    state = ops.conv1d_prepare_f32_cuda(dw)
+    assert (state is not None) == (co % 128 == 0 and ci % 16 == 0)
+    kw = dict(padding=pad, dilation=d, state=state)
+
+    okw = dict(padding=pad, dilation=d)
 
     def oracle(dt):
         a = [O.T(v, dt) for v in (x, w, b, affine, alpha, res)]
         if variant.startswith("snake"):
             return O.conv1d_fused(a[0], a[1], a[2], a[3], "snake", alpha=a[4],
-                                  residual=a[5] if variant == "snake_res" else None, **kw)
+                                  residual=a[5] if variant == "snake_res" else None, **okw)
         if variant.startswith("leaky"):
             rk = dict(residual=a[5], out_scale=0.7071067811865476) if variant == "leaky_res" else {}
-            return O.conv1d_fused(a[0], a[1], a[2], a[3], "leaky", slope=0.2, **kw, **rk)
-        return O.conv1d_fused(a[0], a[1], a[2], a[3], "none", **kw)
+            return O.conv1d_fused(a[0], a[1], a[2], a[3], "leaky", slope=0.2, **okw, **rk)
+        return O.conv1d_fused(a[0], a[1], a[2], a[3], "none", **okw)
 
     if variant.startswith("snake"):
         out, stats = ops.conv1d_snake_f32_cuda(dx, dw, db, daf, dal, residual=dres if variant == "snake_res" else None,
@@ -77,6 +94,21 @@ def test_conv1d_fused(cuda, ci, co, l, k, d, variant):
     assert e_gpu <= 2 * e_cpu + 2e-7
     check_stats(stats, out)
     np.testing.assert_allclose(stats[..., 0], st32.numpy()[..., 0], atol=2e-5, rtol=2e-5)
+    assert ops.conv_tc_status() == 0
+    if state is not None:  # the CUDA-core kernel on the same operands agrees with the tensor-core one
+        ops.set_conv_path("simt")
+        try:
+            if variant.startswith("snake"):
+                o2, s2 = ops.conv1d_snake_f32_cuda(dx, dw, db, daf, dal,
+                                                   residual=dres if variant == "snake_res" else None, **kw)
+            elif variant.startswith("leaky"):
+                rk = dict(residual=dres, out_scale=0.7071067811865476) if variant == "leaky_res" else {}
+                o2, s2 = ops.conv1d_leaky_f32_cuda(dx, dw, db, daf, slope=0.2, **kw, **rk)
+            else:
+                o2, s2 = ops.conv1d_affine_f32_cuda(dx, dw, db, daf, **kw)
+        finally:
+            ops.set_conv_path("auto")
+        assert rel_l2(out, o2.cpu().numpy()) <= REL_L2
 
 
 def test_conv1d_fused_golden(cuda):
