@@ -262,6 +262,48 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         dist.destroy_process_group()
 
 
+def run_sweep(args):
+    """Conv kernel sweep (f32, batch 1): one fused conv1d_snake_res launch per step at each point, timed with CUDA
+    events; prints one JSON line per point with achieved TFLOP/s (2 Co Ci K L / time) and the fraction of the 3xTF32
+    tensor roofline. --point Ci,Co,L,K,d runs a single point (used for ncu captures)."""
+    from lokinfer_b200 import ops
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    dev = torch.device("cuda:0")
+    pk = peaks()
+    peak = pk["bf16_tflops"] / 2.0 / 3.0
+    if args.point:
+        points = [tuple(int(v) for v in args.point.split(","))]
+    else:
+        points = [(c, c, l, k, d) for c in (128, 256, 512) for k in (3, 7, 11) for d in (1, 3, 5)
+                  for l in (320, 3200, 19200, 124800)]
+    for ci, co, l, k, d in points:
+        x, w, b, affine, alpha, res = synth.conv_case(ci, co, l, k, 7, big=False)
+        dx, dw, db, daf, dal, dres = [ops.to_cuda(v, dev) for v in (x, w, b, affine, alpha, res)]
+        st = ops.conv1d_prepare_f32_cuda(dw)
+        pad = d * (k - 1) // 2
+
+        def step():
+            return ops.conv1d_snake_f32_cuda(dx, dw, db, daf, dal, residual=dres, padding=pad, dilation=d, state=st)
+
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        flops = 2.0 * co * ci * k * l
+        tf = flops / (ms * 1e-3) / 1e12
+        print(json.dumps({"sweep": "conv1d_snake_res_f32_cuda", "ci": ci, "co": co, "L": l, "K": k, "dilation": d,
+                          "ms": ms, "tflops": tf, "frac_3xtf32_roofline": tf / peak, "peak_tflops": peak,
+                          "peak_source": pk["source"], "path": "tcgen05" if st is not None else "cuda-core",
+                          "tc_status": ops.conv_tc_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -270,6 +312,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--t", type=int, default=2080, help="generator input frames per utterance (2080 = 26 s, 320 = 4 s)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sweep", default=None, choices=["conv"], help="run the conv kernel sweep instead of the generator")
+    ap.add_argument("--point", default=None, help="single sweep point Ci,Co,L,K,dilation")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -277,6 +321,10 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.sweep:
+        if rank == 0:
+            run_sweep(args)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         print(f"bench.py: --gpus {args.gpus} needs torchrun with {args.gpus} ranks; running 1 rank", file=sys.stderr)

@@ -117,7 +117,7 @@ LKC_API int lkc_conv1d_leaky_mean3_f32_cuda(const LkcArgs* a, void* stream);
  *                                                  Ci % 16 == 0, K <= 64), the CUDA-core kernel serves it
  *   lkc_conv1d_tc_pack_f32_cuda: ptrs w[Co,Ci,K] | wp[n]; ints w(3) wp(1)     hi / lo TF32 split in the UMMA layout
  *   st = lkc_conv1d_state_create(wp, Co, Ci, K)    host-side handle; pass it as LkcArgs.state of the conv1d_* calls
- * A conv call with a state whose shape is eligible ((K - 1) * dilation <= 64, no mean3 input) runs on the tensor
+ * A conv call with a state whose shape is eligible ((K - 1) * dilation <= 50, no mean3 input) runs on the tensor
  * cores; anything else runs on the CUDA-core kernel with identical semantics. lkc_conv1d_tc_status reads (and
  * optionally clears) the device status word the kernel sets if one of its bounded waits gave up (0 = ok); it
  * synchronises the device. lkc_set_conv_path(1) forces the CUDA-core kernel (A/B testing), 0 restores the default. */
@@ -128,6 +128,11 @@ LKC_API LkcConvState* lkc_conv1d_state_create(const void* wp, int64_t co, int64_
 LKC_API void lkc_conv1d_state_destroy(LkcConvState* st);
 LKC_API int lkc_conv1d_tc_status(int* status, int reset);
 LKC_API int lkc_set_conv_path(int mode);
+/* Role-level cycle counters of the tensor-core kernel (the counterpart of the reference's per-kernel profiler,
+ * include/lokinfer/runtime/runtime.h:69-74): enable != 0 turns recording on for later launches; counters16 (may be
+ * NULL) receives the 16 sums recorded so far (MMA / epilogue / producer / weight-producer wait and phase cycles, see
+ * conv_tc.cu) and the counters are cleared. Synchronises the device. */
+LKC_API int lkc_conv1d_tc_profile(int enable, int64_t* counters16);
 
 /* conv_transpose1d_poly[_mean3]_f32_cpu (kernels/cpu/kokoro_conv.cpp:139-229, adapters :294-309):
  *   out = reflect_pad_left(conv_transpose1d(leaky(xin, slope), w, b, stride, padding), pad_left) + res,

@@ -198,6 +198,10 @@ extern "C" LKC_API int lkc_conv1d_tc_status(int* status, int reset) {
   return convTcStatus(status, reset != 0);
 }
 
+extern "C" LKC_API int lkc_conv1d_tc_profile(int enable, int64_t* counters16) {
+  return convTcProfile(enable, reinterpret_cast<long long*>(counters16));
+}
+
 extern "C" LKC_API int lkc_set_conv_path(int mode) {
   LKC_REQUIRE(mode == 0 || mode == 1, "set_conv_path: mode must be 0 (auto) or 1 (CUDA cores only)");
   gConvPath = mode;

@@ -14,16 +14,20 @@
 // and restarted; Dlo (columns 256-511) takes every lo product of the tile, where the same drift is scaled by 2^-11.
 //
 // One persistent CTA per SM, 20 warps in 5 warpgroups, warp-specialised (registers rebalanced with setmaxnreg):
-//   warps 0-7   accumulate + epilogue: per chunk tcgen05.ld of Dhi into 128 running sums per thread; per tile + Dlo,
-//               bias / residual / oscale, chunk statistics, and a shared-memory transpose so that global reads
-//               (residual) and writes (out) are contiguous along time
-//   warps 8-15  activation producers: global x -> affine -> Snake / leaky -> hi / lo split -> shared memory in the
-//               K-major no-swizzle UMMA layout [channel group of 4][time row][4 channels]: a tap shift of kk*d time
-//               steps is a +16*kk*d byte offset of the descriptor start address, so one staged window serves all taps
+//   warps 0-7   accumulate + epilogue: 128 running sums per thread, started from bias + residual (read with lanes
+//               along time, all loads in flight at once, transposed through shared memory) while the first chunk's
+//               MMAs run; per chunk += Dhi (tcgen05.ld); per tile += Dlo, oscale, chunk statistics and a transposed,
+//               time-contiguous store
+//   warps 8-15  activation producers: cp.async of the raw input window of the NEXT chunk into a staging buffer (the
+//               global latency hides behind a whole chunk of work), then affine -> Snake / leaky -> hi / lo split of
+//               the current chunk into shared memory in the K-major no-swizzle UMMA layout [channel group of 4]
+//               [time row][4 channels]: a tap shift of kk*d time steps is a +16*kk*d byte offset of the descriptor
+//               start address, so one staged window serves all taps
 //   warp 16     weight producer: cp.async.bulk of pre-packed 16 KB blocks (hi | lo of one [128 co x 16 ci] tap slice,
 //               already in the UMMA layout) from global (L2-resident) into a ring of shared-memory stages
-//   warp 17     MMA issuer: one lane issues tcgen05.mma (kind::tf32, M128 N256 K8) and tcgen05.commit; the lo MMAs of
-//               a tap trail its hi MMAs by LAG taps so that the drain of Dhi overlaps tensor-core work
+//   warp 17     hi MMA issuer: one lane issues the two hi*hi tcgen05.mma (kind::tf32, M128 N256 K8) of every tap
+//   warp 18     lo MMA issuer: the four lo MMAs of every tap. Two issuing threads keep the tensor pipe fed while one
+//               of them does its bookkeeping, and the lo stream runs on while Dhi is being drained
 // All hand-offs are mbarriers. Every wait is bounded: on a timeout the kernel records a status word, drains and
 // returns (TMEM is freed on every path).
 #include "lkc_common.h"
@@ -34,10 +38,11 @@ namespace {
 constexpr int NT = 256;         // time columns per tile (= UMMA N)
 constexpr int MT = 128;         // output channels per tile (= UMMA M)
 constexpr int KC = 16;          // input channels per staged chunk (one weight stage, two K8 steps)
-constexpr int NB = 3;           // activation buffers
+constexpr int NB = 2;           // activation (hi/lo) buffers
+constexpr int NRAW = 2;         // raw-input staging buffers filled by cp.async one chunk ahead
 constexpr int EPI_WARPS = 8, PRO_WARPS = 8;
-constexpr int W_WARP = EPI_WARPS + PRO_WARPS, MMA_WARP = W_WARP + 1;
-constexpr int NWARPS = EPI_WARPS + PRO_WARPS + 4;  // two idle warps complete the fifth warpgroup
+constexpr int W_WARP = EPI_WARPS + PRO_WARPS, MMA_WARP = W_WARP + 1, MMA_LO_WARP = W_WARP + 2;
+constexpr int NWARPS = EPI_WARPS + PRO_WARPS + 4;  // one idle warp completes the fifth warpgroup
 constexpr int NTHREADS = NWARPS * 32;  // 640
 constexpr int LAUNCH_REGS = 96, EPI_REGS = 168, PRO_REGS = 48, CTL_REGS = 40;
 static_assert(NTHREADS * LAUNCH_REGS <= 65536, "launch register budget");
@@ -45,14 +50,12 @@ static_assert(NTHREADS * LAUNCH_REGS <= 65536, "launch register budget");
 // the decreases release would block forever.
 static_assert(EPI_WARPS * 32 * EPI_REGS + PRO_WARPS * 32 * PRO_REGS + 4 * 32 * CTL_REGS <= NTHREADS * LAUNCH_REGS,
               "register pool");
-constexpr int LAG = 2;  // taps by which the lo MMAs trail the hi MMAs
 constexpr int W_STAGE_FLOATS = 2 * MT * KC;           // hi + lo
 constexpr int W_STAGE_BYTES = W_STAGE_FLOATS * 4;     // 16384
 constexpr int STAGE_PITCH = 33;                       // floats per row of an epilogue transpose tile
 constexpr int STAGE_FLOATS = 32 * STAGE_PITCH;
-constexpr int MAX_HALO = 64;
-constexpr int MAX_W_STAGES = 4;
-static_assert(LAG + 2 <= MAX_W_STAGES, "the weight ring must hold the lagging taps plus one in flight");
+constexpr int MAX_HALO = 50;     // (K - 1) * dilation of the widest Kokoro conv (K 11, dilation 5)
+constexpr int MAX_W_STAGES = 6, MIN_W_STAGES = 3;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr uint64_t WAIT_LIMIT_NS = 200ull * 1000 * 1000;  // 0.2 s: a healthy wait is tens of microseconds
 constexpr int kMaxSmem = 232448;  // 227 KB per CTA on sm_100
@@ -67,9 +70,11 @@ struct TcArgs {
   int wStages;     // weight ring depth
   int numTTiles, numCoBlk;
   int* status;
+  long long* prof;  // null, or 16 cycle counters summed over CTAs (see convTcProfile)
 };
 
-__device__ int gTcStatus = 0;  // 0 = ok; else (role << 8 | code) of the first bounded wait that gave up
+__device__ int gTcStatus = 0;
+__device__ long long gTcProf[16];  // wait / phase cycle sums of one representative warp per role (profiling runs)  // 0 = ok; else (role << 8 | code) of the first bounded wait that gave up
 
 // ---------------------------------------------------------------------------------------------- PTX helpers
 
@@ -133,6 +138,15 @@ __device__ __forceinline__ void bulkCopyG2S(void* dst, const void* src, uint32_t
                    smemAddr(dst)),
                "l"(src), "r"(bytes), "r"(smemAddr(bar))
                : "memory");
+}
+
+__device__ __forceinline__ void cpAsync4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smemAddr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cpAsyncWait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 __device__ __forceinline__ void tmemAlloc(uint32_t* slot, uint32_t cols) {
@@ -232,30 +246,34 @@ __device__ __forceinline__ void regDec() {
 // Position in the flattened (tile, 16-channel chunk, tap) sequence one CTA walks through.
 struct Cursor {
   int tile, c, kk;
-  uint32_t chunkIt, wIt, tileIt;
-  __device__ __forceinline__ void advance(int k, int nChunks, int stride) {
-    ++wIt;
+  int stage, buf;                                   // weight-ring stage, activation buffer
+  uint32_t stagePhase, bufPhase, chunkPar, tilePar;  // parities of the ring passes / chunk count / tile count
+  __device__ __forceinline__ void advance(int k, int nChunks, int stride, int wStages) {
+    if (++stage == wStages) stage = 0, stagePhase ^= 1;
     if (++kk == k) {
       kk = 0;
-      ++chunkIt;
+      chunkPar ^= 1;
+      if (++buf == NB) buf = 0, bufPhase ^= 1;
       if (++c == nChunks) {
         c = 0;
         tile += stride;
-        ++tileIt;
+        tilePar ^= 1;
       }
     }
   }
 };
 
-template <int ACT>
+template <int ACT, bool PROF>
 __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   extern __shared__ __align__(1024) unsigned char smemRaw[];
   const int rows = a.rows;
   const int actBufFloats = 2 * KC * rows;  // hi + lo
   float* const sAct = reinterpret_cast<float*>(smemRaw);          // NB buffers of [2 (hi, lo)][KC/4][rows][4]
-  float* const sW = sAct + NB * actBufFloats;                     // wStages stages of [2 (hi, lo)][KC/4][MT][4]
+  float* const sRaw = sAct + NB * actBufFloats;                   // NRAW buffers of [KC][rows] raw input
+  float* const sW = sRaw + NRAW * KC * rows;                      // wStages stages of [2 (hi, lo)][KC/4][MT][4]
   float* const sStage = sW + a.wStages * W_STAGE_FLOATS;          // EPI_WARPS transpose tiles of [32][STAGE_PITCH]
-  uint64_t* const bFull = reinterpret_cast<uint64_t*>(sStage + EPI_WARPS * STAGE_FLOATS);
+  float* const sPar = sStage + EPI_WARPS * STAGE_FLOATS;          // [5][ci]: mean, scale, beta, alpha, 1 / alpha
+  uint64_t* const bFull = reinterpret_cast<uint64_t*>(sPar + 5 * a.ci);
   uint64_t* const bEmpty = bFull + NB;
   uint64_t* const wFull = bEmpty + NB;
   uint64_t* const wEmpty = wFull + MAX_W_STAGES;
@@ -271,8 +289,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   const int nChunks16 = a.ci / KC;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NB; ++i) mbarInit(&bFull[i], PRO_WARPS), mbarInit(&bEmpty[i], 1);
-    for (int i = 0; i < MAX_W_STAGES; ++i) mbarInit(&wFull[i], 1), mbarInit(&wEmpty[i], 1);
+    for (int i = 0; i < NB; ++i) mbarInit(&bFull[i], PRO_WARPS), mbarInit(&bEmpty[i], 2);      // freed by both issuers
+    for (int i = 0; i < MAX_W_STAGES; ++i) mbarInit(&wFull[i], 1), mbarInit(&wEmpty[i], 2);  // freed by both issuers
     mbarInit(hiFull, 1), mbarInit(hiEmpty, EPI_WARPS), mbarInit(loFull, 1), mbarInit(loEmpty, EPI_WARPS);
     *abortFlag = 0;
     fenceBarrierInit();
@@ -287,6 +305,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   const uint32_t tmemBase = *tmemSlot;
   const uint32_t tmemHi = tmemBase, tmemLo = tmemBase + NT;
 
+  // mbarWait that adds the cycles it spent to acc when profiling is on
+  constexpr bool profOn = PROF;
+  auto waitT = [&](uint64_t* bar, uint32_t parity, long long& acc) -> bool {
+    if (!profOn) return mbarWait(bar, parity, abortFlag);
+    const long long t0 = clock64();
+    const bool ok = mbarWait(bar, parity, abortFlag);
+    acc += clock64() - t0;
+    return ok;
+  };
+  auto profAdd = [&](int slot, long long v) {
+    if (profOn && lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(a.prof + slot), (unsigned long long)v);
+  };
   auto giveUp = [&](int role, int code) {
     if (lane == 0) {
       atomicCAS(a.status, 0, (role << 8) | code);
@@ -302,13 +332,44 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
     const uint32_t laneBase = uint32_t(q * 32) << 16;
     uint32_t chunkIt = 0, tileIt = 0;
     bool dead = false;
+    long long wHi = 0, wLo = 0, cPre = 0, cFin = 0;
+    const long long tStart = clock64();
     for (int t = blockIdx.x; t < numTiles && !dead; t += gridDim.x, ++tileIt) {
       const int tt = t / a.numCoBlk, cb = t - tt * a.numCoBlk;
+      const long long tPre = clock64();
+      const int64_t tChunk = int64_t(tt) * NT + g * 128;  // first output column of this warp's 128-column chunk
+      const int coBase = cb * MT + q * 32;
+      const int co = coBase + lane;
+      const float bias = a.bias ? a.bias[co] : 0.f;
+      const int64_t nValid64 = a.lo - tChunk;
+      const int nValid = nValid64 <= 0 ? 0 : (nValid64 < 128 ? int(nValid64) : 128);
+      // Running sums start from bias (+ residual). The residual tile is read with lanes along time (all 128 loads
+      // of the thread in flight at once) and transposed through shared memory; this overlaps the first chunk's MMAs.
       float S[128];
+      if (a.residual) {
 #pragma unroll
-      for (int j = 0; j < 128; ++j) S[j] = 0.f;
+        for (int b = 0; b < 4; ++b) {
+          const bool ok = b * 32 + lane < nValid;
+          const float* rp = a.residual + int64_t(coBase) * a.lo + tChunk + b * 32 + lane;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) S[b * 32 + i] = ok ? rp[int64_t(i) * a.lo] : 0.f;
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tile[i * STAGE_PITCH + lane] = S[b * 32 + i];
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) S[b * 32 + j] = tile[lane * STAGE_PITCH + j] + bias;
+          __syncwarp();
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 128; ++j) S[j] = bias;
+      }
+      cPre += clock64() - tPre;
       for (int c = 0; c < nChunks16; ++c, ++chunkIt) {
-        if (!mbarWait(hiFull, chunkIt & 1, abortFlag)) {
+        if (!waitT(hiFull, chunkIt & 1, wHi)) {
           giveUp(1, 1);
           dead = true;
           break;
@@ -326,10 +387,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         if (lane == 0) mbarArrive(hiEmpty);
       }
       if (dead) break;
-      if (!mbarWait(loFull, tileIt & 1, abortFlag)) {
+      if (!waitT(loFull, tileIt & 1, wLo)) {
         giveUp(1, 2);
         break;
       }
+      const long long tFin = clock64();
       tcFenceAfter();
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
@@ -341,40 +403,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) mbarArrive(loEmpty);
+      if (a.residual && a.outScale != 1.f) {
+#pragma unroll
+        for (int j = 0; j < 128; ++j) S[j] *= a.outScale;
+      }
 
-      const int64_t tChunk = int64_t(tt) * NT + g * 128;  // first output column of this warp's 128-column chunk
-      const int coBase = cb * MT + q * 32;
-      const int co = coBase + lane;
-      const float bias = a.bias ? a.bias[co] : 0.f;
-      const int64_t nValid64 = a.lo - tChunk;
-      const int nValid = nValid64 <= 0 ? 0 : (nValid64 < 128 ? int(nValid64) : 128);
       float pMean[4], pM2[4];
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
         const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);  // valid columns here
         const int64_t tb = tChunk + b * 32;
-        if (a.residual) {
-          // residual tile [32 channels][32 columns] read with lanes along time, transposed through shared memory
-#pragma unroll 8
-          for (int i = 0; i < 32; ++i)
-            tile[i * STAGE_PITCH + lane] = lane < nb ? a.residual[int64_t(coBase + i) * a.lo + tb + lane] : 0.f;
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) S[b * 32 + j] = (S[b * 32 + j] + bias) + tile[lane * STAGE_PITCH + j];
-          if (a.outScale != 1.f) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) S[b * 32 + j] *= a.outScale;
-          }
-          __syncwarp();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) S[b * 32 + j] += bias;
-        }
         // partial statistics of the valid columns (two passes in registers)
-        float s = 0.f;
+        float sum = 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) s += j < nb ? S[b * 32 + j] : 0.f;
-        const float m = nb > 0 ? s / float(nb) : 0.f;
+        for (int j = 0; j < 32; ++j) sum += j < nb ? S[b * 32 + j] : 0.f;
+        const float m = nb > 0 ? sum / float(nb) : 0.f;
         float m2 = 0.f;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -382,13 +425,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           m2 = fmaf(d, d, m2);
         }
         pMean[b] = m, pM2[b] = m2;
-        // transpose back and store with lanes along time
+        // transpose and store with lanes along time
 #pragma unroll
         for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
         __syncwarp();
         if (lane < nb) {
-#pragma unroll 8
-          for (int i = 0; i < 32; ++i) a.out[int64_t(coBase + i) * a.lo + tb + lane] = tile[i * STAGE_PITCH + lane];
+          float* op = a.out + int64_t(coBase) * a.lo + tb + lane;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) op[int64_t(i) * a.lo] = tile[i * STAGE_PITCH + lane];
         }
         __syncwarp();
       }
@@ -412,7 +456,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         st[0] = mean;
         st[1] = m2;
       }
+      cFin += clock64() - tFin;
     }
+    if (warp == 0) profAdd(5, wHi), profAdd(6, wLo), profAdd(7, cPre), profAdd(8, cFin), profAdd(9, clock64() - tStart);
   } else if (warp < EPI_WARPS + PRO_WARPS) {
     // ------------------------------------------------------------------ activation producers
     regDec<PRO_REGS>();
@@ -420,76 +466,103 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
     const int cg = pw & 3, half = pw >> 2;  // channel group of 4 inside the 16-channel chunk; row half
     const int rowsHalf = (rows + 1) >> 1;
     const int r0 = half * rowsHalf, r1 = (r0 + rowsHalf < rows) ? r0 + rowsHalf : rows;
-    uint32_t chunkIt = 0;
-    bool dead = false;
-    for (int t = blockIdx.x; t < numTiles && !dead; t += gridDim.x) {
+    constexpr int SLOTS = (((NT + MAX_HALO + 1) >> 1) + 31) / 32;  // row slots of 32 lanes per warp
+    // per-channel parameters, once: sPar = [mean | scale | beta | alpha | 1 / alpha]
+    for (int c = threadIdx.x - EPI_WARPS * 32; c < a.ci; c += PRO_WARPS * 32) {
+      sPar[c] = a.affine ? a.affine[c] : 0.f;
+      sPar[a.ci + c] = a.affine ? a.affine[a.ci + c] : 1.f;
+      sPar[2 * a.ci + c] = a.affine ? a.affine[2 * a.ci + c] : 0.f;
+      const float al = ACT == 1 ? a.alpha[c] : 1.f;
+      sPar[3 * a.ci + c] = al;
+      sPar[4 * a.ci + c] = 1.f / al;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(PRO_WARPS * 32) : "memory");  // producer warps only
+
+    // cp.async of this thread's part of the raw window of (tile t, chunk c) into staging buffer rb
+    auto issueCopies = [&](int t, int c, int rb) {
       const int tt = t / a.numCoBlk;
       const int64_t pos0 = int64_t(tt) * NT - a.padding;  // input position of row 0
-      for (int c = 0; c < nChunks16; ++c, ++chunkIt) {
-        const uint32_t buf = chunkIt % NB;
-        if (!mbarWait(&bEmpty[buf], ((chunkIt / NB) & 1) ^ 1, abortFlag)) {
-          giveUp(2, 1);
-          dead = true;
-          break;
+      const float* xc = a.x + int64_t(c * KC + cg * 4) * a.l;
+      float* dst = sRaw + rb * (KC * rows) + cg * 4 * rows;
+#pragma unroll
+      for (int sl = 0; sl < SLOTS; ++sl) {
+        const int r = r0 + sl * 32 + lane;
+        const int64_t pos = pos0 + r;
+        if (r < r1 && pos >= 0 && pos < a.l) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) cpAsync4(dst + e * rows + r, xc + int64_t(e) * a.l + pos);
         }
-        float* hi = sAct + buf * actBufFloats + cg * rows * 4;
-        float* lo = hi + KC * rows;
-        const int ch = c * KC + cg * 4;
-        float mean[4], scale[4], beta[4], alpha[4], inv[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          mean[e] = a.affine ? a.affine[ch + e] : 0.f;
-          scale[e] = a.affine ? a.affine[a.ci + ch + e] : 1.f;
-          beta[e] = a.affine ? a.affine[2 * a.ci + ch + e] : 0.f;
-          alpha[e] = ACT == 1 ? a.alpha[ch + e] : 0.f;
-          inv[e] = ACT == 1 ? 1.f / alpha[e] : 0.f;
-        }
-        const float* xc = a.x + int64_t(ch) * a.l;
-        for (int rb = r0; rb < r1; rb += 64) {
-          float raw[2][4];
-          bool ok[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int r = rb + u * 32 + lane;
-            const int64_t pos = pos0 + r;
-            ok[u] = r < r1 && pos >= 0 && pos < a.l;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) raw[u][e] = ok[u] ? xc[int64_t(e) * a.l + pos] : 0.f;
-          }
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int r = rb + u * 32 + lane;
-            if (r < r1) {
-              float4 h, l;
-              float v[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                v[e] = ok[u] ? activate<ACT>(raw[u][e], mean[e], scale[e], beta[e], alpha[e], inv[e], a.slope) : 0.f;
-              h.x = tf32Round(v[0]), h.y = tf32Round(v[1]), h.z = tf32Round(v[2]), h.w = tf32Round(v[3]);
-              l.x = v[0] - h.x, l.y = v[1] - h.y, l.z = v[2] - h.z, l.w = v[3] - h.w;
-              *reinterpret_cast<float4*>(hi + r * 4) = h;
-              *reinterpret_cast<float4*>(lo + r * 4) = l;
-            }
-          }
-        }
-        fenceProxyAsync();  // generic-proxy stores -> visible to the tensor core (async proxy)
-        __syncwarp();
-        if (lane == 0) mbarArrive(&bFull[buf]);
       }
+    };
+
+    int t = blockIdx.x, c = 0;
+    uint32_t it = 0;
+    long long wB = 0, wCp = 0, cTr = 0;
+    const long long tStart = clock64();
+    if (t < numTiles) issueCopies(t, c, 0);
+    cpAsyncCommit();
+    while (t < numTiles) {
+      int tn = t, cn = c + 1;
+      if (cn == nChunks16) cn = 0, tn = t + gridDim.x;
+      if (tn < numTiles) issueCopies(tn, cn, (it + 1) % NRAW);
+      cpAsyncCommit();
+      const long long tCp = clock64();
+      cpAsyncWait<1>();  // this chunk's copies (the older group) have landed; the next chunk's stay in flight
+      wCp += clock64() - tCp;
+      const uint32_t buf = it % NB;
+      if (!waitT(&bEmpty[buf], ((it / NB) & 1) ^ 1, wB)) {
+        giveUp(2, 1);
+        break;
+      }
+      const long long tTr = clock64();
+      const int tt = t / a.numCoBlk;
+      const int64_t pos0 = int64_t(tt) * NT - a.padding;
+      float* hi = sAct + buf * actBufFloats + cg * rows * 4;
+      float* lo = hi + KC * rows;
+      const float* src = sRaw + (it % NRAW) * (KC * rows) + cg * 4 * rows;
+      const float* par = sPar + c * KC + cg * 4;  // this thread's four channels: broadcast shared-memory reads
+#pragma unroll 1
+      for (int sl = 0; sl < SLOTS; ++sl) {
+        const int r = r0 + sl * 32 + lane;
+        if (r < r1) {
+          const int64_t pos = pos0 + r;
+          const bool ok = pos >= 0 && pos < a.l;
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            v[e] = ok ? activate<ACT>(src[e * rows + r], par[e], par[a.ci + e], par[2 * a.ci + e], par[3 * a.ci + e],
+                                      par[4 * a.ci + e], a.slope)
+                      : 0.f;
+          float4 h, l;
+          h.x = tf32Round(v[0]), h.y = tf32Round(v[1]), h.z = tf32Round(v[2]), h.w = tf32Round(v[3]);
+          l.x = v[0] - h.x, l.y = v[1] - h.y, l.z = v[2] - h.z, l.w = v[3] - h.w;
+          *reinterpret_cast<float4*>(hi + r * 4) = h;
+          *reinterpret_cast<float4*>(lo + r * 4) = l;
+        }
+      }
+      fenceProxyAsync();  // generic-proxy stores -> visible to the tensor core (async proxy)
+      __syncwarp();
+      if (lane == 0) mbarArrive(&bFull[buf]);
+      cTr += clock64() - tTr;
+      t = tn, c = cn, ++it;
     }
+    cpAsyncWait<0>();
+    if (pw == 0) profAdd(10, wB), profAdd(11, wCp), profAdd(12, cTr), profAdd(13, clock64() - tStart);
   } else {
     regDec<CTL_REGS>();
     if (warp == W_WARP) {
       // ---------------------------------------------------------------- weight producer
       uint32_t wIt = 0;
       bool dead = false;
+      long long wW = 0;
+      const long long tStart = clock64();
       const int64_t blocksPerCo = int64_t(nChunks16) * a.k;  // 16 KB blocks per 128-channel output block
       for (int t = blockIdx.x; t < numTiles && !dead; t += gridDim.x) {
         const int tt = t / a.numCoBlk, cb = t - tt * a.numCoBlk;
         const float* src = a.wp + int64_t(cb) * blocksPerCo * W_STAGE_FLOATS;
         for (int64_t blk = 0; blk < blocksPerCo; ++blk, ++wIt) {
           const uint32_t s = wIt % a.wStages;
-          if (!mbarWait(&wEmpty[s], ((wIt / a.wStages) & 1) ^ 1, abortFlag)) {
+          if (!waitT(&wEmpty[s], ((wIt / a.wStages) & 1) ^ 1, wW)) {
             giveUp(3, 1);
             dead = true;
             break;
@@ -501,6 +574,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           __syncwarp();
         }
       }
+      profAdd(14, wW), profAdd(15, clock64() - tStart);
       // Every copy this warp issued must have landed before the CTA may exit. On the normal path the MMA warp has
       // consumed them all; after an abort, wait (bounded) for the stages still in flight.
       if (*abortFlag) {
@@ -513,97 +587,75 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           }
         }
       }
-    } else if (warp == MMA_WARP) {
-      // ---------------------------------------------------------------- MMA issuer
-      const uint32_t actBufBytes = actBufFloats * 4, rowsBytes = rows * 16;
-      const uint32_t actBase = smemAddr(sAct), wBase = smemAddr(sW);
-      const int stride = gridDim.x, k = a.k;
-      const int lagTaps = LAG < k * nChunks16 ? LAG : 0;
-      Cursor hi{int(blockIdx.x), 0, 0, 0u, 0u, 0u}, lo = hi;
-      int ahead = 0;  // taps whose hi MMAs are issued and whose lo MMAs are not
+    } else if (warp == MMA_WARP || warp == MMA_LO_WARP) {
+      // ---------------------------------------------------------------- MMA issuers
+      // Both walk the same (tile, chunk, tap) sequence. Descriptors are the base descriptor plus small offsets in
+      // 16-byte units (the address field is the low 14 bits) and ring positions are wrap counters, so only a handful
+      // of instructions separate two MMA groups: the tensor pipe streams at full rate only when MMAs arrive back to
+      // back.
+      const bool isHi = warp == MMA_WARP;
+      const uint32_t rowsUnits = rows;  // one staged time row = 16 bytes = one descriptor address unit
+      const uint64_t dA0 = makeDesc(smemAddr(sW), MT * 16, 128);
+      const uint64_t dB0 = makeDesc(smemAddr(sAct), rows * 16, 128);
+      constexpr uint32_t kStageU = W_STAGE_BYTES >> 4, kLoAU = (W_STAGE_BYTES / 2) >> 4, kKsAU = (2 * MT * 16) >> 4;
+      const uint32_t bufU = uint32_t(actBufFloats * 4) >> 4, loBU = (KC / 4) * rowsUnits, ksBU = 2 * rowsUnits;
+      const int stride = gridDim.x, k = a.k, dil = a.dilation, wStages = a.wStages;
+      Cursor cu{int(blockIdx.x), 0, 0, 0, 0, 0u, 0u, 0u, 0u};
       bool dead = false;
-      while (lo.tile < numTiles && !dead) {
-        // Greedy order: the hi MMAs of the next tap go first while they may run ahead (at most lagTaps + 1 taps) and
-        // their operands are ready; otherwise pending lo MMAs keep the tensor core busy (e.g. while Dhi is drained).
-        bool doHi = hi.tile < numTiles && ahead <= lagTaps;
-        if (doHi && ahead > 0) {
-          const uint32_t buf = hi.chunkIt % NB, s = hi.wIt % a.wStages;
-          doHi = mbarTest(&wFull[s], (hi.wIt / a.wStages) & 1);
-          if (doHi && hi.kk == 0)
-            doHi = mbarTest(&bFull[buf], (hi.chunkIt / NB) & 1) && mbarTest(hiEmpty, (hi.chunkIt & 1) ^ 1);
-        }
-        if (doHi) {
-          // hi*hi MMAs of tap hi.kk into Dhi
-          const uint32_t buf = hi.chunkIt % NB, s = hi.wIt % a.wStages;
-          if (hi.kk == 0) {
-            if (!mbarWait(&bFull[buf], (hi.chunkIt / NB) & 1, abortFlag)) {
-              giveUp(4, 2);
-              dead = true;
-              break;
-            }
-            if (!mbarWait(hiEmpty, (hi.chunkIt & 1) ^ 1, abortFlag)) {  // Dhi drained by the epilogue warps
+      long long wBf = 0, wHe = 0, wWf = 0;
+      const long long tStart = clock64();
+      while (cu.tile < numTiles) {
+        if (cu.kk == 0) {
+          if (!waitT(&bFull[cu.buf], cu.bufPhase, wBf)) {
+            giveUp(4, 2);
+            dead = true;
+          } else if (isHi) {
+            if (!waitT(hiEmpty, cu.chunkPar ^ 1, wHe)) {  // Dhi drained by the epilogue warps
               giveUp(4, 1);
               dead = true;
-              break;
             }
-          }
-          if (!mbarWait(&wFull[s], (hi.wIt / a.wStages) & 1, abortFlag)) {
-            giveUp(4, 3);
-            dead = true;
-            break;
-          }
-          tcFenceAfter();
-          if (lane == 0) {
-            const uint32_t bHi = actBase + buf * actBufBytes + uint32_t(hi.kk * a.dilation) * 16;
-            const uint32_t aHi = wBase + s * W_STAGE_BYTES;
-#pragma unroll
-            for (int ks = 0; ks < KC / 8; ++ks) {
-              // one K8 step = two 16-byte K chunks: channel groups 2 ks and 2 ks + 1
-              const uint64_t dA = makeDesc(aHi + ks * 2 * (MT * 16), MT * 16, 128);
-              const uint64_t dB = makeDesc(bHi + ks * 2 * rowsBytes, rowsBytes, 128);
-              mmaTf32(tmemHi, dA, dB, kIdesc, (hi.kk == 0 && ks == 0) ? 0u : 1u);
-            }
-            if (hi.kk == k - 1) mmaCommit(hiFull);  // the chunk's chain is complete
-          }
-          __syncwarp();
-          hi.advance(k, nChunks16, stride);
-          ++ahead;
-        } else {
-          // lo MMAs (Wlo Ahi + Whi Alo) of tap lo.kk into Dlo; then the weight stage and, after the last tap of the
-          // chunk, the activation buffer are free
-          const uint32_t buf = lo.chunkIt % NB, s = lo.wIt % a.wStages;
-          if (lo.c == 0 && lo.kk == 0) {
-            if (!mbarWait(loEmpty, (lo.tileIt & 1) ^ 1, abortFlag)) {  // Dlo of the previous tile folded in
+          } else if (cu.c == 0) {
+            if (!waitT(loEmpty, cu.tilePar ^ 1, wHe)) {  // Dlo of the previous tile folded into the running sums
               giveUp(4, 4);
               dead = true;
-              break;
-            }
-            tcFenceAfter();
-          }
-          if (lane == 0) {
-            const uint32_t bHi = actBase + buf * actBufBytes + uint32_t(lo.kk * a.dilation) * 16;
-            const uint32_t bLo = bHi + (KC / 4) * rowsBytes;  // the lo half follows the KC/4 channel groups of hi
-            const uint32_t aHi = wBase + s * W_STAGE_BYTES, aLo = aHi + W_STAGE_BYTES / 2;
-#pragma unroll
-            for (int ks = 0; ks < KC / 8; ++ks) {
-              const uint64_t dAhi = makeDesc(aHi + ks * 2 * (MT * 16), MT * 16, 128);
-              const uint64_t dAlo = makeDesc(aLo + ks * 2 * (MT * 16), MT * 16, 128);
-              const uint64_t dBhi = makeDesc(bHi + ks * 2 * rowsBytes, rowsBytes, 128);
-              const uint64_t dBlo = makeDesc(bLo + ks * 2 * rowsBytes, rowsBytes, 128);
-              mmaTf32(tmemLo, dAlo, dBhi, kIdesc, (lo.c == 0 && lo.kk == 0 && ks == 0) ? 0u : 1u);
-              mmaTf32(tmemLo, dAhi, dBlo, kIdesc, 1u);
-            }
-            mmaCommit(&wEmpty[s]);
-            if (lo.kk == k - 1) {
-              mmaCommit(&bEmpty[buf]);
-              if (lo.c == nChunks16 - 1) mmaCommit(loFull);
             }
           }
-          __syncwarp();
-          lo.advance(k, nChunks16, stride);
-          --ahead;
         }
+        if (!dead && !waitT(&wFull[cu.stage], cu.stagePhase, wWf)) {
+          giveUp(4, 3);
+          dead = true;
+        }
+        if (dead) break;
+        tcFenceAfter();
+        if (lane == 0) {
+          const uint64_t dAh = dA0 + uint32_t(cu.stage) * kStageU;
+          const uint64_t dBh = dB0 + uint32_t(cu.buf) * bufU + uint32_t(cu.kk * dil);
+          if (isHi) {
+            mmaTf32(tmemHi, dAh, dBh, kIdesc, cu.kk == 0 ? 0u : 1u);
+            mmaTf32(tmemHi, dAh + kKsAU, dBh + ksBU, kIdesc, 1u);
+            mmaCommit(&wEmpty[cu.stage]);
+            if (cu.kk == k - 1) {
+              mmaCommit(hiFull);  // the chunk's hi chain is complete
+              mmaCommit(&bEmpty[cu.buf]);
+            }
+          } else {
+            const uint64_t dAl = dAh + kLoAU, dBl = dBh + loBU;
+            mmaTf32(tmemLo, dAl, dBh, kIdesc, (cu.c == 0 && cu.kk == 0) ? 0u : 1u);
+            mmaTf32(tmemLo, dAh, dBl, kIdesc, 1u);
+            mmaTf32(tmemLo, dAl + kKsAU, dBh + ksBU, kIdesc, 1u);
+            mmaTf32(tmemLo, dAh + kKsAU, dBl + ksBU, kIdesc, 1u);
+            mmaCommit(&wEmpty[cu.stage]);  // weight stage free once both issuers' MMAs have read it
+            if (cu.kk == k - 1) {
+              mmaCommit(&bEmpty[cu.buf]);  // last tap of the chunk: activation buffer free
+              if (cu.c == nChunks16 - 1) mmaCommit(loFull);
+            }
+          }
+        }
+        __syncwarp();
+        cu.advance(k, nChunks16, stride, wStages);
       }
+      if (isHi) profAdd(0, wBf), profAdd(1, wHe), profAdd(2, wWf), profAdd(4, clock64() - tStart);
+      else profAdd(3, wHe);
     }
   }
 
@@ -641,9 +693,23 @@ __global__ void packWeightsKernel(const float* __restrict__ w, float* __restrict
 
 }  // namespace
 
+// Dynamic shared memory of one CTA: activation buffers, raw staging, weight ring (as deep as fits, MIN..MAX stages),
+// transpose tiles, per-channel parameters, barriers. 0 if the minimum ring does not fit.
+static size_t convTcSmemBytes(int64_t ci, int rows, int* wStages) {
+  const size_t fixed = size_t(EPI_WARPS) * STAGE_FLOATS * 4 + size_t(5) * ci * 4 + 256;
+  const size_t act = size_t(NB) * 2 * KC * rows * 4 + size_t(NRAW) * KC * rows * 4;
+  if (fixed + act + size_t(MIN_W_STAGES) * W_STAGE_BYTES > size_t(kMaxSmem)) return 0;
+  int ws = int((size_t(kMaxSmem) - fixed - act) / W_STAGE_BYTES);
+  if (ws > MAX_W_STAGES) ws = MAX_W_STAGES;
+  if (wStages) *wStages = ws;
+  return fixed + act + size_t(ws) * W_STAGE_BYTES;
+}
+
 bool convTcEligible(const ConvFusedParams& p) {
-  return p.state != nullptr && p.x2 == nullptr && p.ci % KC == 0 && p.co % MT == 0 && p.ci >= KC &&
-         (p.k - 1) * p.dilation <= MAX_HALO && p.k >= 1 && p.k <= 64 && p.lo >= 1 && p.padding <= (1 << 20);
+  if (!(p.state != nullptr && p.x2 == nullptr && p.ci % KC == 0 && p.co % MT == 0 && p.ci >= KC && p.k >= 1 &&
+        p.k <= 64 && (p.k - 1) * p.dilation <= MAX_HALO && p.lo >= 1 && p.padding <= (1 << 20) && p.ci <= 4096))
+    return false;
+  return convTcSmemBytes(p.ci, NT + int((p.k - 1) * p.dilation), nullptr) != 0;
 }
 
 int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k) { return (co / MT) * (ci / KC) * k * W_STAGE_FLOATS; }
@@ -657,18 +723,36 @@ int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, cud
   return launched("conv1d_tc_pack_f32_cuda");
 }
 
-template <int ACT>
+template <int ACT, bool PROF>
 static int launchTc(const TcArgs& a, int grid, size_t smem, cudaStream_t s) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(convTcKernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    cudaError_t e = cudaFuncSetAttribute(convTcKernel<ACT, PROF>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return failCuda("conv (tensor-core): cudaFuncSetAttribute", e);
     configured[dev] = true;
   }
-  convTcKernel<ACT><<<grid, NTHREADS, smem, s>>>(a);
+  convTcKernel<ACT, PROF><<<grid, NTHREADS, smem, s>>>(a);
   return launched("conv (tensor-core)");
+}
+
+static bool gProfileOn = false;
+
+// Profiling counters of the tensor-core kernel (cycles, summed over CTAs and launches since the last reset; one
+// representative warp per role): [0..4] MMA warp: wait activations, wait Dhi drained, wait weights, wait Dlo folded,
+// total; [5..9] epilogue warp 0: wait Dhi, wait Dlo, residual preload, final phase, total; [10..13] producer warp 0:
+// wait buffer free, wait cp.async, transform, total; [14..15] weight producer: wait stage free, total.
+int convTcProfile(int enable, long long* out16) {
+  gProfileOn = enable != 0;
+  if (out16) {
+    cudaError_t e = cudaMemcpyFromSymbol(out16, gTcProf, sizeof(long long) * 16);
+    if (e != cudaSuccess) return failCuda("conv1d_tc_profile", e);
+  }
+  static const long long zeros[16] = {};
+  cudaError_t e = cudaMemcpyToSymbol(gTcProf, zeros, sizeof zeros);
+  if (e != cudaSuccess) return failCuda("conv1d_tc_profile", e);
+  return 0;
 }
 
 int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
@@ -682,14 +766,11 @@ int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
   const int64_t tTiles = ceilDiv(p.lo, NT);
   LKC_REQUIRE(tTiles * (p.co / MT) < (1 << 30), "conv (tensor-core): too many tiles");
   a.numTTiles = int(tTiles), a.numCoBlk = int(p.co / MT);
-  const size_t fixed = size_t(EPI_WARPS) * STAGE_FLOATS * 4 + 256;  // transpose tiles + barriers / slots
-  const size_t act = size_t(NB) * 2 * KC * a.rows * 4;
-  LKC_REQUIRE(fixed + act + 2 * W_STAGE_BYTES <= size_t(kMaxSmem), "conv (tensor-core): window too large");
-  int ws = int((size_t(kMaxSmem) - fixed - act) / W_STAGE_BYTES);
-  a.wStages = ws > MAX_W_STAGES ? MAX_W_STAGES : ws;
-  const size_t smem = fixed + act + size_t(a.wStages) * W_STAGE_BYTES;
+  const size_t smem = convTcSmemBytes(p.ci, a.rows, &a.wStages);
+  LKC_REQUIRE(smem != 0, "conv (tensor-core): window too large");
   // Per-device constants, looked up once (the first call on a device must not be inside a stream capture).
   static int* statusPtr[64] = {};
+  static long long* profPtr[64] = {};
   static int smCount[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -700,16 +781,22 @@ int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
     if (e != cudaSuccess) return failCuda("conv (tensor-core): cudaGetSymbolAddress", e);
     e = cudaDeviceGetAttribute(&smCount[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return failCuda("conv (tensor-core): cudaDeviceGetAttribute", e);
+    long long* pp = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&pp), gTcProf);
+    if (e != cudaSuccess) return failCuda("conv (tensor-core): cudaGetSymbolAddress", e);
+    profPtr[dev] = pp;
     statusPtr[dev] = ptr;
   }
   a.status = statusPtr[dev];
+  a.prof = gProfileOn ? profPtr[dev] : nullptr;
   const int sms = smCount[dev];
   const int tiles = a.numTTiles * a.numCoBlk;
   const int grid = tiles < sms ? tiles : sms;
+  const bool prof = a.prof != nullptr;
   switch (p.act) {
-    case Act::None: return launchTc<0>(a, grid, smem, s);
-    case Act::Snake: return launchTc<1>(a, grid, smem, s);
-    case Act::Leaky: return launchTc<2>(a, grid, smem, s);
+    case Act::None: return prof ? launchTc<0, true>(a, grid, smem, s) : launchTc<0, false>(a, grid, smem, s);
+    case Act::Snake: return prof ? launchTc<1, true>(a, grid, smem, s) : launchTc<1, false>(a, grid, smem, s);
+    case Act::Leaky: return prof ? launchTc<2, true>(a, grid, smem, s) : launchTc<2, false>(a, grid, smem, s);
   }
   return fail("conv (tensor-core): bad activation");
 }

@@ -72,5 +72,6 @@ int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k);
 int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, cudaStream_t s);
 int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s);
 int convTcStatus(int* out, bool reset);
+int convTcProfile(int enable, long long* out16);
 
 }  // namespace lkc

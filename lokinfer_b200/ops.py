@@ -373,6 +373,21 @@ def conv_tc_status(reset=True) -> int:
     return int(v.value)
 
 
+TC_PROFILE_FIELDS = ("mma_wait_act", "mma_wait_drain", "mma_wait_weights", "mma_wait_lofold", "mma_total",
+                     "epi_wait_hi", "epi_wait_lo", "epi_preload", "epi_final", "epi_total",
+                     "pro_wait_free", "pro_wait_cpasync", "pro_transform", "pro_total", "wpro_wait_free", "wpro_total")
+
+
+def conv_tc_profile(enable: bool) -> dict:
+    """Turns the tensor-core kernel's role-level cycle counters on / off and returns (then clears) what was recorded:
+    cycles summed over CTAs and launches, one representative warp per role. Synchronises the device."""
+    import ctypes
+    buf = (ctypes.c_int64 * 16)()
+    if _lib.lib().lkc_conv1d_tc_profile(1 if enable else 0, buf) != 0:
+        raise _lib.LkcError(_lib.last_error())
+    return dict(zip(TC_PROFILE_FIELDS, [int(v) for v in buf]))
+
+
 def set_conv_path(mode: str) -> None:
     """"auto" (tensor cores when a prepared state is passed and the shape is eligible) or "simt" (CUDA cores only)."""
     check(mode in ("auto", "simt"), "mode must be 'auto' or 'simt'")
