@@ -20,6 +20,14 @@ DILATIONS = (1, 3, 5)
 RES_KERNELS = (3, 7, 11)
 
 
+class _NullCtx:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
 class Generator:
     def __init__(self, sd: dict, device="cuda"):
         self.device = torch.device(device)
@@ -49,6 +57,7 @@ class Generator:
                 if st is not None:
                     self.conv_state[k[: -len(".weight")]] = st
         self._graphs = {}
+        self._streams = None
 
     # ------------------------------------------------------------------ building blocks
 
@@ -89,31 +98,72 @@ class Generator:
 
     # ------------------------------------------------------------------ the graph
 
-    def forward(self, x, har, s, fused=True, outputs=("audio",)):
+    def forward(self, x, har, s, fused=True, outputs=("audio",), concurrent=True):
         """x f32[512, T], har f32[22, 60 T + 1], s f32[128] (cuda tensors) -> the named outputs
-        ("audio" f32[300 T], "post" f32[22, 60 T + 1])."""
+        ("audio" f32[300 T], "post" f32[22, 60 T + 1]).
+
+        The op sequence is the reference's (model.py:735-781). With concurrent=True (fused graph only) the branches
+        that do not depend on each other are queued on side streams, forked from and joined back to torch's current
+        stream: the two noise branches (they only need `har`) and, per stage, the three resblocks (they share their
+        input). The results are the same; independent persistent conv kernels then fill the SMs that the tail of
+        another one leaves idle (a stage-0 conv of the 26 s case has 164 tiles for 148 SMs)."""
         w = self.w
         ops.check(x.dim() == 2 and x.shape[0] == 512, "x must be f32[512, T]")
         sh = shapes(int(x.shape[1]))
         ops.check(tuple(har.shape) == (22, sh["L1"]), f"har must be f32[22, {sh['L1']}]")
         gb = self.style(s)
+        cur = torch.cuda.current_stream(self.device)
+        par = fused and concurrent
+        side = self._side_streams() if par else None
+
+        def on(stream):
+            return torch.cuda.stream(stream) if par else _NullCtx()
+
+        keep = []  # every intermediate stays referenced until all streams are joined
         st = {}
         rb = None
+        noise = [None, None]
+        if par:
+            for i in (0, 1):
+                side[i].wait_stream(cur)
+        for i, (_, _, k_noise) in enumerate(((20, 10, 7), (12, 6, 11))):
+            if not fused:
+                break
+            with on(side[i] if par else None):
+                if i == 0:
+                    xs = ops.conv1d_f32_cuda(har, w["noise_convs.0.weight"], w["noise_convs.0.bias"], stride=6,
+                                             padding=3)
+                else:
+                    xs = ops.conv1d_f32_cuda(har, w["noise_convs.1.weight"], w["noise_convs.1.bias"])
+                noise[i], _ = self.adain_resblock1_fused(xs, gb, f"noise_res.{i}", k_noise)
+                keep.append(xs)
         for i, (k_up, u, k_noise) in enumerate(((20, 10, 7), (12, 6, 11))):
-            if i == 0:
-                xs = ops.conv1d_f32_cuda(har, w["noise_convs.0.weight"], w["noise_convs.0.bias"], stride=6, padding=3)
-            else:
-                xs = ops.conv1d_f32_cuda(har, w["noise_convs.1.weight"], w["noise_convs.1.bias"])
             if fused:
-                xs, _ = self.adain_resblock1_fused(xs, gb, f"noise_res.{i}", k_noise)
+                if par:
+                    cur.wait_stream(side[i])
                 x = ops.conv_transpose1d_poly_f32_cuda(
-                    x if i == 0 else rb[0], self.ups_wp[i], w[f"ups.{i}.bias"], xs, stride=u, padding=(k_up - u) // 2,
-                    taps=k_up // u, slope=0.1, pad_left=1 if i == 1 else 0,
+                    x if i == 0 else rb[0], self.ups_wp[i], w[f"ups.{i}.bias"], noise[i], stride=u,
+                    padding=(k_up - u) // 2, taps=k_up // u, slope=0.1, pad_left=1 if i == 1 else 0,
                     mean3=None if i == 0 else (rb[1], rb[2], 1.0 / 3.0))
                 xst = ops.channel_stats_f32_cuda(x)
-                rb = [self.adain_resblock1_fused(x, gb, f"resblocks.{3 * i + j}", kk, xst)[0]
-                      for j, kk in enumerate(RES_KERNELS)]
+                keep += [x, xst, rb]
+                new_rb = [None, None, None]
+                if par:
+                    side[2].wait_stream(cur)
+                    side[3].wait_stream(cur)
+                # the k = 11 block is the longest: it stays on the current stream
+                for j, stream in ((2, None), (1, side[2] if par else None), (0, side[3] if par else None)):
+                    with on(stream):
+                        new_rb[j] = self.adain_resblock1_fused(x, gb, f"resblocks.{3 * i + j}", RES_KERNELS[j], xst)[0]
+                if par:
+                    cur.wait_stream(side[2])
+                    cur.wait_stream(side[3])
+                rb = new_rb
             else:
+                if i == 0:
+                    xs = ops.conv1d_f32_cuda(har, w["noise_convs.0.weight"], w["noise_convs.0.bias"], stride=6, padding=3)
+                else:
+                    xs = ops.conv1d_f32_cuda(har, w["noise_convs.1.weight"], w["noise_convs.1.bias"])
                 xs = self.adain_resblock1(xs, gb, f"noise_res.{i}", k_noise)
                 x = ops.leaky_relu_f32_cuda(x, slope=0.1)
                 x = ops.conv_transpose1d_f32_cuda(x, w[f"ups.{i}.weight"], w[f"ups.{i}.bias"], stride=u,
@@ -133,8 +183,18 @@ class Generator:
             post = ops.conv1d_f32_cuda(x, w["conv_post.weight"], w["conv_post.bias"], padding=3)
         st["post"] = post
         st["audio"] = ops.istft_logits_f32_cuda(post, n_fft=20, hop=5)
+        if par:
+            # tensors made on a side stream are consumed on the current one: tell the allocator
+            for t in keep + noise + list(rb):
+                if isinstance(t, torch.Tensor):
+                    t.record_stream(cur)
         res = tuple(st[o] for o in outputs)
         return res[0] if len(res) == 1 else res
+
+    def _side_streams(self):
+        if self._streams is None:
+            self._streams = [torch.cuda.Stream(device=self.device) for _ in range(4)]
+        return self._streams
 
     # ------------------------------------------------------------------ CUDA graph replay
 
