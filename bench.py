@@ -205,12 +205,10 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     roofline, cpu_base, kernels = None, None, None
     if rank == 0:
         # per-launch timing of the fused conv kernels (eager pass, CUDA event pair around every launch)
-        with ops.Profile() as prof:
-            for _ in range(2):  # one stream, so that the event pairs bracket one kernel each
-                gen.forward(bufs["x"], bufs["har"], bufs["s"], concurrent=False)
+        # one stream, every launch repeated 4x back to back inside its event pair (after one untimed launch)
+        with ops.Profile(repeat=4) as prof:
+            gen.forward(bufs["x"], bufs["har"], bufs["s"], concurrent=False)
         rows = prof.rows()
-        half = len(rows) // 2
-        rows = rows[half:]  # second pass only (first one warms caches)
         agg = {}
         conv_ms, conv_flops = 0.0, 0.0
         for name, ints, ms in rows:

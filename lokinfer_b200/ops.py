@@ -56,8 +56,12 @@ class Profile:
     active every kernel launch is bracketed by a CUDA event pair on the launching stream and counted. Zero cost
     when off. rows() -> [(kernel name, ints, milliseconds)] after a synchronize."""
 
-    def __init__(self, time_kernels=True):
+    def __init__(self, time_kernels=True, repeat=1):
+        """repeat > 1 launches every kernel `repeat` times back to back inside its event pair and reports the
+        average: the ops are pure (outs never alias operands), and the host's enqueue latency between the start
+        event and the first launch stops inflating the figure for short kernels."""
         self.time_kernels = time_kernels
+        self.repeat = max(1, int(repeat))
         self.calls = []  # (name, ints, start event, end event)
         self.count = 0
 
@@ -72,7 +76,7 @@ class Profile:
 
     def rows(self):
         torch.cuda.synchronize()
-        return [(n, i, a.elapsed_time(b)) for n, i, a, b in self.calls]
+        return [(n, i, a.elapsed_time(b) / self.repeat) for n, i, a, b in self.calls]
 
 
 _profile = None
@@ -93,8 +97,11 @@ def _run(name, operands, outs, attrs_int=(), attrs_float=(), state=None):
             _lib.run(name, [t.data_ptr() for t in ts], ints, attrs_float, state, _stream())
             return
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ptrs = [t.data_ptr() for t in ts]
+        _lib.run(name, ptrs, ints, attrs_float, state, _stream())  # untimed first launch: absorbs the enqueue gap
         a.record()
-        _lib.run(name, [t.data_ptr() for t in ts], ints, attrs_float, state, _stream())
+        for _ in range(prof.repeat):
+            _lib.run(name, ptrs, ints, attrs_float, state, _stream())
         b.record()
         prof.calls.append((name, ints, a, b))
 
