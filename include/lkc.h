@@ -113,8 +113,9 @@ LKC_API int lkc_conv1d_leaky_mean3_f32_cuda(const LkcArgs* a, void* stream);
 /* Tensor-core path of the fused conv family (tcgen05, TMEM accumulators, 3xTF32): the counterpart of the
  * reference's prepare / destroy hooks (PrepareFn / DestroyFn, include/lokinfer/runtime/kernel.h:56-58) and of its
  * build-time weight packing (models/kokoro/model.py:60-65). Run once per constant weight:
- *   n = lkc_conv1d_tc_pack_floats(Co, Ci, K)       floats of the pack; 0 = shape not eligible (needs Co % 128 == 0,
- *                                                  Ci % 16 == 0, K <= 64), the CUDA-core kernel serves it
+ *   n = lkc_conv1d_tc_pack_floats(Co, Ci, K)       floats of the pack; 0 = shape not eligible (needs Ci % 16 == 0,
+ *                                                  K <= 64), the CUDA-core kernel serves it. Co is padded to a
+ *                                                  multiple of 128 with zero rows inside the pack
  *   lkc_conv1d_tc_pack_f32_cuda: ptrs w[Co,Ci,K] | wp[n]; ints w(3) wp(1)     hi / lo TF32 split in the UMMA layout
  *   st = lkc_conv1d_state_create(wp, Co, Ci, K)    host-side handle; pass it as LkcArgs.state of the conv1d_* calls
  * A conv call with a state whose shape is eligible ((K - 1) * dilation <= 50, no mean3 input) runs on the tensor
@@ -148,6 +149,18 @@ LKC_API int lkc_conv_transpose1d_poly_mean3_f32_cuda(const LkcArgs* a, void* str
  * wp[c][r][tt][co] = w[c][co][(r + padding) % stride + (taps - 1 - tt) * stride];
  * ints w(3) wp(4) padding stride. */
 LKC_API int lkc_convt_poly_pack_f32_cuda(const LkcArgs* a, void* stream);
+/* Tensor-core path of conv_transpose1d_poly_f32_cuda (no mean3 input; strides 6 and 10 with K = 2 stride,
+ * 2 padding = stride, Ci % 16 == 0: the two Kokoro upsamplers), prepared like the conv one:
+ *   n = lkc_convt_tc_pack_floats(Ci, Co, K, stride, padding)     0 = not eligible
+ *   lkc_convt_tc_pack_f32_cuda: ptrs w[Ci,Co,K] | wp[n]; ints w(3) wp(1) padding stride
+ *   st = lkc_convt_state_create(wp, Ci, Co, K, stride, padding)   pass as LkcArgs.state of the poly call (the `wp`
+ *        operand of that call stays the CUDA-core pack); destroy with lkc_conv1d_state_destroy.
+ * The left reflect column is computed as (sum - res[co, 2]) + res[co, 0] here, one rounding more than the CUDA-core
+ * kernel's (sum) + res[co, 0]. */
+LKC_API int64_t lkc_convt_tc_pack_floats(int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding);
+LKC_API int lkc_convt_tc_pack_f32_cuda(const LkcArgs* a, void* stream);
+LKC_API LkcConvState* lkc_convt_state_create(const void* wp, int64_t ci, int64_t co, int64_t k, int64_t stride,
+                                             int64_t padding);
 
 /* istft_logits_f32_cpu (kernels/cpu/kokoro_signal.cpp:275-359, adapter :388-391).
  * ptrs x[n_fft+2,L] | out[hop*(L-1)]; ints x(2) out(1) hop n_fft. Fails when n_fft/2+1 > 64, like the reference. */

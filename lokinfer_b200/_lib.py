@@ -51,6 +51,10 @@ def lib():
         l.lkc_conv1d_tc_pack_floats.argtypes = [ctypes.c_int64] * 3
         l.lkc_conv1d_state_create.restype = ctypes.c_void_p
         l.lkc_conv1d_state_create.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64]
+        l.lkc_convt_tc_pack_floats.restype = ctypes.c_int64
+        l.lkc_convt_tc_pack_floats.argtypes = [ctypes.c_int64] * 5
+        l.lkc_convt_state_create.restype = ctypes.c_void_p
+        l.lkc_convt_state_create.argtypes = [ctypes.c_void_p] + [ctypes.c_int64] * 5
         l.lkc_conv1d_state_destroy.restype = None
         l.lkc_conv1d_state_destroy.argtypes = [ctypes.c_void_p]
         l.lkc_conv1d_tc_status.restype = ctypes.c_int

@@ -108,10 +108,12 @@ namespace {
 int gConvPath = 0;  // 0 = tensor cores when eligible, 1 = CUDA-core kernel only
 }
 
+bool convPathForcedSimt() { return gConvPath != 0; }
+
 int convFused(const ConvFusedParams& p, cudaStream_t s) {
   if (gConvPath == 0 && convTcEligible(p)) {
     const ConvState* st = static_cast<const ConvState*>(p.state);
-    LKC_REQUIRE(st->wp && st->co == p.co && st->ci == p.ci && st->k == p.k,
+    LKC_REQUIRE(st->wp && st->stride == 0 && st->co == p.co && st->ci == p.ci && st->k == p.k,
                 "conv1d fused: the prepared state does not match the weight shape");
     return convTc(p, st->wp, s);
   }
@@ -170,14 +172,14 @@ extern "C" LKC_API int lkc_conv1d_nobias_f32_cuda(const LkcArgs* a, void* s) { r
 extern "C" LKC_API int lkc_conv1d_tc_pack_f32_cuda(const LkcArgs* a, void* stream) {
   LKC_REQUIRE(a && a->numPtrs == 2 && a->numInts == 4, "conv1d_tc_pack_f32_cuda: expected w | wp");
   const int64_t co = a->ints[0], ci = a->ints[1], k = a->ints[2];
-  LKC_REQUIRE(co > 0 && ci > 0 && co % 128 == 0 && ci % 16 == 0 && k >= 1 && k <= 64,
-              "conv1d_tc_pack_f32_cuda: needs Co % 128 == 0, Ci % 16 == 0, 1 <= K <= 64");
+  LKC_REQUIRE(co > 0 && ci > 0 && ci % 16 == 0 && k >= 1 && k <= 64,
+              "conv1d_tc_pack_f32_cuda: needs Ci % 16 == 0, 1 <= K <= 64");
   LKC_REQUIRE(a->ints[3] == convTcPackFloats(co, ci, k), "conv1d_tc_pack_f32_cuda: wp must hold lkc_conv1d_tc_pack_floats");
   return convTcPack(F(a, 0), O(a, 1), co, ci, k, S(stream));
 }
 
 extern "C" LKC_API int64_t lkc_conv1d_tc_pack_floats(int64_t co, int64_t ci, int64_t k) {
-  if (co <= 0 || ci <= 0 || co % 128 != 0 || ci % 16 != 0 || k < 1 || k > 64) return 0;
+  if (co <= 0 || ci <= 0 || ci % 16 != 0 || k < 1 || k > 64) return 0;
   return convTcPackFloats(co, ci, k);
 }
 
@@ -186,12 +188,37 @@ extern "C" LKC_API LkcConvState* lkc_conv1d_state_create(const void* wp, int64_t
     fail("conv1d_state_create: shape not eligible for the tensor-core path or null pack");
     return nullptr;
   }
-  ConvState* st = new (std::nothrow) ConvState{static_cast<const float*>(wp), co, ci, k};
+  ConvState* st = new (std::nothrow) ConvState{static_cast<const float*>(wp), co, ci, k, 0};
   if (!st) fail("conv1d_state_create: out of host memory");
   return reinterpret_cast<LkcConvState*>(st);
 }
 
 extern "C" LKC_API void lkc_conv1d_state_destroy(LkcConvState* st) { delete reinterpret_cast<ConvState*>(st); }
+
+// ints: w(Ci, Co, K) wp(n) padding stride
+extern "C" LKC_API int lkc_convt_tc_pack_f32_cuda(const LkcArgs* a, void* stream) {
+  LKC_REQUIRE(a && a->numPtrs == 2 && a->numInts == 6, "convt_tc_pack_f32_cuda: expected w | wp, padding, stride");
+  const int64_t ci = a->ints[0], co = a->ints[1], k = a->ints[2], pad = a->ints[4], s = a->ints[5];
+  LKC_REQUIRE(convtTcEligible(ci, co, k, s, pad),
+              "convt_tc_pack_f32_cuda: needs stride 6 or 10, K = 2 stride, 2 padding = stride, Ci % 16 == 0");
+  LKC_REQUIRE(a->ints[3] == convtTcPackFloats(ci, co, s), "convt_tc_pack_f32_cuda: wp must hold lkc_convt_tc_pack_floats");
+  return convtTcPack(F(a, 0), O(a, 1), ci, co, k, s, pad, S(stream));
+}
+
+extern "C" LKC_API int64_t lkc_convt_tc_pack_floats(int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding) {
+  return convtTcEligible(ci, co, k, stride, padding) ? convtTcPackFloats(ci, co, stride) : 0;
+}
+
+extern "C" LKC_API LkcConvState* lkc_convt_state_create(const void* wp, int64_t ci, int64_t co, int64_t k,
+                                                        int64_t stride, int64_t padding) {
+  if (!wp || !convtTcEligible(ci, co, k, stride, padding)) {
+    fail("convt_state_create: shape not eligible for the tensor-core path or null pack");
+    return nullptr;
+  }
+  ConvState* st = new (std::nothrow) ConvState{static_cast<const float*>(wp), co, ci, k, stride};
+  if (!st) fail("convt_state_create: out of host memory");
+  return reinterpret_cast<LkcConvState*>(st);
+}
 
 extern "C" LKC_API int lkc_conv1d_tc_status(int* status, int reset) {
   LKC_REQUIRE(status, "conv1d_tc_status: null out pointer");
@@ -229,6 +256,7 @@ const Entry kEntries[] = {
     {"conv_transpose1d_poly_f32_cuda", lkc_conv_transpose1d_poly_f32_cuda},
     {"conv_transpose1d_poly_mean3_f32_cuda", lkc_conv_transpose1d_poly_mean3_f32_cuda},
     {"convt_poly_pack_f32_cuda", lkc_convt_poly_pack_f32_cuda},
+    {"convt_tc_pack_f32_cuda", lkc_convt_tc_pack_f32_cuda},
     {"gemm_bias_f32_cuda", lkc_gemm_bias_f32_cuda},
     {"istft_logits_f32_cuda", lkc_istft_logits_f32_cuda},
     {"leaky_relu_f32_cuda", lkc_leaky_relu_f32_cuda},

@@ -65,6 +65,8 @@ struct TcArgs {
   float *out, *stats;
   int ci, co, k, dilation, padding;
   int64_t l, lo, nchunks;
+  int64_t outPitch;  // row pitch of out / residual (= lo for a conv; L * stride + padLeft for a ConvTranspose)
+  int padLeft;       // ConvTranspose: 1 = one-sample left reflect pad
   float slope, outScale;
   int rows;        // staged time rows per buffer = NT + (k-1)*dilation
   int wStages;     // weight ring depth
@@ -162,7 +164,22 @@ __device__ __forceinline__ void mmaCommit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar))
                : "memory");
 }
-// 32 lanes x 32 consecutive 32-bit columns: thread i gets lane (base lane + i), registers = columns.
+// tcgen05.ld 32x32b: thread i of the warp gets TMEM lane (base lane + i), registers = consecutive columns.
+// 32 lanes x 16 consecutive columns (keeps the register footprint of the accumulate loop small).
+__device__ __forceinline__ void tmemLoad16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 __device__ __forceinline__ void tmemLoad32(uint32_t taddr, float* v) {
   uint32_t r[32];
   asm volatile(
@@ -253,7 +270,9 @@ struct Cursor {
   }
 };
 
-template <int ACT, bool PROF>
+// PARTIAL: Co is not a multiple of 128 (the last output-channel block has rows that do not exist).
+// TS: 0 = conv1d; 6 / 10 = polyphase ConvTranspose1d of that stride (see the comment above convtTcPackKernel).
+template <int ACT, bool PROF, bool PARTIAL, int TS>
 __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   extern __shared__ __align__(1024) unsigned char smemRaw[];
   const int rows = a.rows;
@@ -328,30 +347,67 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const int tt = t / a.numCoBlk, cb = t - tt * a.numCoBlk;
       const long long tPre = clock64();
       const int64_t tChunk = int64_t(tt) * NT + g * 128;  // first output column of this warp's 128-column chunk
-      const int coBase = cb * MT + q * 32;
-      const int co = coBase + lane;
-      const float bias = a.bias ? a.bias[co] : 0.f;
       const int64_t nValid64 = a.lo - tChunk;
       const int nValid = nValid64 <= 0 ? 0 : (nValid64 < 128 ? int(nValid64) : 128);
-      // Running sums start from bias (+ residual). The residual tile is read with lanes along time (all 128 loads
-      // of the thread in flight at once) and transposed through shared memory; this overlaps the first chunk's MMAs.
+      // conv: the warp's rows are 32 consecutive output channels. ConvTranspose: rows are (channel, phase) pairs,
+      // CQ channels x TS phases per warp (lane = cl * TS + r), the last 32 - CQ * TS rows are zero padding.
+      constexpr int CQ = TS ? 32 / TS : 32, ROWS = TS ? CQ * TS : 32;
+      const int coBase = TS ? (cb * 4 + q) * CQ : cb * MT + q * 32;
+      const int co = TS ? coBase + lane / (TS ? TS : 1) : coBase + lane;
+      const bool rowOk = TS ? (lane < ROWS && co < a.co) : (!PARTIAL || co < a.co);
+      const float bias = (a.bias && rowOk) ? a.bias[co] : 0.f;
+      // channels of this warp that exist (may be <= 0 in the last block)
+      const int coValid = (TS || PARTIAL) ? (a.co - coBase < CQ ? a.co - coBase : CQ) : 32;
+      // Running sums start from bias (+ residual). The residual tile is read with lanes along time (all loads of the
+      // thread in flight at once) and transposed through shared memory; this overlaps the first chunk's MMAs.
       float S[128];
       if (a.residual) {
+        if constexpr (TS == 0) {
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const bool ok = b * 32 + lane < nValid;
-          const float* rp = a.residual + int64_t(coBase) * a.lo + tChunk + b * 32 + lane;
+          for (int b = 0; b < 4; ++b) {
+            const bool ok = b * 32 + lane < nValid;
+            const float* rp = a.residual + int64_t(coBase) * a.outPitch + tChunk + b * 32 + lane;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) S[b * 32 + i] = ok ? rp[int64_t(i) * a.lo] : 0.f;
-        }
+            for (int i = 0; i < 32; ++i)
+              S[b * 32 + i] = (ok && (!PARTIAL || i < coValid)) ? rp[int64_t(i) * a.outPitch] : 0.f;
+          }
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
+          for (int b = 0; b < 4; ++b) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) tile[i * STAGE_PITCH + lane] = S[b * 32 + i];
-          __syncwarp();
+            for (int i = 0; i < 32; ++i) tile[i * STAGE_PITCH + lane] = S[b * 32 + i];
+            __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) S[b * 32 + j] = tile[lane * STAGE_PITCH + j] + bias;
-          __syncwarp();
+            for (int j = 0; j < 32; ++j) S[b * 32 + j] = tile[lane * STAGE_PITCH + j] + bias;
+            __syncwarp();
+          }
+        } else {
+          // channel cl, batch b: the 32 * TS output samples u = (tChunk + 32 b) * TS + idx are contiguous in memory;
+          // load i = cl * TS + f reads idx = 32 f + lane, which is column idx / TS of phase idx % TS
+          const int64_t uEnd = a.lo * TS;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const int64_t u0 = (tChunk + b * 32) * TS;
+#pragma unroll
+            for (int i = 0; i < ROWS; ++i) {
+              const int cl = i / TS, f = i % TS;
+              const int64_t u = u0 + f * 32 + lane;
+              S[b * 32 + i] = (cl < coValid && u < uEnd)
+                                  ? a.residual[int64_t(coBase + cl) * a.outPitch + a.padLeft + u]
+                                  : 0.f;
+            }
+          }
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+#pragma unroll
+            for (int i = 0; i < ROWS; ++i) {
+              const int cl = i / TS, idx = (i % TS) * 32 + lane;
+              tile[(cl * TS + idx % TS) * STAGE_PITCH + idx / TS] = S[b * 32 + i];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) S[b * 32 + j] = tile[lane * STAGE_PITCH + j] + bias;
+            __syncwarp();
+          }
         }
       } else {
 #pragma unroll
@@ -384,11 +440,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const long long tFin = clock64();
       tcFenceAfter();
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        float v[32];
-        tmemLoad32(tmemLo + laneBase + g * 128 + b * 32, v);
+      for (int b = 0; b < 8; ++b) {
+        float v[16];
+        tmemLoad16(tmemLo + laneBase + g * 128 + b * 16, v);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) S[b * 32 + j] += v[j];
+        for (int j = 0; j < 16; ++j) S[b * 16 + j] += v[j];
       }
       tcFenceBefore();
       __syncwarp();
@@ -398,53 +454,83 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         for (int j = 0; j < 128; ++j) S[j] *= a.outScale;
       }
 
-      float pMean[4], pM2[4];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);  // valid columns here
-        const int64_t tb = tChunk + b * 32;
-        // partial statistics of the valid columns (two passes in registers)
-        float sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) sum += j < nb ? S[b * 32 + j] : 0.f;
-        const float m = nb > 0 ? sum / float(nb) : 0.f;
-        float m2 = 0.f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float d = j < nb ? S[b * 32 + j] - m : 0.f;
-          m2 = fmaf(d, d, m2);
-        }
-        pMean[b] = m, pM2[b] = m2;
-        // transpose and store with lanes along time
-#pragma unroll
-        for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
-        __syncwarp();
-        if (lane < nb) {
-          float* op = a.out + int64_t(coBase) * a.lo + tb + lane;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) op[int64_t(i) * a.lo] = tile[i * STAGE_PITCH + lane];
-        }
-        __syncwarp();
-      }
-      if (a.stats && nValid > 0) {
-        // exact combine of the four 32-column partials: mean = sum n_b m_b / n, M2 = sum M2_b + sum n_b (m_b - mean)^2
-        float sum = 0.f;
+      if constexpr (TS == 0) {
+        float pMean[4], pM2[4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);
-          sum = fmaf(float(nb), pMean[b], sum);
+          const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);  // valid columns
+          const int64_t tb = tChunk + b * 32;
+          // partial statistics of the valid columns (two passes in registers)
+          float sum = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum += j < nb ? S[b * 32 + j] : 0.f;
+          const float m = nb > 0 ? sum / float(nb) : 0.f;
+          float m2 = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float d = j < nb ? S[b * 32 + j] - m : 0.f;
+            m2 = fmaf(d, d, m2);
+          }
+          pMean[b] = m, pM2[b] = m2;
+          // transpose and store with lanes along time
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
+          __syncwarp();
+          if (lane < nb) {
+            float* op = a.out + int64_t(coBase) * a.outPitch + tb + lane;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (!PARTIAL || i < coValid) op[int64_t(i) * a.outPitch] = tile[i * STAGE_PITCH + lane];
+          }
+          __syncwarp();
         }
-        const float mean = sum / float(nValid);
-        float m2 = 0.f;
+        if (a.stats && nValid > 0 && (!PARTIAL || co < a.co)) {
+          // exact combine of the four 32-column partials: mean = sum n_b m_b / n, M2 = sum M2_b + sum n_b (m_b - mean)^2
+          float sum = 0.f;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);
+            sum = fmaf(float(nb), pMean[b], sum);
+          }
+          const float mean = sum / float(nValid);
+          float m2 = 0.f;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);
+            const float d = pMean[b] - mean;
+            m2 += pM2[b] + float(nb) * d * d;
+          }
+          float* st = a.stats + (int64_t(co) * a.nchunks + tChunk / 128) * 2;
+          st[0] = mean;
+          st[1] = m2;
+        }
+      } else {
+        // ConvTranspose: interleave the TS phases of each channel back into contiguous output samples
+        const int64_t uEnd = a.lo * TS;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);
-          const float d = pMean[b] - mean;
-          m2 += pM2[b] + float(nb) * d * d;
+          const int64_t u0 = (tChunk + b * 32) * TS;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < ROWS; ++i) {
+            const int cl = i / TS, idx = (i % TS) * 32 + lane;
+            const int64_t u = u0 + idx;
+            if (cl < coValid && u < uEnd)
+              a.out[int64_t(coBase + cl) * a.outPitch + a.padLeft + u] =
+                  tile[(cl * TS + idx % TS) * STAGE_PITCH + idx / TS];
+          }
+          if (a.padLeft && b == 0 && tChunk == 0 && lane < coValid && uEnd > 1) {
+            // one-sample left reflect pad: out[co, 0] = unpadded[co, 1] + res[co, 0]; the running sum of (column 0,
+            // phase 1) already holds res[co, 1 + padLeft], which is taken out again (one extra rounding)
+            const int64_t row = int64_t(coBase + lane) * a.outPitch;
+            const float r1 = a.residual ? a.residual[row + a.padLeft + 1] : 0.f;
+            const float r0 = a.residual ? a.residual[row] : 0.f;
+            a.out[row] = (tile[(lane * TS + 1) * STAGE_PITCH] - r1) + r0;
+          }
+          __syncwarp();
         }
-        float* st = a.stats + (int64_t(co) * a.nchunks + tChunk / 128) * 2;
-        st[0] = mean;
-        st[1] = m2;
       }
       cFin += clock64() - tFin;
     }
@@ -660,7 +746,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
 __global__ void packWeightsKernel(const float* __restrict__ w, float* __restrict__ wp, int co, int ci, int k) {
   // wp index = ((((cb * nC16 + c16) * k + kk) * 2 + part) * 4 + kc) * 128 * 4 + col * 4 + e
   const int nC16 = ci / KC;
-  const int64_t n = int64_t(co / MT) * nC16 * k * W_STAGE_FLOATS;
+  const int64_t n = int64_t((co + MT - 1) / MT) * nC16 * k * W_STAGE_FLOATS;  // rows past Co are zero
   for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < n; idx += int64_t(gridDim.x) * blockDim.x) {
     int64_t r = idx;
     const int e = int(r % 4);
@@ -675,7 +761,42 @@ __global__ void packWeightsKernel(const float* __restrict__ w, float* __restrict
     r /= k;
     const int c16 = int(r % nC16);
     const int cb = int(r / nC16);
-    const float v = w[(int64_t(cb * MT + col) * ci + (c16 * KC + kc * 4 + e)) * k + kk];
+    const int row = cb * MT + col;
+    const float v = row < co ? w[(int64_t(row) * ci + (c16 * KC + kc * 4 + e)) * k + kk] : 0.f;
+    const float h = tf32Round(v);
+    wp[idx] = part == 0 ? h : v - h;
+  }
+}
+
+// Polyphase ConvTranspose1d (K = 2 s, 2 p = s) on the same kernel: out[co, j s + r] = sum_c sum_tt Wr[r][co][c][tt] *
+// leaky(x)[c, j + q_r - 1 + tt], q_r = (r + p) div s, is a 3-tap conv over the window (j - 1, j, j + 1) whose output rows
+// are (channel, phase) pairs: window tap wt carries Wr[..][tt = wt - q_r] when that is 0 or 1 and zero otherwise (one
+// of the three taps of every row is zero). Rows are grouped so that each epilogue warp (32 accumulator rows) owns
+// CQ = 32 / s whole channels with all their phases (row = cl * s + r, the last 32 - CQ s rows are zero), which lets it
+// write each channel's samples j s + r as one contiguous run. One 128-row block therefore holds 4 CQ channels.
+__global__ void convtTcPackKernel(const float* __restrict__ w, float* __restrict__ wp, int ci, int co, int k, int s,
+                                  int p) {
+  const int nC16 = ci / KC, cq = 32 / s, cpb = 4 * cq;
+  const int64_t n = int64_t((co + cpb - 1) / cpb) * nC16 * 3 * W_STAGE_FLOATS;
+  for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < n; idx += int64_t(gridDim.x) * blockDim.x) {
+    int64_t r = idx;
+    const int e = int(r % 4);
+    r /= 4;
+    const int row = int(r % MT);
+    r /= MT;
+    const int kc = int(r % 4);
+    r /= 4;
+    const int part = int(r % 2);
+    r /= 2;
+    const int wt = int(r % 3);
+    r /= 3;
+    const int c16 = int(r % nC16);
+    const int cb = int(r / nC16);
+    const int q = row / 32, i = row % 32, cl = i / s, ph = i % s;
+    const int o = (cb * 4 + q) * cq + cl, c = c16 * KC + kc * 4 + e;
+    const int tt = wt - (ph + p) / s;
+    float v = 0.f;
+    if (i < cq * s && o < co && (tt == 0 || tt == 1)) v = w[(int64_t(c) * co + o) * k + (ph + p) % s + (1 - tt) * s];
     const float h = tf32Round(v);
     wp[idx] = part == 0 ? h : v - h;
   }
@@ -696,35 +817,42 @@ static size_t convTcSmemBytes(int64_t ci, int rows, int* wStages) {
 }
 
 bool convTcEligible(const ConvFusedParams& p) {
-  if (!(p.state != nullptr && p.x2 == nullptr && p.ci % KC == 0 && p.co % MT == 0 && p.ci >= KC && p.k >= 1 &&
+  if (!(p.state != nullptr && p.x2 == nullptr && p.ci % KC == 0 && p.co >= 1 && p.ci >= KC && p.k >= 1 &&
         p.k <= 64 && (p.k - 1) * p.dilation <= MAX_HALO && p.lo >= 1 && p.padding <= (1 << 20) && p.ci <= 4096))
     return false;
   return convTcSmemBytes(p.ci, NT + int((p.k - 1) * p.dilation), nullptr) != 0;
 }
 
-int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k) { return (co / MT) * (ci / KC) * k * W_STAGE_FLOATS; }
+int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k) {
+  return ((co + MT - 1) / MT) * (ci / KC) * k * W_STAGE_FLOATS;
+}
 
 int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, cudaStream_t s) {
-  LKC_REQUIRE(co % MT == 0 && ci % KC == 0 && co > 0 && ci > 0 && k >= 1 && k <= 64,
-              "conv1d_tc_pack_f32_cuda: needs Co % 128 == 0, Ci % 16 == 0, 1 <= K <= 64");
+  LKC_REQUIRE(ci % KC == 0 && co > 0 && ci > 0 && k >= 1 && k <= 64,
+              "conv1d_tc_pack_f32_cuda: needs Ci % 16 == 0, 1 <= K <= 64");
   const int64_t n = convTcPackFloats(co, ci, k);
   const int blocks = static_cast<int>(ceilDiv(n, 256) > 4096 ? 4096 : ceilDiv(n, 256));
   packWeightsKernel<<<blocks, 256, 0, s>>>(w, wp, int(co), int(ci), int(k));
   return launched("conv1d_tc_pack_f32_cuda");
 }
 
-template <int ACT, bool PROF>
-static int launchTc(const TcArgs& a, int grid, size_t smem, cudaStream_t s) {
+template <int ACT, bool PROF, bool PARTIAL, int TS = 0>
+static int launchTc2(const TcArgs& a, int grid, size_t smem, cudaStream_t s) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(convTcKernel<ACT, PROF>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    cudaError_t e = cudaFuncSetAttribute(convTcKernel<ACT, PROF, PARTIAL, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return failCuda("conv (tensor-core): cudaFuncSetAttribute", e);
     configured[dev] = true;
   }
-  convTcKernel<ACT, PROF><<<grid, NTHREADS, smem, s>>>(a);
+  convTcKernel<ACT, PROF, PARTIAL, TS><<<grid, NTHREADS, smem, s>>>(a);
   return launched("conv (tensor-core)");
+}
+
+template <int ACT, bool PROF>
+static int launchTc(const TcArgs& a, int grid, size_t smem, cudaStream_t s) {
+  return a.co % MT == 0 ? launchTc2<ACT, PROF, false>(a, grid, smem, s) : launchTc2<ACT, PROF, true>(a, grid, smem, s);
 }
 
 static bool gProfileOn = false;
@@ -745,20 +873,11 @@ int convTcProfile(int enable, long long* out16) {
   return 0;
 }
 
-int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
-  TcArgs a;
-  a.x = p.x, a.wp = wp, a.bias = p.bias, a.affine = p.affine, a.alpha = p.alpha, a.residual = p.residual;
-  a.out = p.out, a.stats = p.stats;
-  a.ci = int(p.ci), a.co = int(p.co), a.k = int(p.k), a.dilation = int(p.dilation), a.padding = int(p.padding);
-  a.l = p.l, a.lo = p.lo, a.nchunks = statChunks(p.lo);
-  a.slope = p.slope, a.outScale = p.outScale;
-  a.rows = NT + (a.k - 1) * a.dilation;
-  const int64_t tTiles = ceilDiv(p.lo, NT);
-  LKC_REQUIRE(tTiles * (p.co / MT) < (1 << 30), "conv (tensor-core): too many tiles");
-  a.numTTiles = int(tTiles), a.numCoBlk = int(p.co / MT);
-  const size_t smem = convTcSmemBytes(p.ci, a.rows, &a.wStages);
-  LKC_REQUIRE(smem != 0, "conv (tensor-core): window too large");
-  // Per-device constants, looked up once (the first call on a device must not be inside a stream capture).
+// Per-device constants, looked up once (the first call on a device must not be inside a stream capture), and the
+// launch geometry shared by the conv and ConvTranspose entry points.
+static int finishArgs(TcArgs& a, int* grid, size_t* smem) {
+  *smem = convTcSmemBytes(a.ci, a.rows, &a.wStages);
+  LKC_REQUIRE(*smem != 0, "conv (tensor-core): window too large");
   static int* statusPtr[64] = {};
   static long long* profPtr[64] = {};
   static int smCount[64] = {};
@@ -779,9 +898,26 @@ int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
   }
   a.status = statusPtr[dev];
   a.prof = gProfileOn ? profPtr[dev] : nullptr;
-  const int sms = smCount[dev];
   const int tiles = a.numTTiles * a.numCoBlk;
-  const int grid = tiles < sms ? tiles : sms;
+  *grid = tiles < smCount[dev] ? tiles : smCount[dev];
+  return 0;
+}
+
+int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
+  TcArgs a;
+  a.x = p.x, a.wp = wp, a.bias = p.bias, a.affine = p.affine, a.alpha = p.alpha, a.residual = p.residual;
+  a.out = p.out, a.stats = p.stats;
+  a.ci = int(p.ci), a.co = int(p.co), a.k = int(p.k), a.dilation = int(p.dilation), a.padding = int(p.padding);
+  a.l = p.l, a.lo = p.lo, a.nchunks = statChunks(p.lo), a.outPitch = p.lo, a.padLeft = 0;
+  a.slope = p.slope, a.outScale = p.outScale;
+  a.rows = NT + (a.k - 1) * a.dilation;
+  const int64_t tTiles = ceilDiv(p.lo, NT);
+  const int64_t coBlk = ceilDiv(p.co, MT);  // output channels past Co are zero rows of the pack and never stored
+  LKC_REQUIRE(tTiles * coBlk < (1 << 30), "conv (tensor-core): too many tiles");
+  a.numTTiles = int(tTiles), a.numCoBlk = int(coBlk);
+  int grid = 0;
+  size_t smem = 0;
+  if (int rc = finishArgs(a, &grid, &smem)) return rc;
   const bool prof = a.prof != nullptr;
   switch (p.act) {
     case Act::None: return prof ? launchTc<0, true>(a, grid, smem, s) : launchTc<0, false>(a, grid, smem, s);
@@ -789,6 +925,48 @@ int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
     case Act::Leaky: return prof ? launchTc<2, true>(a, grid, smem, s) : launchTc<2, false>(a, grid, smem, s);
   }
   return fail("conv (tensor-core): bad activation");
+}
+
+// ---- polyphase ConvTranspose1d on the tensor-core kernel
+
+bool convtTcEligible(int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding) {
+  return (stride == 6 || stride == 10) && k == 2 * stride && 2 * padding == stride && ci % KC == 0 && ci >= KC &&
+         ci <= 4096 && co >= 1 && convTcSmemBytes(ci, NT + 2, nullptr) != 0;
+}
+
+int64_t convtTcPackFloats(int64_t ci, int64_t co, int64_t stride) {
+  const int64_t cpb = 4 * (32 / stride);
+  return ceilDiv(co, cpb) * (ci / KC) * 3 * W_STAGE_FLOATS;
+}
+
+int convtTcPack(const float* w, float* wp, int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding,
+                cudaStream_t s) {
+  LKC_REQUIRE(convtTcEligible(ci, co, k, stride, padding),
+              "convt_tc_pack_f32_cuda: needs stride 6 or 10, K = 2 stride, 2 padding = stride, Ci % 16 == 0");
+  const int64_t n = convtTcPackFloats(ci, co, stride);
+  const int blocks = static_cast<int>(ceilDiv(n, 256) > 4096 ? 4096 : ceilDiv(n, 256));
+  convtTcPackKernel<<<blocks, 256, 0, s>>>(w, wp, int(ci), int(co), int(k), int(stride), int(padding));
+  return launched("convt_tc_pack_f32_cuda");
+}
+
+int convtTc(const ConvtParams& p, const float* wp, cudaStream_t s) {
+  TcArgs a;
+  a.x = p.x, a.wp = wp, a.bias = p.bias, a.affine = nullptr, a.alpha = nullptr, a.residual = p.res;
+  a.out = p.out, a.stats = nullptr;
+  a.ci = int(p.ci), a.co = int(p.co), a.k = 3, a.dilation = 1, a.padding = 1;
+  a.l = p.l, a.lo = p.l, a.nchunks = 0, a.outPitch = p.l * p.stride + p.padLeft, a.padLeft = int(p.padLeft);
+  a.slope = p.slope, a.outScale = 1.f;
+  a.rows = NT + 2;
+  const int64_t tTiles = ceilDiv(p.l, NT), coBlk = ceilDiv(p.co, 4 * (32 / p.stride));
+  LKC_REQUIRE(tTiles * coBlk < (1 << 30), "conv_transpose1d_poly (tensor-core): too many tiles");
+  a.numTTiles = int(tTiles), a.numCoBlk = int(coBlk);
+  int grid = 0;
+  size_t smem = 0;
+  if (int rc = finishArgs(a, &grid, &smem)) return rc;
+  const bool prof = a.prof != nullptr;
+  if (p.stride == 6)
+    return prof ? launchTc2<2, true, false, 6>(a, grid, smem, s) : launchTc2<2, false, false, 6>(a, grid, smem, s);
+  return prof ? launchTc2<2, true, false, 10>(a, grid, smem, s) : launchTc2<2, false, false, 10>(a, grid, smem, s);
 }
 
 int convTcStatus(int* out, bool reset) {

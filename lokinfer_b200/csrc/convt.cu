@@ -224,6 +224,16 @@ int runPoly(const LkcArgs* a, void* stream, bool mean3) {
   p.inScale = mean3 ? static_cast<float>(a->floats[0]) : 1.f;
   p.slope = static_cast<float>(a->floats[mean3 ? 1 : 0]);
   cudaStream_t st = S(stream);
+  if (a->state && !mean3 && !convPathForcedSimt()) {
+    // prepared tensor-core pack of this weight (lkc_convt_state_create): same contract on tcgen05
+    const ConvState* cs = static_cast<const ConvState*>(a->state);
+    LKC_REQUIRE(cs->wp && cs->stride == s && cs->ci == ci && cs->co == co && cs->k == taps * s,
+                "conv_transpose1d_poly: the prepared state does not match the weight shape");
+    if (convtTcEligible(ci, co, taps * s, s, pad)) {
+      ConvtParams cp{p.x, p.bias, p.res, p.out, ci, l, co, s, padLeft, p.slope};
+      return convtTc(cp, cs->wp, st);
+    }
+  }
   if (taps == 2 && ceilDiv(co, BCO) <= 65535) {
     switch (s) {
       case 2: return launchPoly<2, 2>(p, st);

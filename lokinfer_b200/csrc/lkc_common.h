@@ -64,9 +64,23 @@ int convSimt(const ConvFusedParams& p, int64_t stride, cudaStream_t s);
 
 // Tensor-core (tcgen05, 3xTF32) fused conv (conv_tc.cu). `state` of ConvFusedParams is an LkcConvState.
 struct ConvState {
-  const float* wp;  // packed weights (convTcPack)
+  const float* wp;  // packed weights (convTcPack / convtTcPack)
   int64_t co, ci, k;
+  int64_t stride;  // 0 = conv1d pack; otherwise the ConvTranspose1d stride the pack was made for
 };
+// Operands of the polyphase ConvTranspose1d (convt.cu decodes them, conv_tc.cu can run them).
+struct ConvtParams {
+  const float *x, *bias, *res;
+  float* out;
+  int64_t ci, l, co, stride, padLeft;
+  float slope;
+};
+bool convtTcEligible(int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding);
+int64_t convtTcPackFloats(int64_t ci, int64_t co, int64_t stride);
+int convtTcPack(const float* w, float* wp, int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding,
+                cudaStream_t s);
+int convtTc(const ConvtParams& p, const float* wp, cudaStream_t s);
+bool convPathForcedSimt();
 bool convTcEligible(const ConvFusedParams& p);
 int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k);
 int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, cudaStream_t s);

@@ -48,6 +48,8 @@ class Generator:
         if "ups.0.weight" in self.w:  # a state dict of resblocks only is enough for adain_resblock1*
             self.ups_wp = [ops.convt_poly_weights_cuda(self.w["ups.0.weight"], 10, 5),
                            ops.convt_poly_weights_cuda(self.w["ups.1.weight"], 6, 3)]
+            self.ups_state = [ops.conv_transpose1d_prepare_f32_cuda(self.w["ups.0.weight"], 10, 5),
+                              ops.conv_transpose1d_prepare_f32_cuda(self.w["ups.1.weight"], 6, 3)]
         self.ident128 = torch.stack([torch.zeros(128), torch.ones(128), torch.zeros(128)]).to(self.device).contiguous()
         # Prepared state of every fused-conv weight the tensor-core kernel accepts (packed once, at init).
         self.conv_state = {}
@@ -141,10 +143,16 @@ class Generator:
             if fused:
                 if par:
                     cur.wait_stream(side[i])
+                if i == 0:
+                    xin = x
+                else:
+                    # resblock mean as its own pass (13 us of HBM time at T = 2080), so that the upsampler takes the
+                    # tensor-core path; conv_transpose1d_poly(..., mean3=...) is the fused CUDA-core alternative
+                    xin = ops.add3_scale_f32_cuda(rb[0], rb[1], rb[2], scale=1.0 / 3.0)
+                    keep.append(xin)
                 x = ops.conv_transpose1d_poly_f32_cuda(
-                    x if i == 0 else rb[0], self.ups_wp[i], w[f"ups.{i}.bias"], noise[i], stride=u,
-                    padding=(k_up - u) // 2, taps=k_up // u, slope=0.1, pad_left=1 if i == 1 else 0,
-                    mean3=None if i == 0 else (rb[1], rb[2], 1.0 / 3.0))
+                    xin, self.ups_wp[i], w[f"ups.{i}.bias"], noise[i], stride=u, padding=(k_up - u) // 2,
+                    taps=k_up // u, slope=0.1, pad_left=1 if i == 1 else 0, state=self.ups_state[i])
                 xst = ops.channel_stats_f32_cuda(x)
                 keep += [x, xst, rb]
                 new_rb = [None, None, None]
@@ -175,9 +183,11 @@ class Generator:
                 x = ops.add3_scale_f32_cuda(rb[0], rb[1], rb[2], scale=1.0 / 3.0)
             st[f"stage{i}"] = rb if fused else x
         if fused:
-            post, _ = ops.conv1d_leaky_mean3_f32_cuda(rb[0], rb[1], rb[2], w["conv_post.weight"], w["conv_post.bias"],
-                                                      self.ident128, in_scale=1.0 / 3.0, slope=0.01, padding=3,
-                                                      state=self.conv_state.get("conv_post"))
+            # resblock mean, then the direct fused conv (model.py:774-776): on this device the extra pass over the
+            # mean costs ~40 us of HBM time, and the conv then runs on the tensor cores (Co = 22 padded to 128 rows)
+            xm = ops.add3_scale_f32_cuda(rb[0], rb[1], rb[2], scale=1.0 / 3.0)
+            post, _ = ops.conv1d_leaky_f32_cuda(xm, w["conv_post.weight"], w["conv_post.bias"], self.ident128,
+                                                slope=0.01, padding=3, state=self.conv_state.get("conv_post"))
         else:
             x = ops.leaky_relu_f32_cuda(x, slope=0.01)
             post = ops.conv1d_f32_cuda(x, w["conv_post.weight"], w["conv_post.bias"], padding=3)

@@ -239,10 +239,11 @@ def convt_poly_weights_cuda(w, stride: int, padding: int):
     return wp
 
 
-def conv_transpose1d_poly_f32_cuda(x, wp, b, res, stride, padding, taps, slope, pad_left=0, mean3=None):
+def conv_transpose1d_poly_f32_cuda(x, wp, b, res, stride, padding, taps, slope, pad_left=0, mean3=None, state=None):
     """reflect_pad_left(conv_transpose1d(leaky_relu(x, slope), w, b, stride, padding), pad_left) + res, polyphase
     (wp = convt_poly_weights_cuda(w, stride, padding), K = taps * stride): x f32[Ci, L] -> f32[Co, L*s + pad_left].
-    mean3 = (x2, x3, scale): the input is ((x + x2) + x3) * scale."""
+    mean3 = (x2, x3, scale): the input is ((x + x2) + x3) * scale. state = conv_transpose1d_prepare_f32_cuda(w, ...)
+    runs the same contract on the tensor cores (ignored with mean3)."""
     pad_left, padding, stride = _int(pad_left, "pad_left"), _int(padding, "padding"), _int(stride, "stride")
     taps, slope = _int(taps, "taps"), _float(slope, "slope")
     _f32(x, res, rank=2)
@@ -263,7 +264,11 @@ def conv_transpose1d_poly_f32_cuda(x, wp, b, res, stride, padding, taps, slope, 
         _run("conv_transpose1d_poly_mean3_f32_cuda", [x, x2, x3, wp, b, res], [out], attrs_int=at,
              attrs_float=[_float(sc, "in_scale"), slope])
     else:
-        _run("conv_transpose1d_poly_f32_cuda", [x, wp, b, res], [out], attrs_int=at, attrs_float=[slope])
+        if state is not None:
+            check(isinstance(state, ConvState) and state.shape == (int(x.shape[0]), int(b.shape[0]), taps * stride, stride),
+                  "state must come from conv_transpose1d_prepare_f32_cuda of this weight")
+        _run("conv_transpose1d_poly_f32_cuda", [x, wp, b, res], [out], attrs_int=at, attrs_float=[slope],
+             state=None if state is None else state.handle)
     return out
 
 
@@ -356,7 +361,7 @@ class ConvState:
 def conv1d_prepare_f32_cuda(w):
     """Packs a constant conv weight f32[Co, Ci, K] once for the tensor-core path (run at init, like the reference's
     hoisted weight preparation, docs/passes/hoist-init.md). Returns None when the shape is served by the CUDA-core
-    kernel instead (Co % 128, Ci % 16 or K > 64)."""
+    kernel instead (Ci % 16 != 0 or K > 64)."""
     _f32(w, rank=3)
     co, ci, k = (int(d) for d in w.shape)
     n = int(_lib.lib().lkc_conv1d_tc_pack_floats(co, ci, k))
@@ -368,6 +373,24 @@ def conv1d_prepare_f32_cuda(w):
     if not handle:
         raise _lib.LkcError(_lib.last_error())
     return ConvState(handle, wp, (co, ci, k))
+
+
+def conv_transpose1d_prepare_f32_cuda(w, stride, padding):
+    """Packs a constant ConvTranspose1d weight f32[Ci, Co, K] once for the tensor-core path of
+    conv_transpose1d_poly_f32_cuda. Returns None when the shape is served by the CUDA-core kernel only (the
+    tensor-core path takes stride 6 or 10 with K = 2 stride, 2 padding = stride, Ci % 16 == 0)."""
+    _f32(w, rank=3)
+    s, p = _int(stride, "stride"), _int(padding, "padding")
+    ci, co, k = (int(d) for d in w.shape)
+    n = int(_lib.lib().lkc_convt_tc_pack_floats(ci, co, k, s, p))
+    if n == 0:
+        return None
+    wp = _new(w, (n,))
+    _run("convt_tc_pack_f32_cuda", [w], [wp], attrs_int=[p, s])
+    handle = _lib.lib().lkc_convt_state_create(wp.data_ptr(), ci, co, k, s, p)
+    if not handle:
+        raise _lib.LkcError(_lib.last_error())
+    return ConvState(handle, wp, (ci, co, k, s))
 
 
 def conv_tc_status(reset=True) -> int:

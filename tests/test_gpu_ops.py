@@ -37,13 +37,13 @@ CONV_CASES = [(8, 8, 50, 3, 1), (16, 12, 700, 7, 3), (12, 16, 97, 11, 5), (128, 
               (128, 22, 961, 7, 1), (22, 128, 961, 1, 1)]
 
 
-# Shapes the tensor-core kernel takes (Co % 128 == 0, Ci % 16 == 0): every Kokoro (C, K, dilation) plus tile edges:
+# Shapes the tensor-core kernel takes (Ci % 16 == 0; Co is padded to a multiple of 128 inside the pack): every Kokoro (C, K, dilation) plus tile edges:
 # one partial tile, exact tile / chunk multiples, one column past a tile, many tiles per CTA, L < halo.
 TC_CASES = [(128, 128, 1201, 3, 1), (128, 128, 1201, 7, 3), (128, 128, 5000, 11, 5), (256, 256, 640, 11, 5),
             (256, 256, 333, 3, 5), (128, 128, 256, 3, 1), (128, 128, 257, 7, 1), (128, 128, 128, 11, 1),
             (128, 128, 20, 11, 5), (128, 128, 1, 3, 1), (16, 128, 700, 7, 3), (48, 128, 300, 5, 2),
             (256, 128, 900, 3, 3), (128, 256, 900, 7, 5), (128, 128, 45000, 3, 1), (256, 256, 20800, 7, 1),
-            (128, 128, 19201, 11, 3)]
+            (128, 128, 19201, 11, 3), (128, 22, 5000, 7, 1), (32, 200, 700, 3, 1), (16, 129, 300, 5, 1)]
 
 
 @pytest.mark.parametrize("ci,co,l,k,d", CONV_CASES + TC_CASES)
@@ -60,7 +60,7 @@ def test_conv1d_fused(cuda, ci, co, l, k, d, variant):
     res = res[:, :lo]
     dx, dw, db, daf, dal, dres = dev(cuda, x, w, b, affine, alpha, np.ascontiguousarray(res))
     state = ops.conv1d_prepare_f32_cuda(dw)
-    assert (state is not None) == (co % 128 == 0 and ci % 16 == 0)
+    assert (state is not None) == (ci % 16 == 0)
     kw = dict(padding=pad, dilation=d, state=state)
 
     okw = dict(padding=pad, dilation=d)
@@ -158,7 +158,8 @@ def test_channel_stats_and_adain_affine(cuda, c, l):
 
 CONVT_CASES = [(8, 32, 5, 4, 2, 0), (16, 40, 37, 8, 4, 1), (512, 256, 26, 20, 10, 0), (512, 256, 294, 20, 10, 0),
                (256, 128, 2940, 12, 6, 1), (256, 128, 1, 12, 6, 1), (64, 64, 700, 12, 6, 1), (16, 8, 33, 6, 3, 1),
-               (8, 4, 9, 5, 5, 0)]
+               (8, 4, 9, 5, 5, 0), (256, 128, 20800, 12, 6, 1), (512, 256, 2080, 20, 10, 0), (32, 7, 257, 20, 10, 1),
+               (48, 21, 256, 12, 6, 0)]
 
 
 @pytest.mark.parametrize("ci,co,l,k,s,pl", CONVT_CASES)
@@ -187,6 +188,16 @@ def test_conv_transpose1d_poly(cuda, ci, co, l, k, s, pl, mean3):
     assert got.shape == (co, l * s + pl)
     assert rel_l2(got, oracle(torch.float32)) <= REL_L2
     np.testing.assert_allclose(got, oracle(torch.float64), atol=1e-4, rtol=1e-4)
+    st = ops.conv_transpose1d_prepare_f32_cuda(d[3], s, p)
+    assert (st is not None) == (s in (6, 10) and k == 2 * s and ci % 16 == 0)
+    if st is not None and not mean3:  # the tensor-core path on the same operands
+        got_tc = ops.conv_transpose1d_poly_f32_cuda(d[0], wp, d[4], d[5], stride=s, padding=p, taps=k // s, slope=0.1,
+                                                    pad_left=pl, state=st).cpu().numpy()
+        assert ops.conv_tc_status() == 0
+        assert rel_l2(got_tc, oracle(torch.float32)) <= REL_L2
+        np.testing.assert_allclose(got_tc, oracle(torch.float64), atol=1e-4, rtol=1e-4)
+        e_tc, e_cpu = rel_l2(got_tc, oracle(torch.float64)), rel_l2(oracle(torch.float32), oracle(torch.float64))
+        assert e_tc <= 2 * e_cpu + 2e-7
     if mean3:  # bit-identical to add3_scale followed by the op (test_kokoro_conv_fused.py:252-264)
         m = ops.add3_scale_f32_cuda(d[0], d[1], d[2], 1.0 / 3.0)
         exp = ops.conv_transpose1d_poly_f32_cuda(m, wp, d[4], d[5], stride=s, padding=p, taps=k // s, slope=0.1,
