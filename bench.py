@@ -106,8 +106,8 @@ def cpu_generator_rate(t_sample: int, reps: int, warmup: int, threads: int | Non
     """audio-s/s of the CPU oracle (f32, basic-op graph) for an utterance of t_sample frames."""
     from oracle import kokoro_oracle as O
 
-    if threads:
-        torch.set_num_threads(threads)
+    # all host cores of this process (torchrun exports OMP_NUM_THREADS=1, which would otherwise pin torch to one)
+    torch.set_num_threads(threads or len(os.sched_getaffinity(0)))
     cores = torch.get_num_threads()
     sd = synth.generator_weights(0)
     sd_t = {k: O.T(v) for k, v in sd.items()}
@@ -152,6 +152,8 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     dev = torch.device(f"cuda:{local_rank}")
     torch.cuda.set_device(dev)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's banner off stdout: rank 0 prints exactly one JSON line
         dist.init_process_group("nccl", device_id=dev)
     t = args.t
     sh = synth.shapes(t)

@@ -57,6 +57,7 @@ constexpr int STAGE_FLOATS = 32 * STAGE_PITCH;
 constexpr int MAX_HALO = 50;     // (K - 1) * dilation of the widest Kokoro conv (K 11, dilation 5)
 constexpr int MAX_W_STAGES = 6, MIN_W_STAGES = 3;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
+constexpr uint32_t SLEEP_EPI_NS = 256, SLEEP_PRO_NS = 128, SLEEP_W_NS = 256, SLEEP_MMA_NS = 32;
 constexpr uint64_t WAIT_LIMIT_NS = 200ull * 1000 * 1000;  // 0.2 s: a healthy wait is tens of microseconds
 constexpr int kMaxSmem = 232448;  // 227 KB per CTA on sm_100
 
@@ -73,6 +74,7 @@ struct TcArgs {
   int numTTiles, numCoBlk;
   int* status;
   long long* prof;  // null, or 16 cycle counters summed over CTAs (see convTcProfile)
+  int debug;        // timing experiments of the profiling build only (results are wrong when non-zero)
 };
 
 __device__ int gTcStatus = 0;
@@ -110,11 +112,14 @@ __device__ __forceinline__ uint64_t globalTimerNs() {
   return t;
 }
 // Bounded wait: gives up (false) after SPIN_LIMIT polls or WAIT_LIMIT_NS of wall time, whichever comes first, or as
-// soon as another role has aborted.
-__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile int* abortFlag) {
+// soon as another role has aborted. Between polls the warp sleeps `sleepNs`: the warp scheduler issues greedily from
+// a ready warp, so a tight spin loop starves the producer warps that share its scheduler (measured: the producers
+// ran at a tenth of their instruction rate next to spinning epilogue warps). Latency-critical waiters pass 0.
+__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile int* abortFlag, uint32_t sleepNs) {
   if (mbarTryWait(bar, parity)) return true;
   const uint64_t t0 = globalTimerNs();
   for (uint32_t spins = 0; !mbarTryWait(bar, parity); ++spins) {
+    if (sleepNs) __nanosleep(sleepNs);
     if (*abortFlag || spins >= SPIN_LIMIT) return false;
     if ((spins & 63) == 63 && globalTimerNs() - t0 > WAIT_LIMIT_NS) return false;
   }
@@ -232,12 +237,15 @@ __device__ __forceinline__ float sinSq(float u) {
   return (__float_as_int(t) & 1) ? 1.f - q : q;
 }
 
+// Prologue of one element with per-channel constants folded once per launch (sPar rows m, a, b, inv):
+//   Snake: u = (x - mean) * (alpha scale) + alpha beta; result = (u + sin^2(u)) / alpha  (= v + sin^2(alpha v) / alpha)
+//   leaky / none: v = (x - mean) * scale + beta
+// Centering first keeps the precision when the variance is tiny next to the mean, as in the reference.
 template <int ACT>
-__device__ __forceinline__ float activate(float v, float mean, float scale, float beta, float alpha, float inv,
-                                          float slope) {
-  v = (v - mean) * scale + beta;
-  if (ACT == 1) v = fmaf(inv, sinSq(alpha * v), v);
-  if (ACT == 2) v = v >= 0.f ? v : v * slope;
+__device__ __forceinline__ float activate(float x, float m, float a, float b, float inv, float slope) {
+  const float v = fmaf(x - m, a, b);
+  if (ACT == 1) return (v + sinSq(v)) * inv;
+  if (ACT == 2) return v >= 0.f ? v : v * slope;
   return v;
 }
 
@@ -281,8 +289,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   float* const sRaw = sAct + NB * actBufFloats;                   // NRAW buffers of [KC][rows] raw input
   float* const sW = sRaw + NRAW * KC * rows;                      // wStages stages of [2 (hi, lo)][KC/4][MT][4]
   float* const sStage = sW + a.wStages * W_STAGE_FLOATS;          // EPI_WARPS transpose tiles of [32][STAGE_PITCH]
-  float* const sPar = sStage + EPI_WARPS * STAGE_FLOATS;          // [5][ci]: mean, scale, beta, alpha, 1 / alpha
-  uint64_t* const bFull = reinterpret_cast<uint64_t*>(sPar + 5 * a.ci);
+  float* const sPar = sStage + EPI_WARPS * STAGE_FLOATS;          // [4][ci]: folded prologue constants
+  uint64_t* const bFull = reinterpret_cast<uint64_t*>(sPar + 4 * a.ci);
   uint64_t* const bEmpty = bFull + NB;
   uint64_t* const wFull = bEmpty + NB;
   uint64_t* const wEmpty = wFull + MAX_W_STAGES;
@@ -316,10 +324,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
 
   // mbarWait that adds the cycles it spent to acc when profiling is on
   constexpr bool profOn = PROF;
-  auto waitT = [&](uint64_t* bar, uint32_t parity, long long& acc) -> bool {
-    if (!profOn) return mbarWait(bar, parity, abortFlag);
+  const int dbg = PROF ? a.debug : 0;
+  auto waitT = [&](uint64_t* bar, uint32_t parity, long long& acc, uint32_t sleepNs) -> bool {
+    if (!profOn) return mbarWait(bar, parity, abortFlag, sleepNs);
     const long long t0 = clock64();
-    const bool ok = mbarWait(bar, parity, abortFlag);
+    const bool ok = mbarWait(bar, parity, abortFlag, sleepNs);
     acc += clock64() - t0;
     return ok;
   };
@@ -358,67 +367,53 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const float bias = (a.bias && rowOk) ? a.bias[co] : 0.f;
       // channels of this warp that exist (may be <= 0 in the last block)
       const int coValid = (TS || PARTIAL) ? (a.co - coBase < CQ ? a.co - coBase : CQ) : 32;
-      // Running sums start from bias (+ residual). The residual tile is read with lanes along time (all loads of the
-      // thread in flight at once) and transposed through shared memory; this overlaps the first chunk's MMAs.
+      // Running sums start from the bias. The residual is added one 32-column batch at a time: while the warp waits
+      // for chunk c, a cp.async brings residual batch c (lanes along time, contiguous in memory) into the warp's
+      // transpose tile; after chunk c has been drained the batch is read back with lanes along channels and added.
+      // The global latency hides behind a whole chunk of MMAs and no registers are held while waiting.
       float S[128];
-      if (a.residual) {
+#pragma unroll
+      for (int j = 0; j < 128; ++j) S[j] = bias;
+      const bool hasRes = a.residual != nullptr && !(dbg & 4);
+      auto fetchResidual = [&](int b) {  // batch b of the warp's 128 columns -> tile (zero where out of range)
         if constexpr (TS == 0) {
+          const bool ok = b * 32 + lane < nValid;
+          const float* rp = a.residual + int64_t(coBase) * a.outPitch + tChunk + b * 32 + lane;
 #pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            const bool ok = b * 32 + lane < nValid;
-            const float* rp = a.residual + int64_t(coBase) * a.outPitch + tChunk + b * 32 + lane;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              S[b * 32 + i] = (ok && (!PARTIAL || i < coValid)) ? rp[int64_t(i) * a.outPitch] : 0.f;
-          }
-#pragma unroll
-          for (int b = 0; b < 4; ++b) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) tile[i * STAGE_PITCH + lane] = S[b * 32 + i];
-            __syncwarp();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) S[b * 32 + j] = tile[lane * STAGE_PITCH + j] + bias;
-            __syncwarp();
+          for (int i = 0; i < 32; ++i) {
+            if (ok && (!PARTIAL || i < coValid)) cpAsync4(&tile[i * STAGE_PITCH + lane], rp + int64_t(i) * a.outPitch);
+            else tile[i * STAGE_PITCH + lane] = 0.f;
           }
         } else {
-          // channel cl, batch b: the 32 * TS output samples u = (tChunk + 32 b) * TS + idx are contiguous in memory;
-          // load i = cl * TS + f reads idx = 32 f + lane, which is column idx / TS of phase idx % TS
-          const int64_t uEnd = a.lo * TS;
+          // channel cl: the 32 * TS output samples u = (tChunk + 32 b) * TS + idx are contiguous in memory; copy
+          // i = cl * TS + f moves idx = 32 f + lane, which is column idx / TS of phase idx % TS
+          const int64_t uEnd = a.lo * TS, u0 = (tChunk + b * 32) * TS;
 #pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            const int64_t u0 = (tChunk + b * 32) * TS;
-#pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-              const int cl = i / TS, f = i % TS;
-              const int64_t u = u0 + f * 32 + lane;
-              S[b * 32 + i] = (cl < coValid && u < uEnd)
-                                  ? a.residual[int64_t(coBase + cl) * a.outPitch + a.padLeft + u]
-                                  : 0.f;
-            }
-          }
-#pragma unroll
-          for (int b = 0; b < 4; ++b) {
-#pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-              const int cl = i / TS, idx = (i % TS) * 32 + lane;
-              tile[(cl * TS + idx % TS) * STAGE_PITCH + idx / TS] = S[b * 32 + i];
-            }
-            __syncwarp();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) S[b * 32 + j] = tile[lane * STAGE_PITCH + j] + bias;
-            __syncwarp();
+          for (int i = 0; i < ROWS; ++i) {
+            const int cl = i / TS, idx = (i % TS) * 32 + lane;
+            float* dst = &tile[(cl * TS + idx % TS) * STAGE_PITCH + idx / TS];
+            if (cl < coValid && u0 + idx < uEnd)
+              cpAsync4(dst, a.residual + int64_t(coBase + cl) * a.outPitch + a.padLeft + u0 + idx);
+            else *dst = 0.f;
           }
         }
-      } else {
+        cpAsyncCommit();
+      };
+      auto addResidual = [&](int b) {
+        cpAsyncWait<0>();
+        __syncwarp();
+        if (TS == 0 || lane < ROWS) {
 #pragma unroll
-        for (int j = 0; j < 128; ++j) S[j] = bias;
-      }
+          for (int j = 0; j < 32; ++j) S[b * 32 + j] += tile[lane * STAGE_PITCH + j];
+        }
+        __syncwarp();
+      };
       cPre += clock64() - tPre;
-      for (int c = 0; c < nChunks16; ++c, ++chunkIt) {
-        if (!waitT(hiFull, chunkIt & 1, wHi)) {
+      // wait for the chunk's hi chain, add it to the running sums, hand Dhi back
+      auto drainChunk = [&]() -> bool {
+        if (!waitT(hiFull, chunkIt & 1, wHi, SLEEP_EPI_NS)) {
           giveUp(1, 1);
-          dead = true;
-          break;
+          return false;
         }
         tcFenceAfter();
 #pragma unroll
@@ -431,9 +426,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         tcFenceBefore();
         __syncwarp();
         if (lane == 0) mbarArrive(hiEmpty);
+        ++chunkIt;
+        return true;
+      };
+      int c = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {  // the first four chunks each carry one residual batch (static register indices)
+        if (!dead && c < nChunks16) {
+          if (hasRes) fetchResidual(b);
+          dead = !drainChunk();
+          if (!dead && hasRes) addResidual(b);
+          ++c;
+        } else if (!dead && hasRes) {  // fewer chunks than batches (Ci < 64): the rest, unhidden
+          fetchResidual(b);
+          addResidual(b);
+        }
       }
+      for (; !dead && c < nChunks16; ++c) dead = !drainChunk();
       if (dead) break;
-      if (!waitT(loFull, tileIt & 1, wLo)) {
+      if (!waitT(loFull, tileIt & 1, wLo, SLEEP_EPI_NS)) {
         giveUp(1, 2);
         break;
       }
@@ -476,7 +487,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
           __syncwarp();
-          if (lane < nb) {
+          if (lane < nb && !(dbg & 8)) {
             float* op = a.out + int64_t(coBase) * a.outPitch + tb + lane;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -543,14 +554,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
     const int rowsHalf = (rows + 1) >> 1;
     const int r0 = half * rowsHalf, r1 = (r0 + rowsHalf < rows) ? r0 + rowsHalf : rows;
     constexpr int SLOTS = (((NT + MAX_HALO + 1) >> 1) + 31) / 32;  // row slots of 32 lanes per warp
-    // per-channel parameters, once: sPar = [mean | scale | beta | alpha | 1 / alpha]
+    // per-channel parameters, once: sPar = [mean | a | b | inv] with a = scale, b = beta (x alpha for Snake), inv = 1/alpha
     for (int c = threadIdx.x - EPI_WARPS * 32; c < a.ci; c += PRO_WARPS * 32) {
-      sPar[c] = a.affine ? a.affine[c] : 0.f;
-      sPar[a.ci + c] = a.affine ? a.affine[a.ci + c] : 1.f;
-      sPar[2 * a.ci + c] = a.affine ? a.affine[2 * a.ci + c] : 0.f;
       const float al = ACT == 1 ? a.alpha[c] : 1.f;
-      sPar[3 * a.ci + c] = al;
-      sPar[4 * a.ci + c] = 1.f / al;
+      sPar[c] = a.affine ? a.affine[c] : 0.f;
+      sPar[a.ci + c] = (a.affine ? a.affine[a.ci + c] : 1.f) * al;
+      sPar[2 * a.ci + c] = (a.affine ? a.affine[2 * a.ci + c] : 0.f) * al;
+      sPar[3 * a.ci + c] = 1.f / al;
     }
     asm volatile("bar.sync 1, %0;" ::"n"(PRO_WARPS * 32) : "memory");  // producer warps only
 
@@ -580,13 +590,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
     while (t < numTiles) {
       int tn = t, cn = c + 1;
       if (cn == nChunks16) cn = 0, tn = t + gridDim.x;
-      if (tn < numTiles) issueCopies(tn, cn, (it + 1) % NRAW);
+      if (tn < numTiles && !(dbg & 2)) issueCopies(tn, cn, (it + 1) % NRAW);
       cpAsyncCommit();
       const long long tCp = clock64();
       cpAsyncWait<1>();  // this chunk's copies (the older group) have landed; the next chunk's stay in flight
       wCp += clock64() - tCp;
       const uint32_t buf = it % NB;
-      if (!waitT(&bEmpty[buf], ((it / NB) & 1) ^ 1, wB)) {
+      if (!waitT(&bEmpty[buf], ((it / NB) & 1) ^ 1, wB, SLEEP_PRO_NS)) {
         giveUp(2, 1);
         break;
       }
@@ -596,19 +606,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       float* hi = sAct + buf * actBufFloats + cg * rows * 4;
       float* lo = hi + KC * rows;
       const float* src = sRaw + (it % NRAW) * (KC * rows) + cg * 4 * rows;
-      const float* par = sPar + c * KC + cg * 4;  // this thread's four channels: broadcast shared-memory reads
+      // this thread's four channels: constants in registers for the whole chunk (they were re-read from shared
+      // memory per row slot before: 800 of the producers' 1440 shared-memory wavefronts per chunk)
+      float pm[4], pa[4], pb[4], pi[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float* par = sPar + c * KC + cg * 4 + e;
+        pm[e] = par[0], pa[e] = par[a.ci], pb[e] = par[2 * a.ci], pi[e] = par[3 * a.ci];
+      }
 #pragma unroll 1
       for (int sl = 0; sl < SLOTS; ++sl) {
         const int r = r0 + sl * 32 + lane;
-        if (r < r1) {
+        if (r < r1 && !(dbg & 1)) {
           const int64_t pos = pos0 + r;
           const bool ok = pos >= 0 && pos < a.l;
           float v[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            v[e] = ok ? activate<ACT>(src[e * rows + r], par[e], par[a.ci + e], par[2 * a.ci + e], par[3 * a.ci + e],
-                                      par[4 * a.ci + e], a.slope)
-                      : 0.f;
+            v[e] = ok ? activate<ACT>(src[e * rows + r], pm[e], pa[e], pb[e], pi[e], a.slope) : 0.f;
           float4 h, l;
           h.x = tf32Round(v[0]), h.y = tf32Round(v[1]), h.z = tf32Round(v[2]), h.w = tf32Round(v[3]);
           l.x = v[0] - h.x, l.y = v[1] - h.y, l.z = v[2] - h.z, l.w = v[3] - h.w;
@@ -638,7 +653,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         const float* src = a.wp + int64_t(cb) * blocksPerCo * W_STAGE_FLOATS;
         for (int64_t blk = 0; blk < blocksPerCo; ++blk, ++wIt) {
           const uint32_t s = wIt % a.wStages;
-          if (!waitT(&wEmpty[s], ((wIt / a.wStages) & 1) ^ 1, wW)) {
+          if (!waitT(&wEmpty[s], ((wIt / a.wStages) & 1) ^ 1, wW, SLEEP_W_NS)) {
             giveUp(3, 1);
             dead = true;
             break;
@@ -682,22 +697,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const long long tStart = clock64();
       while (cu.tile < numTiles) {
         if (cu.kk == 0) {
-          if (!waitT(&bFull[cu.buf], cu.bufPhase, wBf)) {
+          if (!waitT(&bFull[cu.buf], cu.bufPhase, wBf, SLEEP_MMA_NS)) {
             giveUp(4, 2);
             dead = true;
           } else if (isHi) {
-            if (!waitT(hiEmpty, cu.chunkPar ^ 1, wHe)) {  // Dhi drained by the epilogue warps
+            if (!waitT(hiEmpty, cu.chunkPar ^ 1, wHe, SLEEP_MMA_NS)) {  // Dhi drained by the epilogue warps
               giveUp(4, 1);
               dead = true;
             }
           } else if (cu.c == 0) {
-            if (!waitT(loEmpty, cu.tilePar ^ 1, wHe)) {  // Dlo of the previous tile folded into the running sums
+            if (!waitT(loEmpty, cu.tilePar ^ 1, wHe, SLEEP_MMA_NS)) {  // Dlo of the previous tile folded into the running sums
               giveUp(4, 4);
               dead = true;
             }
           }
         }
-        if (!dead && !waitT(&wFull[cu.stage], cu.stagePhase, wWf)) {
+        if (!dead && !waitT(&wFull[cu.stage], cu.stagePhase, wWf, SLEEP_MMA_NS)) {
           giveUp(4, 3);
           dead = true;
         }
@@ -807,7 +822,7 @@ __global__ void convtTcPackKernel(const float* __restrict__ w, float* __restrict
 // Dynamic shared memory of one CTA: activation buffers, raw staging, weight ring (as deep as fits, MIN..MAX stages),
 // transpose tiles, per-channel parameters, barriers. 0 if the minimum ring does not fit.
 static size_t convTcSmemBytes(int64_t ci, int rows, int* wStages) {
-  const size_t fixed = size_t(EPI_WARPS) * STAGE_FLOATS * 4 + size_t(5) * ci * 4 + 256;
+  const size_t fixed = size_t(EPI_WARPS) * STAGE_FLOATS * 4 + size_t(4) * ci * 4 + 256;
   const size_t act = size_t(NB) * 2 * KC * rows * 4 + size_t(NRAW) * KC * rows * 4;
   if (fixed + act + size_t(MIN_W_STAGES) * W_STAGE_BYTES > size_t(kMaxSmem)) return 0;
   int ws = int((size_t(kMaxSmem) - fixed - act) / W_STAGE_BYTES);
@@ -856,6 +871,7 @@ static int launchTc(const TcArgs& a, int grid, size_t smem, cudaStream_t s) {
 }
 
 static bool gProfileOn = false;
+static int gDebugFlags = 0;
 
 // Profiling counters of the tensor-core kernel (cycles, summed over CTAs and launches since the last reset; one
 // representative warp per role): [0..4] MMA warp: wait activations, wait Dhi drained, wait weights, wait Dlo folded,
@@ -863,6 +879,7 @@ static bool gProfileOn = false;
 // wait buffer free, wait cp.async, transform, total; [14..15] weight producer: wait stage free, total.
 int convTcProfile(int enable, long long* out16) {
   gProfileOn = enable != 0;
+  gDebugFlags = enable > 1 ? (enable >> 4) : 0;  // enable = 1 | (flags << 4): timing experiments
   if (out16) {
     cudaError_t e = cudaMemcpyFromSymbol(out16, gTcProf, sizeof(long long) * 16);
     if (e != cudaSuccess) return failCuda("conv1d_tc_profile", e);
@@ -898,6 +915,7 @@ static int finishArgs(TcArgs& a, int* grid, size_t* smem) {
   }
   a.status = statusPtr[dev];
   a.prof = gProfileOn ? profPtr[dev] : nullptr;
+  a.debug = gProfileOn ? gDebugFlags : 0;
   const int tiles = a.numTTiles * a.numCoBlk;
   *grid = tiles < smCount[dev] ? tiles : smCount[dev];
   return 0;
