@@ -124,6 +124,25 @@ def cpu_generator_rate(t_sample: int, reps: int, warmup: int, threads: int | Non
     return 300.0 * t_sample / SAMPLE_RATE / sec, sec, cores
 
 
+def init_nccl(dev):
+    """Process group over NCCL (rank / world size / master address from the torchrun environment). NCCL prints its
+    version banner on stdout when the communicator is created: stdout is pointed at stderr until the first
+    collective is done, so that rank 0's stdout carries exactly one JSON line."""
+    import torch.distributed as dist
+
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        dist.init_process_group("nccl", device_id=dev)
+        dist.barrier()
+        torch.cuda.synchronize()
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
 def run_reference(args, rank: int):
     if rank != 0:
         return
@@ -152,9 +171,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     dev = torch.device(f"cuda:{local_rank}")
     torch.cuda.set_device(dev)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's banner off stdout: rank 0 prints exactly one JSON line
-        dist.init_process_group("nccl", device_id=dev)
+        init_nccl(dev)
     t = args.t
     sh = synth.shapes(t)
     audio_s = sh["S"] / SAMPLE_RATE
@@ -262,6 +279,70 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         dist.destroy_process_group()
 
 
+def run_batch(args, rank: int, local_rank: int, world: int):
+    """Config 3: 64 independent utterances with T ~ U{120..800} (seeded), sharded by utterance across the ranks
+    (longest-processing-time-first on T, lokinfer_b200/sharding.py), no inter-GPU communication. One step = every
+    utterance once (each rank replays the CUDA graphs of its own utterances back to back); strong scaling: the total
+    work is fixed as N grows. Reports aggregate audio-seconds/sec = all audio seconds / max-over-ranks time."""
+    import torch.distributed as dist
+
+    from lokinfer_b200 import Generator, sharding
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        init_nccl(dev)
+    lengths = np.random.default_rng(64).integers(120, 801, 64).tolist()
+    plan = sharding.assign(lengths, world)
+    mine = plan[rank]
+    gen = Generator(synth.generator_weights(0), dev)
+    graphs = []
+    for i in mine:  # one graph per distinct length; inputs are resident in HBM
+        t = lengths[i]
+        inp = synth.generator_inputs(t, 100 + i)
+        bufs = gen.capture(t)
+        for k in ("x", "har", "s"):
+            bufs[k].copy_(torch.from_numpy(inp[k]))
+        graphs.append(bufs["graph"])
+    torch.cuda.synchronize()
+
+    def step():
+        for g in graphs:
+            g.replay()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        step()
+    b.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        total_audio = sharding.audio_seconds(lengths)
+        line = {
+            "metric": METRIC, "value": total_audio * args.steps / (float(ms.item()) * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": float(ms.item()) / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "kokoro_generator_batch64", "utterances": 64, "T_range": [120, 800],
+                       "audio_seconds_per_step": total_audio, "sharding": "by utterance, longest first, no communication",
+                       "rank_loads_T": sharding.loads(lengths, plan)},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_sweep(args):
     """Conv kernel sweep (f32, batch 1): one fused conv1d_snake_res launch per step at each point, timed with CUDA
     events; prints one JSON line per point with achieved TFLOP/s (2 Co Ci K L / time) and the fraction of the 3xTF32
@@ -313,6 +394,9 @@ def main():
     ap.add_argument("--t", type=int, default=2080, help="generator input frames per utterance (2080 = 26 s, 320 = 4 s)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--sweep", default=None, choices=["conv"], help="run the conv kernel sweep instead of the generator")
+    ap.add_argument("--workload", default="single", choices=["single", "batch64"],
+                    help="single: one utterance of --t frames per GPU (default, weak scaling); batch64: 64 utterances of "
+                         "120..800 frames sharded across the GPUs (strong scaling)")
     ap.add_argument("--point", default=None, help="single sweep point Ci,Co,L,K,dilation")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -325,6 +409,9 @@ def main():
     if args.sweep:
         if rank == 0:
             run_sweep(args)
+        return
+    if args.workload == "batch64":
+        run_batch(args, rank, local_rank, world)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         print(f"bench.py: --gpus {args.gpus} needs torchrun with {args.gpus} ranks; running 1 rank", file=sys.stderr)

@@ -221,31 +221,34 @@ __device__ __forceinline__ float tf32Round(float v) {
 
 // sin(u)^2 for any finite u, absolute error ~1.5e-7: u = n pi/2 + r with |r| <= pi/4 (three-term Cody-Waite),
 // sin^2(u) = sin^2(r) for even n and 1 - sin^2(r) for odd n.
-__device__ __forceinline__ float sinSq(float u) {
-  const float t = fmaf(u, 0.6366197723675814f, 12582912.f);
-  const float n = t - 12582912.f;
-  float r = fmaf(n, -1.5703125f, u);
-  r = fmaf(n, -4.837512969970703125e-4f, r);
-  r = fmaf(n, -7.54978995489188216e-8f, r);
-  const float s2 = r * r;
-  float p = fmaf(s2, 2.7557319e-6f, -1.9841270e-4f);
-  p = fmaf(p, s2, 8.3333333e-3f);
-  p = fmaf(p, s2, -1.6666667e-1f);
-  p = fmaf(p, s2, 1.f);
-  const float s = r * p;
-  const float q = s * s;
-  return (__float_as_int(t) & 1) ? 1.f - q : q;
+// Two elements at a time on the packed f32x2 pipe (fma.rn.f32x2 and friends: one instruction, two lanes of math),
+// two independent lanes of the same operation sequence.
+__device__ __forceinline__ float2 sinSq2(float2 u) {
+  const float2 kMagic = make_float2(12582912.f, 12582912.f);
+  const float2 t = __ffma2_rn(u, make_float2(0.6366197723675814f, 0.6366197723675814f), kMagic);
+  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  float2 r = __ffma2_rn(n, make_float2(-1.5703125f, -1.5703125f), u);
+  r = __ffma2_rn(n, make_float2(-4.837512969970703125e-4f, -4.837512969970703125e-4f), r);
+  r = __ffma2_rn(n, make_float2(-7.54978995489188216e-8f, -7.54978995489188216e-8f), r);
+  const float2 s2 = __fmul2_rn(r, r);
+  float2 p = __ffma2_rn(s2, make_float2(2.7557319e-6f, 2.7557319e-6f), make_float2(-1.9841270e-4f, -1.9841270e-4f));
+  p = __ffma2_rn(p, s2, make_float2(8.3333333e-3f, 8.3333333e-3f));
+  p = __ffma2_rn(p, s2, make_float2(-1.6666667e-1f, -1.6666667e-1f));
+  p = __ffma2_rn(p, s2, make_float2(1.f, 1.f));
+  const float2 sn = __fmul2_rn(r, p);
+  const float2 q = __fmul2_rn(sn, sn);
+  return make_float2((__float_as_int(t.x) & 1) ? 1.f - q.x : q.x, (__float_as_int(t.y) & 1) ? 1.f - q.y : q.y);
 }
 
-// Prologue of one element with per-channel constants folded once per launch (sPar rows m, a, b, inv):
+// Prologue with per-channel constants folded once per launch (sPar rows mean, a, b, inv):
 //   Snake: u = (x - mean) * (alpha scale) + alpha beta; result = (u + sin^2(u)) / alpha  (= v + sin^2(alpha v) / alpha)
 //   leaky / none: v = (x - mean) * scale + beta
 // Centering first keeps the precision when the variance is tiny next to the mean, as in the reference.
 template <int ACT>
-__device__ __forceinline__ float activate(float x, float m, float a, float b, float inv, float slope) {
-  const float v = fmaf(x - m, a, b);
-  if (ACT == 1) return (v + sinSq(v)) * inv;
-  if (ACT == 2) return v >= 0.f ? v : v * slope;
+__device__ __forceinline__ float2 activate2(float2 x, float2 negm, float2 a, float2 b, float2 inv, float slope) {
+  const float2 v = __ffma2_rn(__fadd2_rn(x, negm), a, b);
+  if (ACT == 1) return __fmul2_rn(__fadd2_rn(v, sinSq2(v)), inv);
+  if (ACT == 2) return make_float2(v.x >= 0.f ? v.x : v.x * slope, v.y >= 0.f ? v.y : v.y * slope);
   return v;
 }
 
@@ -421,7 +424,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           float v[32];
           tmemLoad32(tmemHi + laneBase + g * 128 + b * 32, v);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) S[b * 32 + j] += v[j];
+          for (int j = 0; j < 32; j += 2) {  // packed f32x2 adds: half the instructions of the accumulate loop
+            const float2 sum = __fadd2_rn(make_float2(S[b * 32 + j], S[b * 32 + j + 1]), make_float2(v[j], v[j + 1]));
+            S[b * 32 + j] = sum.x, S[b * 32 + j + 1] = sum.y;
+          }
         }
         tcFenceBefore();
         __syncwarp();
@@ -608,11 +614,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const float* src = sRaw + (it % NRAW) * (KC * rows) + cg * 4 * rows;
       // this thread's four channels: constants in registers for the whole chunk (they were re-read from shared
       // memory per row slot before: 800 of the producers' 1440 shared-memory wavefronts per chunk)
-      float pm[4], pa[4], pb[4], pi[4];
+      float2 nm[2], pa[2], pb[2], pi[2];  // channel pairs (0, 1) and (2, 3); nm = -mean
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float* par = sPar + c * KC + cg * 4 + e;
-        pm[e] = par[0], pa[e] = par[a.ci], pb[e] = par[2 * a.ci], pi[e] = par[3 * a.ci];
+      for (int h = 0; h < 2; ++h) {
+        const float* par = sPar + c * KC + cg * 4 + 2 * h;
+        nm[h] = make_float2(-par[0], -par[1]);
+        pa[h] = make_float2(par[a.ci], par[a.ci + 1]);
+        pb[h] = make_float2(par[2 * a.ci], par[2 * a.ci + 1]);
+        pi[h] = make_float2(par[3 * a.ci], par[3 * a.ci + 1]);
       }
 #pragma unroll 1
       for (int sl = 0; sl < SLOTS; ++sl) {
@@ -620,13 +629,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         if (r < r1 && !(dbg & 1)) {
           const int64_t pos = pos0 + r;
           const bool ok = pos >= 0 && pos < a.l;
-          float v[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            v[e] = ok ? activate<ACT>(src[e * rows + r], pm[e], pa[e], pb[e], pi[e], a.slope) : 0.f;
-          float4 h, l;
-          h.x = tf32Round(v[0]), h.y = tf32Round(v[1]), h.z = tf32Round(v[2]), h.w = tf32Round(v[3]);
-          l.x = v[0] - h.x, l.y = v[1] - h.y, l.z = v[2] - h.z, l.w = v[3] - h.w;
+          float4 h = make_float4(0.f, 0.f, 0.f, 0.f), l = h;
+          if (ok) {
+            const float2 v01 = activate2<ACT>(make_float2(src[r], src[rows + r]), nm[0], pa[0], pb[0], pi[0], a.slope);
+            const float2 v23 =
+                activate2<ACT>(make_float2(src[2 * rows + r], src[3 * rows + r]), nm[1], pa[1], pb[1], pi[1], a.slope);
+            h.x = tf32Round(v01.x), h.y = tf32Round(v01.y), h.z = tf32Round(v23.x), h.w = tf32Round(v23.y);
+            const float2 l01 = __fadd2_rn(v01, make_float2(-h.x, -h.y)), l23 = __fadd2_rn(v23, make_float2(-h.z, -h.w));
+            l = make_float4(l01.x, l01.y, l23.x, l23.y);
+          }
           *reinterpret_cast<float4*>(hi + r * 4) = h;
           *reinterpret_cast<float4*>(lo + r * 4) = l;
         }
