@@ -12,7 +12,8 @@ data-path collective -> weak scaling; time = max over ranks.
             x / har / s, the replay, and the device -> host copy of the waveform inside the timed region.
 `roofline`: the fused conv kernels (the dominant kernels), timed live per launch with CUDA events in an extra
             eager pass; achieved = algorithmic conv FLOPs (2 Co Ci K Lo per launch) / summed launch time, against
-            the 3xTF32 tensor roofline = measured bf16 peak / 2 (TF32 rate) / 3 (three TF32 products per f32 one).
+            the split-operand tensor roofline = measured dense bf16 peak / 3 (the kernel spends three f16 MMA products,
+            which run at the bf16 rate, per f32 multiply-add: hi*hi, lo*hi, hi*lo).
 `cpu_baseline` / --impl reference: the CPU oracle (torch f32, the basic-op graph the reference's eager PyTorch
             modules run) on the host cores, on a bounded sample (a shorter utterance of the same model).
 """
@@ -241,14 +242,15 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                 conv_ms += ms
                 conv_flops += 2.0 * co * ci * k * l  # "same" padding: Lo = L
         pk = peaks()
-        peak = pk["bf16_tflops"] / 2.0 / 3.0
+        peak = pk["bf16_tflops"] / 3.0  # three f16-rate MMA products per f32 product
         achieved = conv_flops / (conv_ms * 1e-3) / 1e12
         total_ms = sum(v[1] for v in agg.values())
         kernels = {n: {"launches": v[0], "ms": round(v[1], 4), "share": round(v[1] / total_ms, 4)}
                    for n, v in sorted(agg.items(), key=lambda kv: -kv[1][1])}
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "traffic": None, "kernel": "conv1d_{snake,leaky}[_res]_f32_cuda (all fused conv launches of one "
-                    "forward)", "peak_source": f"{pk['source']}: bf16 {pk['bf16_tflops']} TF/s / 2 (TF32) / 3 (3xTF32)",
+                    "forward)", "peak_source": f"{pk['source']}: bf16 {pk['bf16_tflops']} TF/s / 3 (f16 hi/lo split: 3 MMA products per f32 "
+                    "product)",
                     "conv_ms_per_step": conv_ms, "conv_flops_per_step": conv_flops}
         if world == 1 and not args.no_cpu:
             t_sample = min(t, 520)
@@ -345,14 +347,14 @@ def run_batch(args, rank: int, local_rank: int, world: int):
 
 def run_sweep(args):
     """Conv kernel sweep (f32, batch 1): one fused conv1d_snake_res launch per step at each point, timed with CUDA
-    events; prints one JSON line per point with achieved TFLOP/s (2 Co Ci K L / time) and the fraction of the 3xTF32
-    tensor roofline. --point Ci,Co,L,K,d runs a single point (used for ncu captures)."""
+    events; prints one JSON line per point with achieved TFLOP/s (2 Co Ci K L / time) and the fraction of the
+    split-operand tensor roofline (measured bf16 peak / 3). --point Ci,Co,L,K,d runs a single point (used for ncu captures)."""
     from lokinfer_b200 import ops
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     dev = torch.device("cuda:0")
     pk = peaks()
-    peak = pk["bf16_tflops"] / 2.0 / 3.0
+    peak = pk["bf16_tflops"] / 3.0
     if args.point:
         points = [tuple(int(v) for v in args.point.split(","))]
     else:
@@ -380,7 +382,7 @@ def run_sweep(args):
         flops = 2.0 * co * ci * k * l
         tf = flops / (ms * 1e-3) / 1e12
         print(json.dumps({"sweep": "conv1d_snake_res_f32_cuda", "ci": ci, "co": co, "L": l, "K": k, "dilation": d,
-                          "ms": ms, "tflops": tf, "frac_3xtf32_roofline": tf / peak, "peak_tflops": peak,
+                          "ms": ms, "tflops": tf, "frac_split_roofline": tf / peak, "peak_tflops": peak,
                           "peak_source": pk["source"], "path": "tcgen05" if st is not None else "cuda-core",
                           "tc_status": ops.conv_tc_status()}), flush=True)
 

@@ -116,12 +116,16 @@ LKC_API int lkc_conv1d_leaky_mean3_f32_cuda(const LkcArgs* a, void* stream);
  *   n = lkc_conv1d_tc_pack_floats(Co, Ci, K)       floats of the pack; 0 = shape not eligible (needs Ci % 16 == 0,
  *                                                  K <= 64), the CUDA-core kernel serves it. Co is padded to a
  *                                                  multiple of 128 with zero rows inside the pack
- *   lkc_conv1d_tc_pack_f32_cuda: ptrs w[Co,Ci,K] | wp[n]; ints w(3) wp(1)     hi / lo TF32 split in the UMMA layout
+ *   lkc_conv1d_tc_pack_f32_cuda: ptrs w[Co,Ci,K] | wp[n]; ints w(3) wp(1)     hi / lo operand split in the UMMA layout
  *   st = lkc_conv1d_state_create(wp, Co, Ci, K)    host-side handle; pass it as LkcArgs.state of the conv1d_* calls
  * A conv call with a state whose shape is eligible ((K - 1) * dilation <= 50, no mean3 input) runs on the tensor
  * cores; anything else runs on the CUDA-core kernel with identical semantics. lkc_conv1d_tc_status reads (and
  * optionally clears) the device status word the kernel sets if one of its bounded waits gave up (0 = ok); it
- * synchronises the device. lkc_set_conv_path(1) forces the CUDA-core kernel (A/B testing), 0 restores the default. */
+ * synchronises the device; bit 0x10000 of the word means an activation exceeded the f16 range (65504) under the
+ * f16 operand split and was clamped. lkc_set_conv_path chooses the path and the operand format of packs made
+ * AFTER the call: 0 (default) tensor cores with operands split into f16 hi + f16 lo * 2^-11 (3 kind::f16 MMAs per
+ * 16 channels and tap), 2 tensor cores with tf32 hi + tf32 lo (6 kind::tf32 MMAs), 1 the CUDA-core kernel only
+ * (A/B testing). lkc_*_pack_floats report sizes for the current format; a state remembers the format of its pack. */
 typedef struct LkcConvState LkcConvState;
 LKC_API int64_t lkc_conv1d_tc_pack_floats(int64_t co, int64_t ci, int64_t k);
 LKC_API int lkc_conv1d_tc_pack_f32_cuda(const LkcArgs* a, void* stream);
@@ -134,6 +138,11 @@ LKC_API int lkc_set_conv_path(int mode);
  * NULL) receives the 16 sums recorded so far (MMA / epilogue / producer / weight-producer wait and phase cycles, see
  * conv_tc.cu) and the counters are cleared. Synchronises the device. */
 LKC_API int lkc_conv1d_tc_profile(int enable, int64_t* counters16);
+/* Event timeline of one CTA of the last profiled launch (recorded when enable carries debug flag 16, that is
+ * enable = 1 | (16 << 4)): events (may be NULL) receives 6 roles x 512 entries, each clock << 16 | index << 4 | tag, 0 = unused;
+ * roles are hi issuer, lo issuer, epilogue warp 0, producer warp 0, weight producer, weight-stage arrival. reset != 0 clears the buffer.
+ * Synchronises the device. */
+LKC_API int lkc_conv1d_tc_trace(int64_t* events, int reset);
 
 /* conv_transpose1d_poly[_mean3]_f32_cpu (kernels/cpu/kokoro_conv.cpp:139-229, adapters :294-309):
  *   out = reflect_pad_left(conv_transpose1d(leaky(xin, slope), w, b, stride, padding), pad_left) + res,

@@ -105,17 +105,18 @@ struct Entry {
 
 // Routes one fused conv to the tensor-core kernel when the shape qualifies, else to the CUDA-core kernel.
 namespace {
-int gConvPath = 0;  // 0 = tensor cores when eligible, 1 = CUDA-core kernel only
+int gConvPath = 0;  // 0 = tensor cores, f16 split packs; 1 = CUDA-core kernel only; 2 = tensor cores, tf32 split packs
 }
 
-bool convPathForcedSimt() { return gConvPath != 0; }
+bool convPathForcedSimt() { return gConvPath == 1; }
+bool convPackF16() { return gConvPath != 2; }
 
 int convFused(const ConvFusedParams& p, cudaStream_t s) {
-  if (gConvPath == 0 && convTcEligible(p)) {
+  if (gConvPath != 1 && convTcEligible(p)) {
     const ConvState* st = static_cast<const ConvState*>(p.state);
     LKC_REQUIRE(st->wp && st->stride == 0 && st->co == p.co && st->ci == p.ci && st->k == p.k,
                 "conv1d fused: the prepared state does not match the weight shape");
-    return convTc(p, st->wp, s);
+    return convTc(p, st->wp, st->f16, s);
   }
   return convSimt(p, 1, s);
 }
@@ -174,13 +175,14 @@ extern "C" LKC_API int lkc_conv1d_tc_pack_f32_cuda(const LkcArgs* a, void* strea
   const int64_t co = a->ints[0], ci = a->ints[1], k = a->ints[2];
   LKC_REQUIRE(co > 0 && ci > 0 && ci % 16 == 0 && k >= 1 && k <= 64,
               "conv1d_tc_pack_f32_cuda: needs Ci % 16 == 0, 1 <= K <= 64");
-  LKC_REQUIRE(a->ints[3] == convTcPackFloats(co, ci, k), "conv1d_tc_pack_f32_cuda: wp must hold lkc_conv1d_tc_pack_floats");
-  return convTcPack(F(a, 0), O(a, 1), co, ci, k, S(stream));
+  LKC_REQUIRE(a->ints[3] == convTcPackFloats(co, ci, k, convPackF16()),
+              "conv1d_tc_pack_f32_cuda: wp must hold lkc_conv1d_tc_pack_floats (of the current operand format)");
+  return convTcPack(F(a, 0), O(a, 1), co, ci, k, convPackF16(), S(stream));
 }
 
 extern "C" LKC_API int64_t lkc_conv1d_tc_pack_floats(int64_t co, int64_t ci, int64_t k) {
   if (co <= 0 || ci <= 0 || ci % 16 != 0 || k < 1 || k > 64) return 0;
-  return convTcPackFloats(co, ci, k);
+  return convTcPackFloats(co, ci, k, convPackF16());
 }
 
 extern "C" LKC_API LkcConvState* lkc_conv1d_state_create(const void* wp, int64_t co, int64_t ci, int64_t k) {
@@ -188,7 +190,7 @@ extern "C" LKC_API LkcConvState* lkc_conv1d_state_create(const void* wp, int64_t
     fail("conv1d_state_create: shape not eligible for the tensor-core path or null pack");
     return nullptr;
   }
-  ConvState* st = new (std::nothrow) ConvState{static_cast<const float*>(wp), co, ci, k, 0};
+  ConvState* st = new (std::nothrow) ConvState{static_cast<const float*>(wp), co, ci, k, 0, convPackF16()};
   if (!st) fail("conv1d_state_create: out of host memory");
   return reinterpret_cast<LkcConvState*>(st);
 }
@@ -201,12 +203,13 @@ extern "C" LKC_API int lkc_convt_tc_pack_f32_cuda(const LkcArgs* a, void* stream
   const int64_t ci = a->ints[0], co = a->ints[1], k = a->ints[2], pad = a->ints[4], s = a->ints[5];
   LKC_REQUIRE(convtTcEligible(ci, co, k, s, pad),
               "convt_tc_pack_f32_cuda: needs stride 6 or 10, K = 2 stride, 2 padding = stride, Ci % 16 == 0");
-  LKC_REQUIRE(a->ints[3] == convtTcPackFloats(ci, co, s), "convt_tc_pack_f32_cuda: wp must hold lkc_convt_tc_pack_floats");
-  return convtTcPack(F(a, 0), O(a, 1), ci, co, k, s, pad, S(stream));
+  LKC_REQUIRE(a->ints[3] == convtTcPackFloats(ci, co, s, convPackF16()),
+              "convt_tc_pack_f32_cuda: wp must hold lkc_convt_tc_pack_floats (of the current operand format)");
+  return convtTcPack(F(a, 0), O(a, 1), ci, co, k, s, pad, convPackF16(), S(stream));
 }
 
 extern "C" LKC_API int64_t lkc_convt_tc_pack_floats(int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding) {
-  return convtTcEligible(ci, co, k, stride, padding) ? convtTcPackFloats(ci, co, stride) : 0;
+  return convtTcEligible(ci, co, k, stride, padding) ? convtTcPackFloats(ci, co, stride, convPackF16()) : 0;
 }
 
 extern "C" LKC_API LkcConvState* lkc_convt_state_create(const void* wp, int64_t ci, int64_t co, int64_t k,
@@ -215,7 +218,7 @@ extern "C" LKC_API LkcConvState* lkc_convt_state_create(const void* wp, int64_t 
     fail("convt_state_create: shape not eligible for the tensor-core path or null pack");
     return nullptr;
   }
-  ConvState* st = new (std::nothrow) ConvState{static_cast<const float*>(wp), co, ci, k, stride};
+  ConvState* st = new (std::nothrow) ConvState{static_cast<const float*>(wp), co, ci, k, stride, convPackF16()};
   if (!st) fail("convt_state_create: out of host memory");
   return reinterpret_cast<LkcConvState*>(st);
 }
@@ -229,8 +232,12 @@ extern "C" LKC_API int lkc_conv1d_tc_profile(int enable, int64_t* counters16) {
   return convTcProfile(enable, reinterpret_cast<long long*>(counters16));
 }
 
+extern "C" LKC_API int lkc_conv1d_tc_trace(int64_t* events, int reset) {
+  return convTcTrace(reinterpret_cast<long long*>(events), reset);
+}
+
 extern "C" LKC_API int lkc_set_conv_path(int mode) {
-  LKC_REQUIRE(mode == 0 || mode == 1, "set_conv_path: mode must be 0 (auto) or 1 (CUDA cores only)");
+  LKC_REQUIRE(mode >= 0 && mode <= 2, "set_conv_path: mode must be 0 (f16 split), 1 (CUDA cores only) or 2 (tf32 split)");
   gConvPath = mode;
   return 0;
 }

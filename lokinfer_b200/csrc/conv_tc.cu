@@ -1,35 +1,41 @@
-// Tensor-core fused conv1d for sm_100a: implicit GEMM on tcgen05 with TMEM accumulators, 3xTF32.
+// Tensor-core fused conv1d for sm_100a: implicit GEMM on tcgen05 with TMEM accumulators and split operands.
 //
 //   out[co, t] = sum_{ci, kk} W[co, ci, kk] * A[ci, t + kk d - pad],  A = act((x - mean) * scale + beta), zero outside
 //   [0, L); epilogue + bias [+ residual] [* oscale] and the per-(channel, 128-column chunk) (mean, M2).
 //
 // GEMM view: D[128 co, 256 t] += Wtap[128 co, 16 ci] * Ashift[16 ci, 256 t] for every 16-channel chunk and tap.
-// f32 accuracy comes from the 3xTF32 split: v = hi + lo with hi = tf32(v) (round to nearest) and lo = v - hi (exact
-// in f32); out = sum Whi Ahi + (sum Wlo Ahi + Whi Alo) (the lo*lo term, 2^-22 relative, is dropped).
+// f32 accuracy comes from splitting both operands, v = hi + lo with an 11-bit hi and an 11-bit lo:
+// out = sum Whi Ahi + (sum Wlo Ahi + Whi Alo); the lo*lo term, 2^-22 relative, is dropped. Two operand formats
+// (see Fmt below): f16 halves (default; 3 kind::f16 K16 MMAs per tap and 16 channels) or tf32 halves (6 kind::tf32
+// K8 MMAs).
 //
 // The tensor core adds into its f32 accumulator with truncation, so a long accumulation chain drifts towards zero by
 // about 1.5e-8 of the result per MMA (measured: the error grows linearly with the chain length). Two accumulators
-// keep that out of the result: Dhi (TMEM columns 0-255) takes only the hi*hi products of ONE 16-channel chunk
-// (2 K taps MMAs), is then drained by the epilogue warps into f32 registers (round-to-nearest adds on the CUDA cores)
-// and restarted; Dlo (columns 256-511) takes every lo product of the tile, where the same drift is scaled by 2^-11.
+// keep that out of the result: Dhi (TMEM columns 0-255) takes only the hi*hi products of a short run of MMAs (a drain
+// group, at most 12 chained MMAs), is then drained by the epilogue warps into f32 registers (round-to-nearest adds on
+// the CUDA cores) and restarted; Dlo (columns 256-511) takes every lo product of the tile, where the same drift is
+// scaled by 2^-11.
 //
 // One persistent CTA per SM, 20 warps in 5 warpgroups, warp-specialised (registers rebalanced with setmaxnreg):
-//   warps 0-7   accumulate + epilogue: 128 running sums per thread, started from bias + residual (read with lanes
-//               along time, all loads in flight at once, transposed through shared memory) while the first chunk's
-//               MMAs run; per chunk += Dhi (tcgen05.ld); per tile += Dlo, oscale, chunk statistics and a transposed,
+//   warps 0-7   accumulate + epilogue: 128 running sums per thread, started from the bias; the residual is added one
+//               32-column batch at a time (cp.async into the warp's transpose tile behind a Dhi drain); per drain
+//               group += Dhi (tcgen05.ld); per tile += Dlo, oscale, chunk statistics and a transposed,
 //               time-contiguous store
 //   warps 8-15  activation producers: cp.async of the raw input window of the NEXT chunk into a staging buffer (the
 //               global latency hides behind a whole chunk of work), then affine -> Snake / leaky -> hi / lo split of
-//               the current chunk into shared memory in the K-major no-swizzle UMMA layout [channel group of 4]
-//               [time row][4 channels]: a tap shift of kk*d time steps is a +16*kk*d byte offset of the descriptor
-//               start address, so one staged window serves all taps
-//   warp 16     weight producer: cp.async.bulk of pre-packed 16 KB blocks (hi | lo of one [128 co x 16 ci] tap slice,
-//               already in the UMMA layout) from global (L2-resident) into a ring of shared-memory stages
-//   warp 17     hi MMA issuer: one lane issues the two hi*hi tcgen05.mma (kind::tf32, M128 N256 K8) of every tap
-//   warp 18     lo MMA issuer: the four lo MMAs of every tap. Two issuing threads keep the tensor pipe fed while one
-//               of them does its bookkeeping, and the lo stream runs on while Dhi is being drained
+//               the current chunk into shared memory in the K-major no-swizzle UMMA layout [16-byte K chunk]
+//               [time row][4 f32 or 8 f16 channels]: a tap shift of kk*d time steps is a +16*kk*d byte offset of the
+//               descriptor start address, so one staged window serves all taps
+//   warp 16     weight producer: one cp.async.bulk per tap group (up to 4 taps; hi | lo of [128 co x 16 ci] per tap,
+//               pre-packed in the UMMA layout, L2-resident) into a ring of shared-memory slots
+//   warp 17     MMA issuer (one lane): per tap group one wait, the group's MMAs back to back, one release
+//   warp 18     second issuer in the two-thread variant (hi MMAs on warp 17, lo MMAs on warp 18), else idle
 // All hand-offs are mbarriers. Every wait is bounded: on a timeout the kernel records a status word, drains and
 // returns (TMEM is freed on every path).
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
 #include "lkc_common.h"
 
 namespace lkc {
@@ -38,7 +44,6 @@ namespace {
 constexpr int NT = 256;         // time columns per tile (= UMMA N)
 constexpr int MT = 128;         // output channels per tile (= UMMA M)
 constexpr int KC = 16;          // input channels per staged chunk (one weight stage, two K8 steps)
-constexpr int NB = 2;           // activation (hi/lo) buffers
 constexpr int NRAW = 2;         // raw-input staging buffers filled by cp.async one chunk ahead
 constexpr int EPI_WARPS = 8, PRO_WARPS = 8;
 constexpr int W_WARP = EPI_WARPS + PRO_WARPS, MMA_WARP = W_WARP + 1, MMA_LO_WARP = W_WARP + 2;
@@ -50,14 +55,30 @@ static_assert(NTHREADS * LAUNCH_REGS <= 65536, "launch register budget");
 // the decreases release would block forever.
 static_assert(EPI_WARPS * 32 * EPI_REGS + PRO_WARPS * 32 * PRO_REGS + 4 * 32 * CTL_REGS <= NTHREADS * LAUNCH_REGS,
               "register pool");
-constexpr int W_STAGE_FLOATS = 2 * MT * KC;           // hi + lo
-constexpr int W_STAGE_BYTES = W_STAGE_FLOATS * 4;     // 16384
+// Operand formats (template parameter F16 of the kernel):
+//   tf32 split (F16 = false): hi = tf32(v), lo = v - hi, both stored as f32; per tap and 16 channels 6 MMAs of
+//     kind::tf32 (K8): 2 x hi*hi into Dhi, 2 x (lo*hi + hi*lo) into Dlo.
+//   f16 split (F16 = true): hi = f16(v), lo = f16((v - hi) * 2^11), both with the same 11-bit significand as tf32;
+//     per tap and 16 channels 3 MMAs of kind::f16 (K16): hi*hi into Dhi, lo*hi + hi*lo into Dlo, which is folded in
+//     with the factor 2^-11. Products are exact and accumulate in f32 as before, so the accuracy is that of the
+//     tf32 split at half the tensor time, half the staged bytes and half the weight traffic. Values beyond the f16
+//     range (|v| > 65504) are clamped in the f16 operands and flagged in the status word (kStatusF16Range).
+constexpr float kLoScale = 2048.f;  // 2^11
+constexpr int kStatusF16Range = 0x10000;
+template <bool F16>
+struct Fmt {
+  static constexpr int W_STAGE_BYTES = F16 ? 2 * MT * KC * 2 : 2 * MT * KC * 4;  // hi + lo of [128 co x 16 ci]
+  static constexpr int W_STAGE_FLOATS = W_STAGE_BYTES / 4;
+  static constexpr int NB = F16 ? 3 : 2;  // activation (hi / lo) buffers; the f16 ones are half the size
+  static constexpr int ACT_BYTES_PER_ROW = F16 ? 2 * KC * 2 : 2 * KC * 4;  // hi + lo of one time row, 16 channels
+};
 constexpr int STAGE_PITCH = 33;                       // floats per row of an epilogue transpose tile
 constexpr int STAGE_FLOATS = 32 * STAGE_PITCH;
 constexpr int MAX_HALO = 50;     // (K - 1) * dilation of the widest Kokoro conv (K 11, dilation 5)
-constexpr int MAX_W_STAGES = 6, MIN_W_STAGES = 3;
+constexpr int MAX_W_STAGES = 6, MIN_W_STAGES = 2, PREF_W_STAGES = 3;  // weight ring slots
+constexpr int TAP_GROUP = 4;  // most taps per weight slot: one bulk copy, one wait, MMAs back to back, one release
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
-constexpr uint32_t SLEEP_EPI_NS = 256, SLEEP_PRO_NS = 128, SLEEP_W_NS = 256, SLEEP_MMA_NS = 32;
+constexpr uint32_t SLEEP_EPI_NS = 256, SLEEP_PRO_NS = 128, SLEEP_W_NS = 64, SLEEP_MMA_NS = 32;
 constexpr uint64_t WAIT_LIMIT_NS = 200ull * 1000 * 1000;  // 0.2 s: a healthy wait is tens of microseconds
 constexpr int kMaxSmem = 232448;  // 227 KB per CTA on sm_100
 
@@ -70,13 +91,18 @@ struct TcArgs {
   int padLeft;       // ConvTranspose: 1 = one-sample left reflect pad
   float slope, outScale;
   int rows;        // staged time rows per buffer = NT + (k-1)*dilation
-  int wStages;     // weight ring depth
+  int wStages;     // weight ring depth (slots)
+  int issuers;     // 1: one thread issues all MMAs; 2: one thread for the hi MMAs, one for the lo MMAs
+  int wG;          // taps per weight slot: the k taps of a chunk go in ceil(k / wG) groups of near-equal size
+  int drainN;      // 16-channel chunks accumulated in Dhi between two drains into the running sums
   int numTTiles, numCoBlk;
   int* status;
   long long* prof;  // null, or 16 cycle counters summed over CTAs (see convTcProfile)
   int debug;        // timing experiments of the profiling build only (results are wrong when non-zero)
 };
 
+constexpr int kTraceRoles = 6, kTraceLen = 512;
+__device__ long long gTcTrace[kTraceRoles * kTraceLen];  // profiling build: (clock << 16 | index << 4 | tag) events of CTA 0, per role
 __device__ int gTcStatus = 0;
 __device__ long long gTcProf[16];  // wait / phase cycle sums of one representative warp per role (profiling runs)  // 0 = ok; else (role << 8 | code) of the first bounded wait that gave up
 
@@ -165,6 +191,14 @@ __device__ __forceinline__ void mmaTf32(uint32_t dTmem, uint64_t descA, uint64_t
       "l"(descA), "l"(descB), "r"(idesc), "r"(accum)
       : "memory");
 }
+__device__ __forceinline__ void mmaF16(uint32_t dTmem, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
+      "l"(descA), "l"(descB), "r"(idesc), "r"(accum)
+      : "memory");
+}
 __device__ __forceinline__ void mmaCommit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar))
                : "memory");
@@ -212,6 +246,8 @@ __device__ __forceinline__ uint64_t makeDesc(uint32_t addr, uint32_t lbo, uint32
 // Instruction descriptor: D f32 (bits 4-5 = 1), A and B tf32 (bits 7-9 / 10-12 = 2), both K-major, N >> 3 at bit 17,
 // M >> 4 at bit 24.
 constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(NT >> 3) << 17) | (uint32_t(MT >> 4) << 24);
+// kind::f16 with f16 operands (format 0) and f32 accumulation.
+constexpr uint32_t kIdescF16 = (1u << 4) | (uint32_t(NT >> 3) << 17) | (uint32_t(MT >> 4) << 24);
 
 __device__ __forceinline__ float tf32Round(float v) {
   uint32_t r;
@@ -261,37 +297,19 @@ __device__ __forceinline__ void regDec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-// Position in the flattened (tile, 16-channel chunk, tap) sequence one CTA walks through.
-struct Cursor {
-  int tile, c, kk;
-  int stage, buf;                                   // weight-ring stage, activation buffer
-  uint32_t stagePhase, bufPhase, chunkPar, tilePar;  // parities of the ring passes / chunk count / tile count
-  __device__ __forceinline__ void advance(int k, int nChunks, int stride, int wStages) {
-    if (++stage == wStages) stage = 0, stagePhase ^= 1;
-    if (++kk == k) {
-      kk = 0;
-      chunkPar ^= 1;
-      if (++buf == NB) buf = 0, bufPhase ^= 1;
-      if (++c == nChunks) {
-        c = 0;
-        tile += stride;
-        tilePar ^= 1;
-      }
-    }
-  }
-};
-
 // PARTIAL: Co is not a multiple of 128 (the last output-channel block has rows that do not exist).
 // TS: 0 = conv1d; 6 / 10 = polyphase ConvTranspose1d of that stride (see the comment above convtTcPackKernel).
-template <int ACT, bool PROF, bool PARTIAL, int TS>
+template <int ACT, bool PROF, bool PARTIAL, int TS, bool F16>
 __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
+  constexpr int W_STAGE_BYTES = Fmt<F16>::W_STAGE_BYTES, W_STAGE_FLOATS = Fmt<F16>::W_STAGE_FLOATS;
+  constexpr int NB = Fmt<F16>::NB;
   extern __shared__ __align__(1024) unsigned char smemRaw[];
   const int rows = a.rows;
-  const int actBufFloats = 2 * KC * rows;  // hi + lo
-  float* const sAct = reinterpret_cast<float*>(smemRaw);          // NB buffers of [2 (hi, lo)][KC/4][rows][4]
+  const int actBufFloats = Fmt<F16>::ACT_BYTES_PER_ROW / 4 * rows;  // hi + lo
+  float* const sAct = reinterpret_cast<float*>(smemRaw);          // NB buffers of [2 (hi, lo)][16-byte K chunks][rows]
   float* const sRaw = sAct + NB * actBufFloats;                   // NRAW buffers of [KC][rows] raw input
-  float* const sW = sRaw + NRAW * KC * rows;                      // wStages stages of [2 (hi, lo)][KC/4][MT][4]
-  float* const sStage = sW + a.wStages * W_STAGE_FLOATS;          // EPI_WARPS transpose tiles of [32][STAGE_PITCH]
+  float* const sW = sRaw + NRAW * KC * rows;                      // wStages slots of wG taps of [2 (hi, lo)][16-byte K chunks][MT]
+  float* const sStage = sW + a.wStages * a.wG * W_STAGE_FLOATS;          // EPI_WARPS transpose tiles of [32][STAGE_PITCH]
   float* const sPar = sStage + EPI_WARPS * STAGE_FLOATS;          // [4][ci]: folded prologue constants
   uint64_t* const bFull = reinterpret_cast<uint64_t*>(sPar + 4 * a.ci);
   uint64_t* const bEmpty = bFull + NB;
@@ -307,10 +325,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int numTiles = a.numTTiles * a.numCoBlk;
   const int nChunks16 = a.ci / KC;
+  const int nGroups = (nChunks16 + a.drainN - 1) / a.drainN;  // Dhi drains per tile
+  // tap groups of a chunk: the first tgExtra groups have tgBase + 1 taps, the others tgBase
+  const int nTapGroups = (a.k + a.wG - 1) / a.wG, tgBase = a.k / nTapGroups, tgExtra = a.k % nTapGroups;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NB; ++i) mbarInit(&bFull[i], PRO_WARPS), mbarInit(&bEmpty[i], 2);      // freed by both issuers
-    for (int i = 0; i < MAX_W_STAGES; ++i) mbarInit(&wFull[i], 1), mbarInit(&wEmpty[i], 2);  // freed by both issuers
+    for (int i = 0; i < NB; ++i) mbarInit(&bFull[i], PRO_WARPS), mbarInit(&bEmpty[i], a.issuers);
+    for (int i = 0; i < MAX_W_STAGES; ++i) mbarInit(&wFull[i], 1), mbarInit(&wEmpty[i], a.issuers);
     mbarInit(hiFull, 1), mbarInit(hiEmpty, EPI_WARPS), mbarInit(loFull, 1), mbarInit(loEmpty, EPI_WARPS);
     *abortFlag = 0;
     fenceBarrierInit();
@@ -338,6 +359,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   auto profAdd = [&](int slot, long long v) {
     if (profOn && lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(a.prof + slot), (unsigned long long)v);
   };
+  // profiling build, debug flag 16: event timeline of CTA 0 (roles: 0 hi issuer, 1 lo issuer, 2 epilogue warp 0,
+  // 3 producer warp 0, 4 weight producer)
+  auto trace = [&](int role, int tag, int& n, int idx = 0) {
+    if (profOn && (dbg & 16) && blockIdx.x == 0 && lane == 0 && n < kTraceLen)
+      gTcTrace[role * kTraceLen + n++] = (clock64() << 16) | ((idx & 0xfff) << 4) | tag;
+  };
+  int nTr = 0;
   auto giveUp = [&](int role, int code) {
     if (lane == 0) {
       atomicCAS(a.status, 0, (role << 8) | code);
@@ -351,7 +379,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
     const int q = warp & 3, g = warp >> 2;  // TMEM lane quarter, 128-column half of the tile
     float* tile = sStage + warp * STAGE_FLOATS;
     const uint32_t laneBase = uint32_t(q * 32) << 16;
-    uint32_t chunkIt = 0, tileIt = 0;
+    uint32_t groupIt = 0, tileIt = 0;
     bool dead = false;
     long long wHi = 0, wLo = 0, cPre = 0, cFin = 0;
     const long long tStart = clock64();
@@ -414,13 +442,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       cPre += clock64() - tPre;
       // wait for the chunk's hi chain, add it to the running sums, hand Dhi back
       auto drainChunk = [&]() -> bool {
-        if (!waitT(hiFull, chunkIt & 1, wHi, SLEEP_EPI_NS)) {
+        if (!waitT(hiFull, groupIt & 1, wHi, SLEEP_EPI_NS)) {
           giveUp(1, 1);
           return false;
         }
         tcFenceAfter();
+        if (warp == 0) trace(2, 1, nTr);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
+          if (dbg & 32) break;
           float v[32];
           tmemLoad32(tmemHi + laneBase + g * 128 + b * 32, v);
 #pragma unroll
@@ -432,36 +462,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         tcFenceBefore();
         __syncwarp();
         if (lane == 0) mbarArrive(hiEmpty);
-        ++chunkIt;
+        if (warp == 0) trace(2, 2, nTr);
+        ++groupIt;
         return true;
       };
       int c = 0;
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {  // the first four chunks each carry one residual batch (static register indices)
-        if (!dead && c < nChunks16) {
+      for (int b = 0; b < 4; ++b) {  // the first four drains each carry one residual batch (static register indices)
+        if (!dead && c < nGroups) {
           if (hasRes) fetchResidual(b);
           dead = !drainChunk();
           if (!dead && hasRes) addResidual(b);
           ++c;
-        } else if (!dead && hasRes) {  // fewer chunks than batches (Ci < 64): the rest, unhidden
+        } else if (!dead && hasRes) {  // fewer drains than batches: the rest, unhidden
           fetchResidual(b);
           addResidual(b);
         }
       }
-      for (; !dead && c < nChunks16; ++c) dead = !drainChunk();
+      for (; !dead && c < nGroups; ++c) dead = !drainChunk();
       if (dead) break;
       if (!waitT(loFull, tileIt & 1, wLo, SLEEP_EPI_NS)) {
         giveUp(1, 2);
         break;
       }
       const long long tFin = clock64();
+      if (warp == 0) trace(2, 5, nTr);
       tcFenceAfter();
 #pragma unroll
       for (int b = 0; b < 8; ++b) {
         float v[16];
         tmemLoad16(tmemLo + laneBase + g * 128 + b * 16, v);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) S[b * 16 + j] += v[j];
+        for (int j = 0; j < 16; ++j) S[b * 16 + j] = F16 ? fmaf(v[j], 1.f / kLoScale, S[b * 16 + j]) : S[b * 16 + j] + v[j];
       }
       tcFenceBefore();
       __syncwarp();
@@ -550,6 +582,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         }
       }
       cFin += clock64() - tFin;
+      if (warp == 0) trace(2, 6, nTr);
     }
     if (warp == 0) profAdd(5, wHi), profAdd(6, wLo), profAdd(7, cPre), profAdd(8, cFin), profAdd(9, clock64() - tStart);
   } else if (warp < EPI_WARPS + PRO_WARPS) {
@@ -607,10 +640,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         break;
       }
       const long long tTr = clock64();
+      if (pw == 0) trace(3, 1, nTr);
       const int tt = t / a.numCoBlk;
       const int64_t pos0 = int64_t(tt) * NT - a.padding;
-      float* hi = sAct + buf * actBufFloats + cg * rows * 4;
-      float* lo = hi + KC * rows;
+      // tf32 split: [cg][rows][4 f32]; f16 split: [cg / 2][rows][8 f16], this thread's 4 channels = half of a chunk
+      float* hi = F16 ? sAct + buf * actBufFloats + (cg >> 1) * rows * 4 + (cg & 1) * 2
+                      : sAct + buf * actBufFloats + cg * rows * 4;
+      float* lo = hi + actBufFloats / 2;
       const float* src = sRaw + (it % NRAW) * (KC * rows) + cg * 4 * rows;
       // this thread's four channels: constants in registers for the whole chunk (they were re-read from shared
       // memory per row slot before: 800 of the producers' 1440 shared-memory wavefronts per chunk)
@@ -629,22 +665,44 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         if (r < r1 && !(dbg & 1)) {
           const int64_t pos = pos0 + r;
           const bool ok = pos >= 0 && pos < a.l;
-          float4 h = make_float4(0.f, 0.f, 0.f, 0.f), l = h;
+          float2 v01 = make_float2(0.f, 0.f), v23 = v01;
           if (ok) {
-            const float2 v01 = activate2<ACT>(make_float2(src[r], src[rows + r]), nm[0], pa[0], pb[0], pi[0], a.slope);
-            const float2 v23 =
-                activate2<ACT>(make_float2(src[2 * rows + r], src[3 * rows + r]), nm[1], pa[1], pb[1], pi[1], a.slope);
+            v01 = activate2<ACT>(make_float2(src[r], src[rows + r]), nm[0], pa[0], pb[0], pi[0], a.slope);
+            v23 = activate2<ACT>(make_float2(src[2 * rows + r], src[3 * rows + r]), nm[1], pa[1], pb[1], pi[1], a.slope);
+          }
+          if constexpr (!F16) {
+            float4 h, l;
             h.x = tf32Round(v01.x), h.y = tf32Round(v01.y), h.z = tf32Round(v23.x), h.w = tf32Round(v23.y);
             const float2 l01 = __fadd2_rn(v01, make_float2(-h.x, -h.y)), l23 = __fadd2_rn(v23, make_float2(-h.z, -h.w));
             l = make_float4(l01.x, l01.y, l23.x, l23.y);
+            *reinterpret_cast<float4*>(hi + r * 4) = h;
+            *reinterpret_cast<float4*>(lo + r * 4) = l;
+          } else {
+            // hi = f16(v) (clamped to the f16 range), lo = f16((v - hi) * 2^11); 4 channels = 8 bytes of the row's
+            // 16-byte K chunk (channel groups 2 j and 2 j + 1 share chunk j)
+            const float big = fmaxf(fmaxf(fabsf(v01.x), fabsf(v01.y)), fmaxf(fabsf(v23.x), fabsf(v23.y)));
+            if (big > 65504.f) {
+              atomicOr(a.status, kStatusF16Range);
+              v01.x = fminf(fmaxf(v01.x, -65504.f), 65504.f), v01.y = fminf(fmaxf(v01.y, -65504.f), 65504.f);
+              v23.x = fminf(fmaxf(v23.x, -65504.f), 65504.f), v23.y = fminf(fmaxf(v23.y, -65504.f), 65504.f);
+            }
+            const __half2 h01 = __float22half2_rn(v01), h23 = __float22half2_rn(v23);
+            const float2 sc = make_float2(kLoScale, kLoScale);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            const __half2 l01 = __float22half2_rn(__fmul2_rn(__fadd2_rn(v01, make_float2(-f01.x, -f01.y)), sc));
+            const __half2 l23 = __float22half2_rn(__fmul2_rn(__fadd2_rn(v23, make_float2(-f23.x, -f23.y)), sc));
+            uint2 hw, lw;
+            hw.x = *reinterpret_cast<const uint32_t*>(&h01), hw.y = *reinterpret_cast<const uint32_t*>(&h23);
+            lw.x = *reinterpret_cast<const uint32_t*>(&l01), lw.y = *reinterpret_cast<const uint32_t*>(&l23);
+            *reinterpret_cast<uint2*>(hi + r * 4) = hw;
+            *reinterpret_cast<uint2*>(lo + r * 4) = lw;
           }
-          *reinterpret_cast<float4*>(hi + r * 4) = h;
-          *reinterpret_cast<float4*>(lo + r * 4) = l;
         }
       }
       fenceProxyAsync();  // generic-proxy stores -> visible to the tensor core (async proxy)
       __syncwarp();
       if (lane == 0) mbarArrive(&bFull[buf]);
+      if (pw == 0) trace(3, 2, nTr);
       cTr += clock64() - tTr;
       t = tn, c = cn, ++it;
     }
@@ -654,26 +712,36 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
     regDec<CTL_REGS>();
     if (warp == W_WARP) {
       // ---------------------------------------------------------------- weight producer
-      uint32_t wIt = 0;
+      uint32_t wIt = 0, ws = 0, wPh = 1;  // stages issued, ring slot, parity of the slot's previous release
       bool dead = false;
       long long wW = 0;
       const long long tStart = clock64();
-      const int64_t blocksPerCo = int64_t(nChunks16) * a.k;  // 16 KB blocks per 128-channel output block
+      const int64_t blocksPerCo = int64_t(nChunks16) * a.k;  // one block (hi + lo of one tap) per chunk and tap
+      const int slotFloats = a.wG * W_STAGE_FLOATS;
       for (int t = blockIdx.x; t < numTiles && !dead; t += gridDim.x) {
         const int tt = t / a.numCoBlk, cb = t - tt * a.numCoBlk;
         const float* src = a.wp + int64_t(cb) * blocksPerCo * W_STAGE_FLOATS;
-        for (int64_t blk = 0; blk < blocksPerCo; ++blk, ++wIt) {
-          const uint32_t s = wIt % a.wStages;
-          if (!waitT(&wEmpty[s], ((wIt / a.wStages) & 1) ^ 1, wW, SLEEP_W_NS)) {
-            giveUp(3, 1);
-            dead = true;
-            break;
+        for (int c = 0; c < nChunks16 && !dead; ++c) {
+          for (int gi = 0; gi < nTapGroups; ++gi, ++wIt) {
+            const int n = tgBase + (gi < tgExtra ? 1 : 0);
+            if (!waitT(&wEmpty[ws], wPh, wW, SLEEP_W_NS)) {
+              giveUp(3, 1);
+              dead = true;
+              break;
+            }
+            trace(4, 1, nTr, int(wIt));
+            if (lane == 0) {
+              if (dbg & 64) {
+                mbarArrive(&wFull[ws]);
+              } else {
+                mbarArriveExpectTx(&wFull[ws], n * W_STAGE_BYTES);
+                bulkCopyG2S(sW + ws * slotFloats, src, n * W_STAGE_BYTES, &wFull[ws]);
+              }
+            }
+            __syncwarp();
+            src += n * W_STAGE_FLOATS;
+            if (++ws == uint32_t(a.wStages)) ws = 0, wPh ^= 1;  // wrap counters: a division here cost more than the copy
           }
-          if (lane == 0) {
-            mbarArriveExpectTx(&wFull[s], W_STAGE_BYTES);
-            bulkCopyG2S(sW + s * W_STAGE_FLOATS, src + blk * W_STAGE_FLOATS, W_STAGE_BYTES, &wFull[s]);
-          }
-          __syncwarp();
         }
       }
       profAdd(14, wW), profAdd(15, clock64() - tStart);
@@ -689,75 +757,251 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           }
         }
       }
-    } else if (warp == MMA_WARP || warp == MMA_LO_WARP) {
-      // ---------------------------------------------------------------- MMA issuers
-      // Both walk the same (tile, chunk, tap) sequence. Descriptors are the base descriptor plus small offsets in
-      // 16-byte units (the address field is the low 14 bits) and ring positions are wrap counters, so only a handful
-      // of instructions separate two MMA groups: the tensor pipe streams at full rate only when MMAs arrive back to
-      // back.
+    } else if (a.issuers == 2 && (warp == MMA_WARP || warp == MMA_LO_WARP)) {
+      // ---------------------------------------------------------------- MMA issuers (two-thread variant)
+      // The hi warp sends the hi*hi MMAs into Dhi, the lo warp the lo*hi and hi*lo MMAs into Dlo; both walk the same
+      // (tile, chunk, tap group) sequence, one lane each. A release (tcgen05.commit) holds its thread until the
+      // thread's MMAs have drained; with two issuing threads the other one's MMAs fill that gap.
       const bool isHi = warp == MMA_WARP;
-      const uint32_t rowsUnits = rows;  // one staged time row = 16 bytes = one descriptor address unit
       const uint64_t dA0 = makeDesc(smemAddr(sW), MT * 16, 128);
       const uint64_t dB0 = makeDesc(smemAddr(sAct), rows * 16, 128);
       constexpr uint32_t kStageU = W_STAGE_BYTES >> 4, kLoAU = (W_STAGE_BYTES / 2) >> 4, kKsAU = (2 * MT * 16) >> 4;
-      const uint32_t bufU = uint32_t(actBufFloats * 4) >> 4, loBU = (KC / 4) * rowsUnits, ksBU = 2 * rowsUnits;
-      const int stride = gridDim.x, k = a.k, dil = a.dilation, wStages = a.wStages;
-      Cursor cu{int(blockIdx.x), 0, 0, 0, 0, 0u, 0u, 0u, 0u};
-      bool dead = false;
+      const uint32_t bufU = uint32_t(actBufFloats * 4) >> 4, loBU = bufU >> 1, ksBU = 2 * uint32_t(rows);
+      const uint32_t slotU = uint32_t(a.wG) * kStageU;
+      const int k = a.k, dil = a.dilation, wStages = a.wStages, drainN = a.drainN;
+      int slot = 0, buf = 0, g = 0, tapIt = 0;
+      uint32_t slotPh = 0, bufPh = 0, groupPar = 0, tilePar = 0;
+      bool dead = false, ready = false;  // ready: the next round's weight slot is already known to be full
       long long wBf = 0, wHe = 0, wWf = 0;
       const long long tStart = clock64();
-      while (cu.tile < numTiles) {
-        if (cu.kk == 0) {
-          if (!waitT(&bFull[cu.buf], cu.bufPhase, wBf, SLEEP_MMA_NS)) {
+      for (int tile = blockIdx.x; lane == 0 && tile < numTiles && !dead; tile += gridDim.x) {
+        for (int c = 0; c < nChunks16 && !dead; ++c) {
+          if (!waitT(&bFull[buf], bufPh, wBf, SLEEP_MMA_NS)) {
             giveUp(4, 2);
             dead = true;
-          } else if (isHi) {
-            if (!waitT(hiEmpty, cu.chunkPar ^ 1, wHe, SLEEP_MMA_NS)) {  // Dhi drained by the epilogue warps
+            break;
+          }
+          if (isHi) {
+            if (g == 0 && !waitT(hiEmpty, groupPar ^ 1, wHe, SLEEP_MMA_NS)) {  // Dhi drained by the epilogue warps
               giveUp(4, 1);
               dead = true;
+              break;
             }
-          } else if (cu.c == 0) {
-            if (!waitT(loEmpty, cu.tilePar ^ 1, wHe, SLEEP_MMA_NS)) {  // Dlo of the previous tile folded into the running sums
-              giveUp(4, 4);
+          } else if (c == 0 && !waitT(loEmpty, tilePar ^ 1, wHe, SLEEP_MMA_NS)) {  // Dlo of the previous tile folded
+            giveUp(4, 4);
+            dead = true;
+            break;
+          }
+          const uint64_t dBc = dB0 + uint32_t(buf) * bufU;
+          int kk = 0;
+          for (int gi = 0; gi < nTapGroups; ++gi) {
+            const int gN = tgBase + (gi < tgExtra ? 1 : 0);
+            if (!ready && !waitT(&wFull[slot], slotPh, wWf, SLEEP_MMA_NS)) {
+              giveUp(4, 3);
               dead = true;
+              break;
             }
+            tcFenceAfter();
+            trace(isHi ? 0 : 1, kk == 0 ? 1 : 4, nTr, tapIt);
+            const uint64_t dA = dA0 + uint32_t(slot) * slotU, dB = dBc + uint32_t(kk * dil);
+            const uint32_t acc0 = isHi ? ((kk | g) == 0 ? 0u : 1u) : ((kk | c) == 0 ? 0u : 1u);
+            auto issueTap = [&](int j) {
+              const uint64_t dAh = dA + uint32_t(j) * kStageU, dBh = dB + uint32_t(j * dil);
+              const uint32_t acc = j == 0 ? acc0 : 1u;
+              if (isHi) {
+                if constexpr (F16) {
+                  mmaF16(tmemHi, dAh, dBh, kIdescF16, acc);
+                } else {
+                  mmaTf32(tmemHi, dAh, dBh, kIdesc, acc);
+                  mmaTf32(tmemHi, dAh + kKsAU, dBh + ksBU, kIdesc, 1u);
+                }
+              } else {
+                const uint64_t dAl = dAh + kLoAU, dBl = dBh + loBU;
+                if constexpr (F16) {
+                  mmaF16(tmemLo, dAl, dBh, kIdescF16, acc);
+                  mmaF16(tmemLo, dAh, dBl, kIdescF16, 1u);
+                } else {
+                  mmaTf32(tmemLo, dAl, dBh, kIdesc, acc);
+                  mmaTf32(tmemLo, dAh, dBl, kIdesc, 1u);
+                  mmaTf32(tmemLo, dAl + kKsAU, dBh + ksBU, kIdesc, 1u);
+                  mmaTf32(tmemLo, dAh + kKsAU, dBl + ksBU, kIdesc, 1u);
+                }
+              }
+            };
+            issueTap(0);
+            int nslot = slot + 1;
+            uint32_t nph = slotPh;
+            if (nslot == wStages) nslot = 0, nph ^= 1;
+            ready = mbarTryWait(&wFull[nslot], nph);
+#pragma unroll
+            for (int j = 1; j < TAP_GROUP; ++j)
+              if (j < gN) issueTap(j);
+            mmaCommit(&wEmpty[slot]);  // weight slot free once both issuers' MMAs have read it
+            tapIt += gN;
+            trace(isHi ? 0 : 1, 7, nTr, tapIt);
+            kk += gN;
+            slot = nslot, slotPh = nph;
           }
-        }
-        if (!dead && !waitT(&wFull[cu.stage], cu.stagePhase, wWf, SLEEP_MMA_NS)) {
-          giveUp(4, 3);
-          dead = true;
-        }
-        if (dead) break;
-        tcFenceAfter();
-        if (lane == 0) {
-          const uint64_t dAh = dA0 + uint32_t(cu.stage) * kStageU;
-          const uint64_t dBh = dB0 + uint32_t(cu.buf) * bufU + uint32_t(cu.kk * dil);
+          if (dead) break;
+          const bool lastChunk = c == nChunks16 - 1;
           if (isHi) {
-            mmaTf32(tmemHi, dAh, dBh, kIdesc, cu.kk == 0 ? 0u : 1u);
-            mmaTf32(tmemHi, dAh + kKsAU, dBh + ksBU, kIdesc, 1u);
-            mmaCommit(&wEmpty[cu.stage]);
-            if (cu.kk == k - 1) {
-              mmaCommit(hiFull);  // the chunk's hi chain is complete
-              mmaCommit(&bEmpty[cu.buf]);
-            }
-          } else {
-            const uint64_t dAl = dAh + kLoAU, dBl = dBh + loBU;
-            mmaTf32(tmemLo, dAl, dBh, kIdesc, (cu.c == 0 && cu.kk == 0) ? 0u : 1u);
-            mmaTf32(tmemLo, dAh, dBl, kIdesc, 1u);
-            mmaTf32(tmemLo, dAl + kKsAU, dBh + ksBU, kIdesc, 1u);
-            mmaTf32(tmemLo, dAh + kKsAU, dBl + ksBU, kIdesc, 1u);
-            mmaCommit(&wEmpty[cu.stage]);  // weight stage free once both issuers' MMAs have read it
-            if (cu.kk == k - 1) {
-              mmaCommit(&bEmpty[cu.buf]);  // last tap of the chunk: activation buffer free
-              if (cu.c == nChunks16 - 1) mmaCommit(loFull);
-            }
+            // the hi chain of a drain group (drainN chunks, or what is left of the tile) is complete
+            if (g == drainN - 1 || lastChunk) mmaCommit(hiFull);
+          } else if (lastChunk) {
+            mmaCommit(loFull);
           }
+          mmaCommit(&bEmpty[buf]);  // activation buffer free once both issuers' MMAs have read it
+          trace(isHi ? 0 : 1, 3, nTr);
+          if (++buf == NB) buf = 0, bufPh ^= 1;
+          if (++g == drainN || lastChunk) g = 0, groupPar ^= 1;
         }
-        __syncwarp();
-        cu.advance(k, nChunks16, stride, wStages);
+        tilePar ^= 1;
       }
+      __syncwarp();
       if (isHi) profAdd(0, wBf), profAdd(1, wHe), profAdd(2, wWf), profAdd(4, clock64() - tStart);
       else profAdd(3, wHe);
+    } else if (a.issuers == 1 && warp == MMA_WARP) {
+      // ---------------------------------------------------------------- MMA issuer
+      // One thread issues every MMA: hi*hi into Dhi, lo*hi and hi*lo into Dlo. It walks the (tile, chunk, tap group)
+      // sequence, one tap group per round: a single wait for the group's weight slot, its MMAs back to back, a single
+      // release. Measured on this part: a lone thread streams MMAs at the pipe's rate (128 clocks for M128 N256 K16)
+      // as long as nothing but MMAs is issued; the thread is held while an MMA waits for the pipe, and what it
+      // executes between two MMAs is covered by no more than the one MMA in flight. So the bookkeeping for the next
+      // round (ring counters, a first poll of the next slot's barrier) sits right after the round's first MMA, where
+      // it is free, and only the release and, rarely, a real wait separate two rounds.
+      // Order inside a round: the lo MMAs first, then the hi MMAs, so that the wait for the Dhi drain at the start
+      // of a drain group is covered by the round's own lo MMAs. The first round of a tile goes the other way round,
+      // because there Dhi is handed back before Dlo.
+      const uint64_t dA0 = makeDesc(smemAddr(sW), MT * 16, 128);
+      const uint64_t dB0 = makeDesc(smemAddr(sAct), rows * 16, 128);
+      constexpr uint32_t kStageU = W_STAGE_BYTES >> 4, kLoAU = (W_STAGE_BYTES / 2) >> 4, kKsAU = (2 * MT * 16) >> 4;
+      // activation buffer: hi half then lo half; one MMA spans two 16-byte K chunks (K8 of f32 or K16 of f16);
+      // one staged time row = 16 bytes = one descriptor address unit
+      const uint32_t bufU = uint32_t(actBufFloats * 4) >> 4, loBU = bufU >> 1, ksBU = 2 * uint32_t(rows);
+      const uint32_t slotU = uint32_t(a.wG) * kStageU;
+      const int k = a.k, dil = a.dilation, wStages = a.wStages, drainN = a.drainN;
+      int slot = 0, buf = 0, g = 0, tapIt = 0;
+      uint32_t slotPh = 0, bufPh = 0, groupPar = 0, tilePar = 0;
+      bool dead = false, ready = false;  // ready: the next round's weight slot is already known to be full
+      long long wBf = 0, wHe = 0, wWf = 0, wLe = 0;
+      const long long tStart = clock64();
+      for (int tile = blockIdx.x; lane == 0 && tile < numTiles && !dead; tile += gridDim.x) {
+        for (int c = 0; c < nChunks16 && !dead; ++c) {
+          if (!waitT(&bFull[buf], bufPh, wBf, SLEEP_MMA_NS)) {
+            giveUp(4, 2);
+            dead = true;
+            break;
+          }
+          const uint64_t dBc = dB0 + uint32_t(buf) * bufU;
+          int kk = 0;
+          for (int gi = 0; gi < nTapGroups; ++gi) {
+            const int gN = tgBase + (gi < tgExtra ? 1 : 0);
+            if (!ready && !waitT(&wFull[slot], slotPh, wWf, SLEEP_MMA_NS)) {
+              giveUp(4, 3);
+              dead = true;
+              break;
+            }
+            tcFenceAfter();
+            trace(0, kk == 0 ? 1 : 4, nTr, tapIt);
+            const uint64_t dA = dA0 + uint32_t(slot) * slotU, dB = dBc + uint32_t(kk * dil);
+            const uint32_t accHi = (kk | g) == 0 ? 0u : 1u, accLo = (kk | c) == 0 ? 0u : 1u;
+            const bool needHi = (kk | g) == 0, needLo = (kk | c) == 0;  // Dhi drained / Dlo of the last tile folded
+            auto hiTap = [&](int j) {
+              const uint64_t dAh = dA + uint32_t(j) * kStageU, dBh = dB + uint32_t(j * dil);
+              const uint32_t acc = j == 0 ? accHi : 1u;
+              if constexpr (F16) {
+                mmaF16(tmemHi, dAh, dBh, kIdescF16, acc);
+              } else {
+                mmaTf32(tmemHi, dAh, dBh, kIdesc, acc);
+                mmaTf32(tmemHi, dAh + kKsAU, dBh + ksBU, kIdesc, 1u);
+              }
+            };
+            auto loTap = [&](int j) {
+              const uint64_t dAh = dA + uint32_t(j) * kStageU, dBh = dB + uint32_t(j * dil);
+              const uint64_t dAl = dAh + kLoAU, dBl = dBh + loBU;
+              const uint32_t acc = j == 0 ? accLo : 1u;
+              if constexpr (F16) {
+                mmaF16(tmemLo, dAl, dBh, kIdescF16, acc);
+                mmaF16(tmemLo, dAh, dBl, kIdescF16, 1u);
+              } else {
+                mmaTf32(tmemLo, dAl, dBh, kIdesc, acc);
+                mmaTf32(tmemLo, dAh, dBl, kIdesc, 1u);
+                mmaTf32(tmemLo, dAl + kKsAU, dBh + ksBU, kIdesc, 1u);
+                mmaTf32(tmemLo, dAh + kKsAU, dBl + ksBU, kIdesc, 1u);
+              }
+            };
+            int nslot = slot + 1;
+            uint32_t nph = slotPh;
+            if (needLo) {  // first round of a tile: hi, then lo
+              if (needHi && !waitT(hiEmpty, groupPar ^ 1, wHe, SLEEP_MMA_NS)) {
+                giveUp(4, 1);
+                dead = true;
+                break;
+              }
+              tcFenceAfter();
+              hiTap(0);
+              if (nslot == wStages) nslot = 0, nph ^= 1;
+              ready = mbarTryWait(&wFull[nslot], nph);
+#pragma unroll
+              for (int j = 1; j < TAP_GROUP; ++j)
+                if (j < gN) hiTap(j);
+              if (!waitT(loEmpty, tilePar ^ 1, wLe, SLEEP_MMA_NS)) {
+                giveUp(4, 4);
+                dead = true;
+                break;
+              }
+              tcFenceAfter();
+#pragma unroll
+              for (int j = 0; j < TAP_GROUP; ++j)
+                if (j < gN) loTap(j);
+            } else {
+              loTap(0);
+              if (nslot == wStages) nslot = 0, nph ^= 1;
+              ready = mbarTryWait(&wFull[nslot], nph);
+#pragma unroll
+              for (int j = 1; j < TAP_GROUP; ++j)
+                if (j < gN) loTap(j);
+              if (needHi) {
+                if (!waitT(hiEmpty, groupPar ^ 1, wHe, SLEEP_MMA_NS)) {
+                  giveUp(4, 1);
+                  dead = true;
+                  break;
+                }
+                tcFenceAfter();
+              }
+#pragma unroll
+              for (int j = 0; j < TAP_GROUP; ++j)
+                if (j < gN) hiTap(j);
+            }
+            mmaCommit(&wEmpty[slot]);  // weight slot free once the MMAs have read it
+            tapIt += gN;
+            trace(0, 7, nTr, tapIt);
+            kk += gN;
+            slot = nslot, slotPh = nph;
+          }
+          if (dead) break;
+          const bool lastChunk = c == nChunks16 - 1;
+          // the hi chain of a drain group (drainN chunks, or what is left of the tile) is complete
+          if (g == drainN - 1 || lastChunk) mmaCommit(hiFull);
+          if (lastChunk) mmaCommit(loFull);
+          mmaCommit(&bEmpty[buf]);  // activation buffer free once the MMAs have read it
+          trace(0, 3, nTr);
+          if (++buf == NB) buf = 0, bufPh ^= 1;
+          if (++g == drainN || lastChunk) g = 0, groupPar ^= 1;
+        }
+        tilePar ^= 1;
+      }
+      __syncwarp();
+      profAdd(0, wBf), profAdd(1, wHe), profAdd(2, wWf), profAdd(3, wLe), profAdd(4, clock64() - tStart);
+    } else if (profOn && (dbg & 16) && blockIdx.x == 0) {
+      // spare warp, timeline runs only: records when each weight stage lands (role 5)
+      const int64_t total = int64_t((numTiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1) * nChunks16 * nTapGroups;
+      for (int64_t i = 0; i < total && i < kTraceLen; ++i) {
+        const uint64_t t0 = globalTimerNs();
+        while (!mbarTryWait(&wFull[i % a.wStages], (i / a.wStages) & 1) && globalTimerNs() - t0 < WAIT_LIMIT_NS) {
+        }
+        trace(5, 2, nTr, int(i));
+      }
     }
   }
 
@@ -769,18 +1013,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   }
 }
 
-__global__ void packWeightsKernel(const float* __restrict__ w, float* __restrict__ wp, int co, int ci, int k) {
-  // wp index = ((((cb * nC16 + c16) * k + kk) * 2 + part) * 4 + kc) * 128 * 4 + col * 4 + e
+// One packed element: tf32 split -> f32 hi or lo; f16 split -> f16 hi or lo (lo scaled by 2^11).
+__device__ __forceinline__ float splitTf32(float v, int part) {
+  const float h = tf32Round(v);
+  return part == 0 ? h : v - h;
+}
+__device__ __forceinline__ __half splitF16(float v, int part) {
+  const __half h = __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f));
+  return part == 0 ? h : __float2half_rn((v - __half2float(h)) * kLoScale);
+}
+
+// Conv weight pack: stage (cb, c16, kk) = [hi | lo], each [16-byte K chunk][128 rows][chunk elements]
+// (4 f32 or 8 f16 per chunk). Rows past Co are zero.
+template <bool F16>
+__global__ void packWeightsKernel(const float* __restrict__ w, void* __restrict__ wpOut, int co, int ci, int k) {
+  constexpr int CE = F16 ? 8 : 4, NCH = KC / CE;  // elements per chunk, chunks per 16 channels
   const int nC16 = ci / KC;
-  const int64_t n = int64_t((co + MT - 1) / MT) * nC16 * k * W_STAGE_FLOATS;  // rows past Co are zero
+  const int64_t n = int64_t((co + MT - 1) / MT) * nC16 * k * 2 * NCH * MT * CE;
   for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < n; idx += int64_t(gridDim.x) * blockDim.x) {
     int64_t r = idx;
-    const int e = int(r % 4);
-    r /= 4;
+    const int e = int(r % CE);
+    r /= CE;
     const int col = int(r % MT);
     r /= MT;
-    const int kc = int(r % 4);
-    r /= 4;
+    const int kc = int(r % NCH);
+    r /= NCH;
     const int part = int(r % 2);
     r /= 2;
     const int kk = int(r % k);
@@ -788,9 +1045,9 @@ __global__ void packWeightsKernel(const float* __restrict__ w, float* __restrict
     const int c16 = int(r % nC16);
     const int cb = int(r / nC16);
     const int row = cb * MT + col;
-    const float v = row < co ? w[(int64_t(row) * ci + (c16 * KC + kc * 4 + e)) * k + kk] : 0.f;
-    const float h = tf32Round(v);
-    wp[idx] = part == 0 ? h : v - h;
+    const float v = row < co ? w[(int64_t(row) * ci + (c16 * KC + kc * CE + e)) * k + kk] : 0.f;
+    if constexpr (F16) static_cast<__half*>(wpOut)[idx] = splitF16(v, part);
+    else static_cast<float*>(wpOut)[idx] = splitTf32(v, part);
   }
 }
 
@@ -800,18 +1057,20 @@ __global__ void packWeightsKernel(const float* __restrict__ w, float* __restrict
 // of the three taps of every row is zero). Rows are grouped so that each epilogue warp (32 accumulator rows) owns
 // CQ = 32 / s whole channels with all their phases (row = cl * s + r, the last 32 - CQ s rows are zero), which lets it
 // write each channel's samples j s + r as one contiguous run. One 128-row block therefore holds 4 CQ channels.
-__global__ void convtTcPackKernel(const float* __restrict__ w, float* __restrict__ wp, int ci, int co, int k, int s,
+template <bool F16>
+__global__ void convtTcPackKernel(const float* __restrict__ w, void* __restrict__ wpOut, int ci, int co, int k, int s,
                                   int p) {
+  constexpr int CE = F16 ? 8 : 4, NCH = KC / CE;
   const int nC16 = ci / KC, cq = 32 / s, cpb = 4 * cq;
-  const int64_t n = int64_t((co + cpb - 1) / cpb) * nC16 * 3 * W_STAGE_FLOATS;
+  const int64_t n = int64_t((co + cpb - 1) / cpb) * nC16 * 3 * 2 * NCH * MT * CE;
   for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < n; idx += int64_t(gridDim.x) * blockDim.x) {
     int64_t r = idx;
-    const int e = int(r % 4);
-    r /= 4;
+    const int e = int(r % CE);
+    r /= CE;
     const int row = int(r % MT);
     r /= MT;
-    const int kc = int(r % 4);
-    r /= 4;
+    const int kc = int(r % NCH);
+    r /= NCH;
     const int part = int(r % 2);
     r /= 2;
     const int wt = int(r % 3);
@@ -819,66 +1078,100 @@ __global__ void convtTcPackKernel(const float* __restrict__ w, float* __restrict
     const int c16 = int(r % nC16);
     const int cb = int(r / nC16);
     const int q = row / 32, i = row % 32, cl = i / s, ph = i % s;
-    const int o = (cb * 4 + q) * cq + cl, c = c16 * KC + kc * 4 + e;
+    const int o = (cb * 4 + q) * cq + cl, c = c16 * KC + kc * CE + e;
     const int tt = wt - (ph + p) / s;
     float v = 0.f;
     if (i < cq * s && o < co && (tt == 0 || tt == 1)) v = w[(int64_t(c) * co + o) * k + (ph + p) % s + (1 - tt) * s];
-    const float h = tf32Round(v);
-    wp[idx] = part == 0 ? h : v - h;
+    if constexpr (F16) static_cast<__half*>(wpOut)[idx] = splitF16(v, part);
+    else static_cast<float*>(wpOut)[idx] = splitTf32(v, part);
   }
 }
 
 }  // namespace
 
-// Dynamic shared memory of one CTA: activation buffers, raw staging, weight ring (as deep as fits, MIN..MAX stages),
-// transpose tiles, per-channel parameters, barriers. 0 if the minimum ring does not fit.
-static size_t convTcSmemBytes(int64_t ci, int rows, int* wStages) {
-  const size_t fixed = size_t(EPI_WARPS) * STAGE_FLOATS * 4 + size_t(4) * ci * 4 + 256;
-  const size_t act = size_t(NB) * 2 * KC * rows * 4 + size_t(NRAW) * KC * rows * 4;
-  if (fixed + act + size_t(MIN_W_STAGES) * W_STAGE_BYTES > size_t(kMaxSmem)) return 0;
-  int ws = int((size_t(kMaxSmem) - fixed - act) / W_STAGE_BYTES);
-  if (ws > MAX_W_STAGES) ws = MAX_W_STAGES;
-  if (wStages) *wStages = ws;
-  return fixed + act + size_t(ws) * W_STAGE_BYTES;
+// Dynamic shared memory of one CTA (activation buffers, raw staging, weight ring, transpose tiles, per-channel
+// parameters, barriers) and the weight ring it leaves room for: the largest taps-per-slot (<= TAP_GROUP) that still
+// gives MIN_W_STAGES slots. Returns 0 when even single-tap slots do not fit.
+// Tuning overrides for experiments (environment, read once): LKC_TC_WG = taps per weight slot, LKC_TC_WSTAGES = ring
+// slots (both only honoured when they fit), LKC_TC_ISSUERS = 1 or 2.
+static int tuneKnob(const char* name) {
+  const char* v = std::getenv(name);
+  return v ? std::atoi(v) : 0;
+}
+
+static size_t convTcSmemBytes(int64_t ci, int rows, int k, bool f16, int* wStages, int* wG) {
+  static const int forceG = tuneKnob("LKC_TC_WG"), forceS = tuneKnob("LKC_TC_WSTAGES");
+  const size_t tap = f16 ? Fmt<true>::W_STAGE_BYTES : Fmt<false>::W_STAGE_BYTES;
+  const size_t actRow = f16 ? Fmt<true>::ACT_BYTES_PER_ROW : Fmt<false>::ACT_BYTES_PER_ROW;
+  const size_t fixed = size_t(EPI_WARPS) * STAGE_FLOATS * 4 + size_t(4) * ci * 4 + 512;
+  const size_t act = size_t(f16 ? Fmt<true>::NB : Fmt<false>::NB) * actRow * rows + size_t(NRAW) * KC * rows * 4;
+  if (fixed + act > size_t(kMaxSmem)) return 0;
+  const size_t avail = size_t(kMaxSmem) - fixed - act;
+  // Large groups matter more than a deep ring: the largest group size that leaves PREF_W_STAGES slots wins, else
+  // the deepest ring.
+  int bestG = 0, bestWs = 0;
+  for (int g = (forceG >= 1 && forceG <= TAP_GROUP) ? forceG : TAP_GROUP; g >= 1; --g) {
+    const int groups = (k + g - 1) / g, gmax = (k + groups - 1) / groups;  // near-equal groups, the largest has gmax taps
+    int ws = int(avail / (size_t(gmax) * tap));
+    if (ws > MAX_W_STAGES) ws = MAX_W_STAGES;
+    if (forceS >= MIN_W_STAGES && ws > forceS) ws = forceS;
+    if (ws >= PREF_W_STAGES || (forceG && ws >= MIN_W_STAGES)) {
+      bestG = gmax, bestWs = ws;
+      break;
+    }
+    if (ws >= MIN_W_STAGES && ws > bestWs) bestG = gmax, bestWs = ws;
+  }
+  if (bestG == 0) return 0;
+  if (wStages) *wStages = bestWs;
+  if (wG) *wG = bestG;
+  return fixed + act + size_t(bestWs) * bestG * tap;
 }
 
 bool convTcEligible(const ConvFusedParams& p) {
   if (!(p.state != nullptr && p.x2 == nullptr && p.ci % KC == 0 && p.co >= 1 && p.ci >= KC && p.k >= 1 &&
         p.k <= 64 && (p.k - 1) * p.dilation <= MAX_HALO && p.lo >= 1 && p.padding <= (1 << 20) && p.ci <= 4096))
     return false;
-  return convTcSmemBytes(p.ci, NT + int((p.k - 1) * p.dilation), nullptr) != 0;
+  return convTcSmemBytes(p.ci, NT + int((p.k - 1) * p.dilation), int(p.k), false, nullptr, nullptr) != 0;  // the larger format
 }
 
-int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k) {
-  return ((co + MT - 1) / MT) * (ci / KC) * k * W_STAGE_FLOATS;
+int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k, bool f16) {
+  return ((co + MT - 1) / MT) * (ci / KC) * k * (f16 ? Fmt<true>::W_STAGE_FLOATS : Fmt<false>::W_STAGE_FLOATS);
 }
 
-int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, cudaStream_t s) {
+int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, bool f16, cudaStream_t s) {
   LKC_REQUIRE(ci % KC == 0 && co > 0 && ci > 0 && k >= 1 && k <= 64,
               "conv1d_tc_pack_f32_cuda: needs Ci % 16 == 0, 1 <= K <= 64");
-  const int64_t n = convTcPackFloats(co, ci, k);
+  const int64_t n = convTcPackFloats(co, ci, k, f16) * (f16 ? 2 : 1);  // packed elements
   const int blocks = static_cast<int>(ceilDiv(n, 256) > 4096 ? 4096 : ceilDiv(n, 256));
-  packWeightsKernel<<<blocks, 256, 0, s>>>(w, wp, int(co), int(ci), int(k));
+  if (f16) packWeightsKernel<true><<<blocks, 256, 0, s>>>(w, wp, int(co), int(ci), int(k));
+  else packWeightsKernel<false><<<blocks, 256, 0, s>>>(w, wp, int(co), int(ci), int(k));
   return launched("conv1d_tc_pack_f32_cuda");
 }
 
-template <int ACT, bool PROF, bool PARTIAL, int TS = 0>
-static int launchTc2(const TcArgs& a, int grid, size_t smem, cudaStream_t s) {
+template <int ACT, bool PROF, bool PARTIAL, int TS, bool F16>
+static int launchTc3(const TcArgs& a, int grid, size_t smem, cudaStream_t s) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(convTcKernel<ACT, PROF, PARTIAL, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    cudaError_t e = cudaFuncSetAttribute(convTcKernel<ACT, PROF, PARTIAL, TS, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return failCuda("conv (tensor-core): cudaFuncSetAttribute", e);
     configured[dev] = true;
   }
-  convTcKernel<ACT, PROF, PARTIAL, TS><<<grid, NTHREADS, smem, s>>>(a);
+  convTcKernel<ACT, PROF, PARTIAL, TS, F16><<<grid, NTHREADS, smem, s>>>(a);
   return launched("conv (tensor-core)");
 }
 
+template <int ACT, bool PROF, bool PARTIAL, int TS = 0>
+static int launchTc2(const TcArgs& a, bool f16, int grid, size_t smem, cudaStream_t s) {
+  return f16 ? launchTc3<ACT, PROF, PARTIAL, TS, true>(a, grid, smem, s)
+             : launchTc3<ACT, PROF, PARTIAL, TS, false>(a, grid, smem, s);
+}
+
 template <int ACT, bool PROF>
-static int launchTc(const TcArgs& a, int grid, size_t smem, cudaStream_t s) {
-  return a.co % MT == 0 ? launchTc2<ACT, PROF, false>(a, grid, smem, s) : launchTc2<ACT, PROF, true>(a, grid, smem, s);
+static int launchTc(const TcArgs& a, bool f16, int grid, size_t smem, cudaStream_t s) {
+  return a.co % MT == 0 ? launchTc2<ACT, PROF, false>(a, f16, grid, smem, s)
+                        : launchTc2<ACT, PROF, true>(a, f16, grid, smem, s);
 }
 
 static bool gProfileOn = false;
@@ -895,16 +1188,29 @@ int convTcProfile(int enable, long long* out16) {
     cudaError_t e = cudaMemcpyFromSymbol(out16, gTcProf, sizeof(long long) * 16);
     if (e != cudaSuccess) return failCuda("conv1d_tc_profile", e);
   }
-  static const long long zeros[16] = {};
-  cudaError_t e = cudaMemcpyToSymbol(gTcProf, zeros, sizeof zeros);
+  static const long long zeros[kTraceRoles * kTraceLen] = {};
+  cudaError_t e = cudaMemcpyToSymbol(gTcProf, zeros, sizeof(long long) * 16);
   if (e != cudaSuccess) return failCuda("conv1d_tc_profile", e);
+  return 0;
+}
+
+// Event timeline of CTA 0 of the launches since the last reset (profiling runs with debug flag 16; a launch
+// overwrites the previous one): kTraceRoles rows of kTraceLen entries (clock << 16 | index << 4 | tag), 0 = unused.
+int convTcTrace(long long* out, int reset) {
+  static const long long zeros[kTraceRoles * kTraceLen] = {};
+  cudaError_t e = cudaSuccess;
+  if (out) e = cudaMemcpyFromSymbol(out, gTcTrace, sizeof zeros);
+  if (e == cudaSuccess && reset) e = cudaMemcpyToSymbol(gTcTrace, zeros, sizeof zeros);
+  if (e != cudaSuccess) return failCuda("conv1d_tc_trace", e);
   return 0;
 }
 
 // Per-device constants, looked up once (the first call on a device must not be inside a stream capture), and the
 // launch geometry shared by the conv and ConvTranspose entry points.
-static int finishArgs(TcArgs& a, int* grid, size_t* smem) {
-  *smem = convTcSmemBytes(a.ci, a.rows, &a.wStages);
+static int finishArgs(TcArgs& a, bool f16, int* grid, size_t* smem) {
+  *smem = convTcSmemBytes(a.ci, a.rows, a.k, f16, &a.wStages, &a.wG);
+  static const int forceIssuers = tuneKnob("LKC_TC_ISSUERS");
+  a.issuers = forceIssuers == 2 ? 2 : 1;
   LKC_REQUIRE(*smem != 0, "conv (tensor-core): window too large");
   static int* statusPtr[64] = {};
   static long long* profPtr[64] = {};
@@ -927,12 +1233,21 @@ static int finishArgs(TcArgs& a, int* grid, size_t* smem) {
   a.status = statusPtr[dev];
   a.prof = gProfileOn ? profPtr[dev] : nullptr;
   a.debug = gProfileOn ? gDebugFlags : 0;
+  // Dhi is drained into the f32 running sums after at most kMaxChain chained MMAs (the tensor core truncates when
+  // it accumulates, and the error grows with the length of the chain); with a residual, at least four drains per
+  // tile so that each hides one residual batch.
+  constexpr int kMaxChain = 12;
+  const int perChunk = a.k * (f16 ? 1 : 2), nChunks = a.ci / KC;
+  int n = kMaxChain / perChunk;
+  if (a.residual && n > nChunks / 4) n = nChunks / 4;
+  if (a.debug >> 8) n = a.debug >> 8, a.debug &= 0xff;  // profiling build: forced group length
+  a.drainN = n < 1 ? 1 : n;
   const int tiles = a.numTTiles * a.numCoBlk;
   *grid = tiles < smCount[dev] ? tiles : smCount[dev];
   return 0;
 }
 
-int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
+int convTc(const ConvFusedParams& p, const float* wp, bool f16, cudaStream_t s) {
   TcArgs a;
   a.x = p.x, a.wp = wp, a.bias = p.bias, a.affine = p.affine, a.alpha = p.alpha, a.residual = p.residual;
   a.out = p.out, a.stats = p.stats;
@@ -946,12 +1261,12 @@ int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
   a.numTTiles = int(tTiles), a.numCoBlk = int(coBlk);
   int grid = 0;
   size_t smem = 0;
-  if (int rc = finishArgs(a, &grid, &smem)) return rc;
+  if (int rc = finishArgs(a, f16, &grid, &smem)) return rc;
   const bool prof = a.prof != nullptr;
   switch (p.act) {
-    case Act::None: return prof ? launchTc<0, true>(a, grid, smem, s) : launchTc<0, false>(a, grid, smem, s);
-    case Act::Snake: return prof ? launchTc<1, true>(a, grid, smem, s) : launchTc<1, false>(a, grid, smem, s);
-    case Act::Leaky: return prof ? launchTc<2, true>(a, grid, smem, s) : launchTc<2, false>(a, grid, smem, s);
+    case Act::None: return prof ? launchTc<0, true>(a, f16, grid, smem, s) : launchTc<0, false>(a, f16, grid, smem, s);
+    case Act::Snake: return prof ? launchTc<1, true>(a, f16, grid, smem, s) : launchTc<1, false>(a, f16, grid, smem, s);
+    case Act::Leaky: return prof ? launchTc<2, true>(a, f16, grid, smem, s) : launchTc<2, false>(a, f16, grid, smem, s);
   }
   return fail("conv (tensor-core): bad activation");
 }
@@ -960,25 +1275,26 @@ int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s) {
 
 bool convtTcEligible(int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding) {
   return (stride == 6 || stride == 10) && k == 2 * stride && 2 * padding == stride && ci % KC == 0 && ci >= KC &&
-         ci <= 4096 && co >= 1 && convTcSmemBytes(ci, NT + 2, nullptr) != 0;
+         ci <= 4096 && co >= 1 && convTcSmemBytes(ci, NT + 2, 3, false, nullptr, nullptr) != 0;
 }
 
-int64_t convtTcPackFloats(int64_t ci, int64_t co, int64_t stride) {
+int64_t convtTcPackFloats(int64_t ci, int64_t co, int64_t stride, bool f16) {
   const int64_t cpb = 4 * (32 / stride);
-  return ceilDiv(co, cpb) * (ci / KC) * 3 * W_STAGE_FLOATS;
+  return ceilDiv(co, cpb) * (ci / KC) * 3 * (f16 ? Fmt<true>::W_STAGE_FLOATS : Fmt<false>::W_STAGE_FLOATS);
 }
 
 int convtTcPack(const float* w, float* wp, int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding,
-                cudaStream_t s) {
+                bool f16, cudaStream_t s) {
   LKC_REQUIRE(convtTcEligible(ci, co, k, stride, padding),
               "convt_tc_pack_f32_cuda: needs stride 6 or 10, K = 2 stride, 2 padding = stride, Ci % 16 == 0");
-  const int64_t n = convtTcPackFloats(ci, co, stride);
+  const int64_t n = convtTcPackFloats(ci, co, stride, f16) * (f16 ? 2 : 1);
   const int blocks = static_cast<int>(ceilDiv(n, 256) > 4096 ? 4096 : ceilDiv(n, 256));
-  convtTcPackKernel<<<blocks, 256, 0, s>>>(w, wp, int(ci), int(co), int(k), int(stride), int(padding));
+  if (f16) convtTcPackKernel<true><<<blocks, 256, 0, s>>>(w, wp, int(ci), int(co), int(k), int(stride), int(padding));
+  else convtTcPackKernel<false><<<blocks, 256, 0, s>>>(w, wp, int(ci), int(co), int(k), int(stride), int(padding));
   return launched("convt_tc_pack_f32_cuda");
 }
 
-int convtTc(const ConvtParams& p, const float* wp, cudaStream_t s) {
+int convtTc(const ConvtParams& p, const float* wp, bool f16, cudaStream_t s) {
   TcArgs a;
   a.x = p.x, a.wp = wp, a.bias = p.bias, a.affine = nullptr, a.alpha = nullptr, a.residual = p.res;
   a.out = p.out, a.stats = nullptr;
@@ -991,11 +1307,11 @@ int convtTc(const ConvtParams& p, const float* wp, cudaStream_t s) {
   a.numTTiles = int(tTiles), a.numCoBlk = int(coBlk);
   int grid = 0;
   size_t smem = 0;
-  if (int rc = finishArgs(a, &grid, &smem)) return rc;
+  if (int rc = finishArgs(a, f16, &grid, &smem)) return rc;
   const bool prof = a.prof != nullptr;
   if (p.stride == 6)
-    return prof ? launchTc2<2, true, false, 6>(a, grid, smem, s) : launchTc2<2, false, false, 6>(a, grid, smem, s);
-  return prof ? launchTc2<2, true, false, 10>(a, grid, smem, s) : launchTc2<2, false, false, 10>(a, grid, smem, s);
+    return prof ? launchTc2<2, true, false, 6>(a, f16, grid, smem, s) : launchTc2<2, false, false, 6>(a, f16, grid, smem, s);
+  return prof ? launchTc2<2, true, false, 10>(a, f16, grid, smem, s) : launchTc2<2, false, false, 10>(a, f16, grid, smem, s);
 }
 
 int convTcStatus(int* out, bool reset) {

@@ -231,7 +231,7 @@ int runPoly(const LkcArgs* a, void* stream, bool mean3) {
                 "conv_transpose1d_poly: the prepared state does not match the weight shape");
     if (convtTcEligible(ci, co, taps * s, s, pad)) {
       ConvtParams cp{p.x, p.bias, p.res, p.out, ci, l, co, s, padLeft, p.slope};
-      return convtTc(cp, cs->wp, st);
+      return convtTc(cp, cs->wp, cs->f16, st);
     }
   }
   if (taps == 2 && ceilDiv(co, BCO) <= 65535) {

@@ -67,6 +67,7 @@ struct ConvState {
   const float* wp;  // packed weights (convTcPack / convtTcPack)
   int64_t co, ci, k;
   int64_t stride;  // 0 = conv1d pack; otherwise the ConvTranspose1d stride the pack was made for
+  bool f16;        // operand format of the pack: f16 hi/lo split (true) or tf32 hi/lo split (false)
 };
 // Operands of the polyphase ConvTranspose1d (convt.cu decodes them, conv_tc.cu can run them).
 struct ConvtParams {
@@ -76,16 +77,18 @@ struct ConvtParams {
   float slope;
 };
 bool convtTcEligible(int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding);
-int64_t convtTcPackFloats(int64_t ci, int64_t co, int64_t stride);
-int convtTcPack(const float* w, float* wp, int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding,
+int64_t convtTcPackFloats(int64_t ci, int64_t co, int64_t stride, bool f16);
+int convtTcPack(const float* w, float* wp, int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding, bool f16,
                 cudaStream_t s);
-int convtTc(const ConvtParams& p, const float* wp, cudaStream_t s);
+int convtTc(const ConvtParams& p, const float* wp, bool f16, cudaStream_t s);
 bool convPathForcedSimt();
+bool convPackF16();  // operand format new packs are made in (lkc_set_conv_path)
 bool convTcEligible(const ConvFusedParams& p);
-int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k);
-int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, cudaStream_t s);
-int convTc(const ConvFusedParams& p, const float* wp, cudaStream_t s);
+int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k, bool f16);
+int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, bool f16, cudaStream_t s);
+int convTc(const ConvFusedParams& p, const float* wp, bool f16, cudaStream_t s);
 int convTcStatus(int* out, bool reset);
+int convTcTrace(long long* out, int reset);
 int convTcProfile(int enable, long long* out16);
 
 }  // namespace lkc

@@ -233,7 +233,9 @@ class Generator:
 
     def synthesize(self, x_host, har_host, s_host, audio_host=None):
         """End-to-end call with HOST buffers (pinned torch tensors for async copies): host -> device copies, one
-        graph replay, device -> host copy of the waveform. Returns the host waveform tensor."""
+        graph replay, device -> host copy of the waveform. Returns the host waveform tensor. Raises if the tensor-core
+        kernels reported a problem during the call (a bounded wait that gave up, or an activation beyond the f16
+        range of the split operands, which is clamped and would make the waveform wrong)."""
         t = int(x_host.shape[1])
         b = self.capture(t)
         b["x"].copy_(x_host, non_blocking=True)
@@ -244,4 +246,8 @@ class Generator:
             audio_host = torch.empty(b["audio"].shape, dtype=torch.float32, pin_memory=True)
         audio_host.copy_(b["audio"], non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
+        status = ops.conv_tc_status()
+        if status != 0:
+            raise RuntimeError(f"tensor-core conv kernels reported status {status:#x} "
+                               "(0x10000 = activation beyond the f16 range; else role << 8 | wait that gave up)")
         return audio_host

@@ -419,9 +419,13 @@ def conv_tc_profile(enable: bool) -> dict:
 
 
 def set_conv_path(mode: str) -> None:
-    """"auto" (tensor cores when a prepared state is passed and the shape is eligible) or "simt" (CUDA cores only)."""
-    check(mode in ("auto", "simt"), "mode must be 'auto' or 'simt'")
-    if _lib.lib().lkc_set_conv_path(0 if mode == "auto" else 1) != 0:
+    """Convolution path: "auto" = tensor cores when a prepared state is passed and the shape is eligible, operands
+    split into f16 hi/lo halves; "tf32" = the same with tf32 hi/lo halves; "simt" = CUDA cores only. The operand
+    format is fixed when a state is prepared, so states made under "auto" keep the f16 split after a switch to
+    "tf32" and the other way round."""
+    modes = {"auto": 0, "simt": 1, "tf32": 2}
+    check(mode in modes, "mode must be 'auto', 'simt' or 'tf32'")
+    if _lib.lib().lkc_set_conv_path(modes[mode]) != 0:
         raise _lib.LkcError(_lib.last_error())
 
 

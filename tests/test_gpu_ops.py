@@ -111,6 +111,74 @@ def test_conv1d_fused(cuda, ci, co, l, k, d, variant):
         assert rel_l2(out, o2.cpu().numpy()) <= REL_L2
 
 
+TF32_CASES = [(128, 128, 1201, 3, 1), (128, 128, 1201, 7, 3), (256, 256, 640, 11, 5), (128, 128, 257, 7, 1),
+              (16, 128, 700, 7, 3), (128, 22, 5000, 7, 1), (128, 128, 19201, 11, 3)]
+
+
+@pytest.mark.parametrize("ci,co,l,k,d", TF32_CASES)
+@pytest.mark.parametrize("variant", ["snake_res", "affine"])
+def test_conv1d_tensor_core_tf32_split(cuda, ci, co, l, k, d, variant):
+    """The second operand format of the tensor-core kernel (tf32 hi/lo halves, chosen when the state is prepared)
+    is held to the same bars as the default f16 hi/lo split."""
+    from lokinfer_b200 import ops
+    x, w, b, affine, alpha, res = synth.conv_case(ci, co, l, k, ci * 31 + l + k)
+    pad = d * (k - 1) // 2
+    dx, dw, db, daf, dal, dres = dev(cuda, x, w, b, affine, alpha, res)
+    ops.set_conv_path("tf32")
+    try:
+        state = ops.conv1d_prepare_f32_cuda(dw)
+    finally:
+        ops.set_conv_path("auto")
+    assert state is not None
+    if variant == "snake_res":
+        out, stats = ops.conv1d_snake_f32_cuda(dx, dw, db, daf, dal, residual=dres, padding=pad, dilation=d,
+                                               state=state)
+    else:
+        out, stats = ops.conv1d_affine_f32_cuda(dx, dw, db, daf, padding=pad, dilation=d, state=state)
+    out, stats = out.cpu().numpy(), stats.cpu().numpy()
+
+    def oracle(dt):
+        a = [O.T(v, dt) for v in (x, w, b, affine, alpha, res)]
+        if variant == "snake_res":
+            return O.conv1d_fused(a[0], a[1], a[2], a[3], "snake", alpha=a[4], residual=a[5], padding=pad,
+                                  dilation=d)[0].numpy()
+        return O.conv1d_fused(a[0], a[1], a[2], a[3], "none", padding=pad, dilation=d)[0].numpy()
+
+    ref32, ref64 = oracle(torch.float32), oracle(torch.float64)
+    assert rel_l2(out, ref32) <= REL_L2
+    assert rel_l2(out, ref64) <= 2 * rel_l2(ref32, ref64) + 2e-7
+    check_stats(stats, out)
+    assert ops.conv_tc_status() == 0
+
+
+def test_conv1d_f16_split_reports_values_beyond_f16_range(cuda):
+    """Activations beyond the f16 range (65504) are clamped by the f16 operand split and reported in the status
+    word (bit 0x10000); the tf32 split and the CUDA-core kernel take the same input without a report."""
+    from lokinfer_b200 import ops
+    ci = co = 128
+    l, k, d = 600, 3, 1
+    x, w, b, affine, alpha, res = synth.conv_case(ci, co, l, k, 5)
+    x = x.copy()
+    x[3, 100] = 3.0e5
+    affine = np.stack([np.zeros(ci), np.ones(ci), np.zeros(ci)]).astype(np.float32)  # identity prologue
+    dx, dw, db, daf = dev(cuda, x, w, b, affine)
+    st = ops.conv1d_prepare_f32_cuda(dw)
+    assert ops.conv_tc_status() == 0
+    ops.conv1d_affine_f32_cuda(dx, dw, db, daf, padding=1, dilation=1, state=st)
+    assert ops.conv_tc_status() == 0x10000      # reads and clears
+    assert ops.conv_tc_status() == 0
+    ops.set_conv_path("tf32")
+    try:
+        st32 = ops.conv1d_prepare_f32_cuda(dw)
+    finally:
+        ops.set_conv_path("auto")
+    out, _ = ops.conv1d_affine_f32_cuda(dx, dw, db, daf, padding=1, dilation=1, state=st32)
+    assert ops.conv_tc_status() == 0
+    a = [O.T(v) for v in (x, w, b, affine)]
+    ref = O.conv1d_fused(a[0], a[1], a[2], a[3], "none", padding=1, dilation=1)[0].numpy()
+    assert rel_l2(out.cpu().numpy(), ref) <= REL_L2
+
+
 def test_conv1d_fused_golden(cuda):
     from lokinfer_b200 import ops
     import importlib.util, pathlib
