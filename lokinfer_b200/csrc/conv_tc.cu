@@ -49,7 +49,7 @@ constexpr int EPI_WARPS = 8, PRO_WARPS = 8;
 constexpr int W_WARP = EPI_WARPS + PRO_WARPS, MMA_WARP = W_WARP + 1, MMA_LO_WARP = W_WARP + 2;
 constexpr int NWARPS = EPI_WARPS + PRO_WARPS + 4;  // one idle warp completes the fifth warpgroup
 constexpr int NTHREADS = NWARPS * 32;  // 640
-constexpr int LAUNCH_REGS = 96, EPI_REGS = 168, PRO_REGS = 48, CTL_REGS = 40;
+constexpr int LAUNCH_REGS = 96, EPI_REGS = 160, PRO_REGS = 56, CTL_REGS = 40;
 static_assert(NTHREADS * LAUNCH_REGS <= 65536, "launch register budget");
 // setmaxnreg moves registers inside the CTA's own launch allocation (NTHREADS * LAUNCH_REGS); an increase beyond what
 // the decreases release would block forever.
@@ -218,6 +218,18 @@ __device__ __forceinline__ void tmemLoad16(uint32_t taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+
+// The same load without the wait: several may be in flight before one tmemWaitLoads().
+__device__ __forceinline__ void tmemLoad16Async(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmemWaitLoads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmemLoad32(uint32_t taddr, float* v) {
   uint32_t r[32];
@@ -410,16 +422,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         if constexpr (TS == 0) {
           const bool ok = b * 32 + lane < nValid;
           const float* rp = a.residual + int64_t(coBase) * a.outPitch + tChunk + b * 32 + lane;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (ok && (!PARTIAL || i < coValid)) cpAsync4(&tile[i * STAGE_PITCH + lane], rp + int64_t(i) * a.outPitch);
-            else tile[i * STAGE_PITCH + lane] = 0.f;
-          }
+          float* tp = tile + lane;
+          const int rowsOk = ok ? (PARTIAL ? (coValid < 0 ? 0 : coValid) : 32) : 0;  // rows this lane copies
+          int i = 0;
+#pragma unroll 8
+          for (; i < rowsOk; ++i, tp += STAGE_PITCH, rp += a.outPitch) cpAsync4(tp, rp);
+          for (; i < 32; ++i, tp += STAGE_PITCH) *tp = 0.f;
         } else {
           // channel cl: the 32 * TS output samples u = (tChunk + 32 b) * TS + idx are contiguous in memory; copy
           // i = cl * TS + f moves idx = 32 f + lane, which is column idx / TS of phase idx % TS
           const int64_t uEnd = a.lo * TS, u0 = (tChunk + b * 32) * TS;
-#pragma unroll
+#pragma unroll 2
           for (int i = 0; i < ROWS; ++i) {
             const int cl = i / TS, idx = (i % TS) * 32 + lane;
             float* dst = &tile[(cl * TS + idx % TS) * STAGE_PITCH + idx / TS];
@@ -466,20 +479,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         ++groupIt;
         return true;
       };
-      int c = 0;
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {  // the first four drains each carry one residual batch (static register indices)
-        if (!dead && c < nGroups) {
-          if (hasRes) fetchResidual(b);
-          dead = !drainChunk();
-          if (!dead && hasRes) addResidual(b);
-          ++c;
-        } else if (!dead && hasRes) {  // fewer drains than batches: the rest, unhidden
-          fetchResidual(b);
-          addResidual(b);
+      // The first four drains each carry one residual batch; with fewer drains than batches the rest follow unhidden.
+      // One copy of the fetch and of the drain in the code (this kernel is far larger than the instruction cache,
+      // and straight-line code that runs once per tile is fetched at a fraction of the issue rate); only the add
+      // needs static register indices.
+      const int nSteps = hasRes && nGroups < 4 ? 4 : nGroups;
+#pragma unroll 1
+      for (int c = 0; c < nSteps && !dead; ++c) {
+        const bool doRes = hasRes && c < 4;
+        if (doRes) fetchResidual(c);
+        if (c < nGroups) dead = !drainChunk();
+        if (doRes && !dead) {
+          switch (c) {
+            case 0: addResidual(0); break;
+            case 1: addResidual(1); break;
+            case 2: addResidual(2); break;
+            default: addResidual(3); break;
+          }
         }
       }
-      for (; !dead && c < nGroups; ++c) dead = !drainChunk();
       if (dead) break;
       if (!waitT(loFull, tileIt & 1, wLo, SLEEP_EPI_NS)) {
         giveUp(1, 2);
@@ -489,49 +507,69 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       if (warp == 0) trace(2, 5, nTr);
       tcFenceAfter();
 #pragma unroll
-      for (int b = 0; b < 8; ++b) {
-        float v[16];
-        tmemLoad16(tmemLo + laneBase + g * 128 + b * 16, v);
+      for (int b = 0; b < 4; ++b) {  // two 16-column loads in flight per wait
+        uint32_t va[16], vb[16];
+        tmemLoad16Async(tmemLo + laneBase + g * 128 + b * 32, va);
+        tmemLoad16Async(tmemLo + laneBase + g * 128 + b * 32 + 16, vb);
+        tmemWaitLoads();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) S[b * 16 + j] = F16 ? fmaf(v[j], 1.f / kLoScale, S[b * 16 + j]) : S[b * 16 + j] + v[j];
+        for (int j = 0; j < 16; ++j) {
+          const float x = __uint_as_float(va[j]), y = __uint_as_float(vb[j]);
+          S[b * 32 + j] = F16 ? fmaf(x, 1.f / kLoScale, S[b * 32 + j]) : S[b * 32 + j] + x;
+          S[b * 32 + 16 + j] = F16 ? fmaf(y, 1.f / kLoScale, S[b * 32 + 16 + j]) : S[b * 32 + 16 + j] + y;
+        }
       }
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) mbarArrive(loEmpty);
+      if (warp == 0) trace(2, 8, nTr);
       if (a.residual && a.outScale != 1.f) {
 #pragma unroll
         for (int j = 0; j < 128; ++j) S[j] *= a.outScale;
       }
 
       if constexpr (TS == 0) {
+        // Per 32-column batch: the registers go to the warp's tile once (the only straight-line part), then rolled
+        // loops over the tile do the statistics (own row: lanes along channels) and the stores (transposed: lanes
+        // along time). Rolled loops stay in the instruction cache; the unrolled form of this phase (1100
+        // instructions run once per tile) ran at about 20 clocks per instruction.
         float pMean[4], pM2[4];
+        const int rowsValid = PARTIAL ? (coValid < 0 ? 0 : coValid) : 32;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           const int nb = nValid - b * 32 <= 0 ? 0 : (nValid - b * 32 < 32 ? nValid - b * 32 : 32);  // valid columns
-          const int64_t tb = tChunk + b * 32;
-          // partial statistics of the valid columns (two passes in registers)
-          float sum = 0.f;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) sum += j < nb ? S[b * 32 + j] : 0.f;
-          const float m = nb > 0 ? sum / float(nb) : 0.f;
-          float m2 = 0.f;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float d = j < nb ? S[b * 32 + j] - m : 0.f;
-            m2 = fmaf(d, d, m2);
-          }
-          pMean[b] = m, pM2[b] = m2;
-          // transpose and store with lanes along time
 #pragma unroll
           for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
           __syncwarp();
+          // partial statistics of the valid columns of this lane's channel (two passes)
+          const float* row = tile + lane * STAGE_PITCH;
+          float s0 = 0.f, s1 = 0.f;
+          int j = 0;
+#pragma unroll 2
+          for (; j + 1 < nb; j += 2) s0 += row[j], s1 += row[j + 1];
+          if (j < nb) s0 += row[j];
+          const float m = nb > 0 ? (s0 + s1) / float(nb) : 0.f;
+          float q0 = 0.f, q1 = 0.f;
+          j = 0;
+#pragma unroll 2
+          for (; j + 1 < nb; j += 2) {
+            const float d0 = row[j] - m, d1 = row[j + 1] - m;
+            q0 = fmaf(d0, d0, q0), q1 = fmaf(d1, d1, q1);
+          }
+          if (j < nb) {
+            const float d = row[j] - m;
+            q0 = fmaf(d, d, q0);
+          }
+          pMean[b] = m, pM2[b] = q0 + q1;
+          // store with lanes along time
           if (lane < nb && !(dbg & 8)) {
-            float* op = a.out + int64_t(coBase) * a.outPitch + tb + lane;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (!PARTIAL || i < coValid) op[int64_t(i) * a.outPitch] = tile[i * STAGE_PITCH + lane];
+            float* op = a.out + int64_t(coBase) * a.outPitch + tChunk + b * 32 + lane;
+            const float* col = tile + lane;
+#pragma unroll 4
+            for (int i = 0; i < rowsValid; ++i) op[int64_t(i) * a.outPitch] = col[i * STAGE_PITCH];
           }
           __syncwarp();
+          if (warp == 0) trace(2, 10, nTr, b);
         }
         if (a.stats && nValid > 0 && (!PARTIAL || co < a.co)) {
           // exact combine of the four 32-column partials: mean = sum n_b m_b / n, M2 = sum M2_b + sum n_b (m_b - mean)^2
@@ -550,8 +588,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
             m2 += pM2[b] + float(nb) * d * d;
           }
           float* st = a.stats + (int64_t(co) * a.nchunks + tChunk / 128) * 2;
-          st[0] = mean;
-          st[1] = m2;
+          if ((reinterpret_cast<uintptr_t>(a.stats) & 7) == 0) *reinterpret_cast<float2*>(st) = make_float2(mean, m2);
+          else st[0] = mean, st[1] = m2;
         }
       } else {
         // ConvTranspose: interleave the TS phases of each channel back into contiguous output samples
@@ -659,7 +697,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         pb[h] = make_float2(par[2 * a.ci], par[2 * a.ci + 1]);
         pi[h] = make_float2(par[3 * a.ci], par[3 * a.ci + 1]);
       }
-#pragma unroll 1
+#pragma unroll 2
       for (int sl = 0; sl < SLOTS; ++sl) {
         const int r = r0 + sl * 32 + lane;
         if (r < r1 && !(dbg & 1)) {
@@ -768,7 +806,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       constexpr uint32_t kStageU = W_STAGE_BYTES >> 4, kLoAU = (W_STAGE_BYTES / 2) >> 4, kKsAU = (2 * MT * 16) >> 4;
       const uint32_t bufU = uint32_t(actBufFloats * 4) >> 4, loBU = bufU >> 1, ksBU = 2 * uint32_t(rows);
       const uint32_t slotU = uint32_t(a.wG) * kStageU;
-      const int k = a.k, dil = a.dilation, wStages = a.wStages, drainN = a.drainN;
+      const int dil = a.dilation, wStages = a.wStages, drainN = a.drainN;
       int slot = 0, buf = 0, g = 0, tapIt = 0;
       uint32_t slotPh = 0, bufPh = 0, groupPar = 0, tilePar = 0;
       bool dead = false, ready = false;  // ready: the next round's weight slot is already known to be full
@@ -879,7 +917,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       // one staged time row = 16 bytes = one descriptor address unit
       const uint32_t bufU = uint32_t(actBufFloats * 4) >> 4, loBU = bufU >> 1, ksBU = 2 * uint32_t(rows);
       const uint32_t slotU = uint32_t(a.wG) * kStageU;
-      const int k = a.k, dil = a.dilation, wStages = a.wStages, drainN = a.drainN;
+      const int dil = a.dilation, wStages = a.wStages, drainN = a.drainN;
       int slot = 0, buf = 0, g = 0, tapIt = 0;
       uint32_t slotPh = 0, bufPh = 0, groupPar = 0, tilePar = 0;
       bool dead = false, ready = false;  // ready: the next round's weight slot is already known to be full
@@ -1093,7 +1131,7 @@ __global__ void convtTcPackKernel(const float* __restrict__ w, void* __restrict_
 // parameters, barriers) and the weight ring it leaves room for: the largest taps-per-slot (<= TAP_GROUP) that still
 // gives MIN_W_STAGES slots. Returns 0 when even single-tap slots do not fit.
 // Tuning overrides for experiments (environment, read once): LKC_TC_WG = taps per weight slot, LKC_TC_WSTAGES = ring
-// slots (both only honoured when they fit), LKC_TC_ISSUERS = 1 or 2.
+// slots (both only honoured when they fit), LKC_TC_ISSUERS = 1 or 2, LKC_TC_GRID = fewer CTAs than SMs.
 static int tuneKnob(const char* name) {
   const char* v = std::getenv(name);
   return v ? std::atoi(v) : 0;
@@ -1244,6 +1282,8 @@ static int finishArgs(TcArgs& a, bool f16, int* grid, size_t* smem) {
   a.drainN = n < 1 ? 1 : n;
   const int tiles = a.numTTiles * a.numCoBlk;
   *grid = tiles < smCount[dev] ? tiles : smCount[dev];
+  static const int forceGrid = tuneKnob("LKC_TC_GRID");
+  if (forceGrid > 0 && forceGrid < *grid) *grid = forceGrid;
   return 0;
 }
 
