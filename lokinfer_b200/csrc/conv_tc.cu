@@ -600,7 +600,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
           __syncwarp();
-#pragma unroll
+#pragma unroll 2
           for (int i = 0; i < ROWS; ++i) {
             const int cl = i / TS, idx = (i % TS) * 32 + lane;
             const int64_t u = u0 + idx;
@@ -642,50 +642,55 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
     asm volatile("bar.sync 1, %0;" ::"n"(PRO_WARPS * 32) : "memory");  // producer warps only
 
     // cp.async of this thread's part of the raw window of (tile t, chunk c) into staging buffer rb
-    auto issueCopies = [&](int t, int c, int rb) {
-      const int tt = t / a.numCoBlk;
-      const int64_t pos0 = int64_t(tt) * NT - a.padding;  // input position of row 0
-      const float* xc = a.x + int64_t(c * KC + cg * 4) * a.l;
-      float* dst = sRaw + rb * (KC * rows) + cg * 4 * rows;
+    // cp.async of this thread's part of the raw window of chunk c of the tile whose window starts at input position
+    // posT (= tile column * NT - padding) into staging buffer rb. Pointer increments only: this runs once per chunk
+    // on every producer thread.
+    auto issueCopies = [&](int64_t posT, int c, int rb) {
+      const float* xc = a.x + int64_t(c * KC + cg * 4) * a.l + posT + r0 + lane;
+      float* dst = sRaw + rb * (KC * rows) + cg * 4 * rows + r0 + lane;
+      int64_t pos = posT + r0 + lane;
+      int r = r0 + lane;
 #pragma unroll
-      for (int sl = 0; sl < SLOTS; ++sl) {
-        const int r = r0 + sl * 32 + lane;
-        const int64_t pos = pos0 + r;
+      for (int sl = 0; sl < SLOTS; ++sl, r += 32, pos += 32, xc += 32, dst += 32) {
         if (r < r1 && pos >= 0 && pos < a.l) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) cpAsync4(dst + e * rows + r, xc + int64_t(e) * a.l + pos);
+          cpAsync4(dst, xc);
+          cpAsync4(dst + rows, xc + a.l);
+          cpAsync4(dst + 2 * rows, xc + 2 * a.l);
+          cpAsync4(dst + 3 * rows, xc + 3 * a.l);
         }
       }
     };
 
     int t = blockIdx.x, c = 0;
-    uint32_t it = 0;
+    uint32_t it = 0, buf = 0, bufPar = 1, rawBuf = 0;  // chunk count; activation buffer + parity of its last release; raw buffer
     long long wB = 0, wCp = 0, cTr = 0;
     const long long tStart = clock64();
-    if (t < numTiles) issueCopies(t, c, 0);
+    int64_t pos0 = int64_t(t / a.numCoBlk) * NT - a.padding;  // input position of row 0 of the current tile's window
+    if (t < numTiles) issueCopies(pos0, c, 0);
     cpAsyncCommit();
     while (t < numTiles) {
       int tn = t, cn = c + 1;
-      if (cn == nChunks16) cn = 0, tn = t + gridDim.x;
-      if (tn < numTiles && !(dbg & 2)) issueCopies(tn, cn, (it + 1) % NRAW);
+      int64_t posN = pos0;
+      if (cn == nChunks16) {
+        cn = 0, tn = t + gridDim.x;
+        posN = int64_t(tn / a.numCoBlk) * NT - a.padding;
+      }
+      if (tn < numTiles && !(dbg & 2)) issueCopies(posN, cn, rawBuf ^ 1);
       cpAsyncCommit();
       const long long tCp = clock64();
       cpAsyncWait<1>();  // this chunk's copies (the older group) have landed; the next chunk's stay in flight
       wCp += clock64() - tCp;
-      const uint32_t buf = it % NB;
-      if (!waitT(&bEmpty[buf], ((it / NB) & 1) ^ 1, wB, SLEEP_PRO_NS)) {
+      if (!waitT(&bEmpty[buf], bufPar, wB, SLEEP_PRO_NS)) {
         giveUp(2, 1);
         break;
       }
       const long long tTr = clock64();
       if (pw == 0) trace(3, 1, nTr);
-      const int tt = t / a.numCoBlk;
-      const int64_t pos0 = int64_t(tt) * NT - a.padding;
       // tf32 split: [cg][rows][4 f32]; f16 split: [cg / 2][rows][8 f16], this thread's 4 channels = half of a chunk
       float* hi = F16 ? sAct + buf * actBufFloats + (cg >> 1) * rows * 4 + (cg & 1) * 2
                       : sAct + buf * actBufFloats + cg * rows * 4;
       float* lo = hi + actBufFloats / 2;
-      const float* src = sRaw + (it % NRAW) * (KC * rows) + cg * 4 * rows;
+      const float* src = sRaw + rawBuf * (KC * rows) + cg * 4 * rows;
       // this thread's four channels: constants in registers for the whole chunk (they were re-read from shared
       // memory per row slot before: 800 of the producers' 1440 shared-memory wavefronts per chunk)
       float2 nm[2], pa[2], pb[2], pi[2];  // channel pairs (0, 1) and (2, 3); nm = -mean
@@ -742,7 +747,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       if (lane == 0) mbarArrive(&bFull[buf]);
       if (pw == 0) trace(3, 2, nTr);
       cTr += clock64() - tTr;
-      t = tn, c = cn, ++it;
+      t = tn, c = cn, pos0 = posN, ++it;
+      rawBuf ^= 1;
+      if (++buf == NB) buf = 0, bufPar ^= 1;
     }
     cpAsyncWait<0>();
     if (pw == 0) profAdd(10, wB), profAdd(11, wCp), profAdd(12, cTr), profAdd(13, clock64() - tStart);
