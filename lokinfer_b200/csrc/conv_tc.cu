@@ -75,7 +75,7 @@ struct Fmt {
 constexpr int STAGE_PITCH = 33;                       // floats per row of an epilogue transpose tile
 constexpr int STAGE_FLOATS = 32 * STAGE_PITCH;
 constexpr int MAX_HALO = 50;     // (K - 1) * dilation of the widest Kokoro conv (K 11, dilation 5)
-constexpr int MAX_W_STAGES = 6, MIN_W_STAGES = 2, PREF_W_STAGES = 3;  // weight ring slots
+constexpr int MAX_W_STAGES = 4, MIN_W_STAGES = 2, PREF_W_STAGES = 2;  // weight ring slots
 constexpr int TAP_GROUP = 4;  // most taps per weight slot: one bulk copy, one wait, MMAs back to back, one release
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr uint32_t SLEEP_EPI_NS = 256, SLEEP_PRO_NS = 128, SLEEP_W_NS = 64, SLEEP_MMA_NS = 32;
@@ -95,6 +95,7 @@ struct TcArgs {
   int issuers;     // 1: one thread issues all MMAs; 2: one thread for the hi MMAs, one for the lo MMAs
   int wG;          // taps per weight slot: the k taps of a chunk go in ceil(k / wG) groups of near-equal size
   int drainN;      // 16-channel chunks accumulated in Dhi between two drains into the running sums
+  int drainFirst;  // the same for the first drain group of a tile (longer: it runs under the previous tile's epilogue)
   int numTTiles, numCoBlk;
   int* status;
   long long* prof;  // null, or 16 cycle counters summed over CTAs (see convTcProfile)
@@ -337,7 +338,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int numTiles = a.numTTiles * a.numCoBlk;
   const int nChunks16 = a.ci / KC;
-  const int nGroups = (nChunks16 + a.drainN - 1) / a.drainN;  // Dhi drains per tile
+  // Dhi drains per tile: a first group of drainFirst chunks, then groups of drainN
+  const int nGroups = nChunks16 <= a.drainFirst ? 1 : 1 + (nChunks16 - a.drainFirst + a.drainN - 1) / a.drainN;
   // tap groups of a chunk: the first tgExtra groups have tgBase + 1 taps, the others tgBase
   const int nTapGroups = (a.k + a.wG - 1) / a.wG, tgBase = a.k / nTapGroups, tgExtra = a.k % nTapGroups;
 
@@ -814,7 +816,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const uint32_t bufU = uint32_t(actBufFloats * 4) >> 4, loBU = bufU >> 1, ksBU = 2 * uint32_t(rows);
       const uint32_t slotU = uint32_t(a.wG) * kStageU;
       const int dil = a.dilation, wStages = a.wStages, drainN = a.drainN;
-      int slot = 0, buf = 0, g = 0, tapIt = 0;
+      int slot = 0, buf = 0, g = 0, tapIt = 0, grpLen = a.drainFirst;
       uint32_t slotPh = 0, bufPh = 0, groupPar = 0, tilePar = 0;
       bool dead = false, ready = false;  // ready: the next round's weight slot is already known to be full
       long long wBf = 0, wHe = 0, wWf = 0;
@@ -891,14 +893,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           const bool lastChunk = c == nChunks16 - 1;
           if (isHi) {
             // the hi chain of a drain group (drainN chunks, or what is left of the tile) is complete
-            if (g == drainN - 1 || lastChunk) mmaCommit(hiFull);
+            if (g == grpLen - 1 || lastChunk) mmaCommit(hiFull);
           } else if (lastChunk) {
             mmaCommit(loFull);
           }
           mmaCommit(&bEmpty[buf]);  // activation buffer free once both issuers' MMAs have read it
           trace(isHi ? 0 : 1, 3, nTr);
           if (++buf == NB) buf = 0, bufPh ^= 1;
-          if (++g == drainN || lastChunk) g = 0, groupPar ^= 1;
+          if (++g == grpLen || lastChunk) g = 0, groupPar ^= 1, grpLen = lastChunk ? a.drainFirst : drainN;
         }
         tilePar ^= 1;
       }
@@ -925,7 +927,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const uint32_t bufU = uint32_t(actBufFloats * 4) >> 4, loBU = bufU >> 1, ksBU = 2 * uint32_t(rows);
       const uint32_t slotU = uint32_t(a.wG) * kStageU;
       const int dil = a.dilation, wStages = a.wStages, drainN = a.drainN;
-      int slot = 0, buf = 0, g = 0, tapIt = 0;
+      int slot = 0, buf = 0, g = 0, tapIt = 0, grpLen = a.drainFirst;
       uint32_t slotPh = 0, bufPh = 0, groupPar = 0, tilePar = 0;
       bool dead = false, ready = false;  // ready: the next round's weight slot is already known to be full
       long long wBf = 0, wHe = 0, wWf = 0, wLe = 0;
@@ -1027,12 +1029,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           if (dead) break;
           const bool lastChunk = c == nChunks16 - 1;
           // the hi chain of a drain group (drainN chunks, or what is left of the tile) is complete
-          if (g == drainN - 1 || lastChunk) mmaCommit(hiFull);
+          if (g == grpLen - 1 || lastChunk) mmaCommit(hiFull);
           if (lastChunk) mmaCommit(loFull);
           mmaCommit(&bEmpty[buf]);  // activation buffer free once the MMAs have read it
           trace(0, 3, nTr);
           if (++buf == NB) buf = 0, bufPh ^= 1;
-          if (++g == drainN || lastChunk) g = 0, groupPar ^= 1;
+          if (++g == grpLen || lastChunk) g = 0, groupPar ^= 1, grpLen = lastChunk ? a.drainFirst : drainN;
         }
         tilePar ^= 1;
       }
@@ -1138,7 +1140,8 @@ __global__ void convtTcPackKernel(const float* __restrict__ w, void* __restrict_
 // parameters, barriers) and the weight ring it leaves room for: the largest taps-per-slot (<= TAP_GROUP) that still
 // gives MIN_W_STAGES slots. Returns 0 when even single-tap slots do not fit.
 // Tuning overrides for experiments (environment, read once): LKC_TC_WG = taps per weight slot, LKC_TC_WSTAGES = ring
-// slots (both only honoured when they fit), LKC_TC_ISSUERS = 1 or 2, LKC_TC_GRID = fewer CTAs than SMs.
+// slots (both only honoured when they fit), LKC_TC_ISSUERS = 1 or 2, LKC_TC_GRID = fewer CTAs than SMs,
+// LKC_TC_DRAIN_FIRST = chunks in the first drain group of a tile.
 static int tuneKnob(const char* name) {
   const char* v = std::getenv(name);
   return v ? std::atoi(v) : 0;
@@ -1152,8 +1155,8 @@ static size_t convTcSmemBytes(int64_t ci, int rows, int k, bool f16, int* wStage
   const size_t act = size_t(f16 ? Fmt<true>::NB : Fmt<false>::NB) * actRow * rows + size_t(NRAW) * KC * rows * 4;
   if (fixed + act > size_t(kMaxSmem)) return 0;
   const size_t avail = size_t(kMaxSmem) - fixed - act;
-  // Large groups matter more than a deep ring: the largest group size that leaves PREF_W_STAGES slots wins, else
-  // the deepest ring.
+  // Large groups matter more than a deep ring (measured: two slots of four taps beat four slots of three): the
+  // largest group size that leaves PREF_W_STAGES slots wins, else the deepest ring.
   int bestG = 0, bestWs = 0;
   for (int g = (forceG >= 1 && forceG <= TAP_GROUP) ? forceG : TAP_GROUP; g >= 1; --g) {
     const int groups = (k + g - 1) / g, gmax = (k + groups - 1) / groups;  // near-equal groups, the largest has gmax taps
@@ -1287,6 +1290,13 @@ static int finishArgs(TcArgs& a, bool f16, int* grid, size_t* smem) {
   if (a.residual && n > nChunks / 4) n = nChunks / 4;
   if (a.debug >> 8) n = a.debug >> 8, a.debug &= 0xff;  // profiling build: forced group length
   a.drainN = n < 1 ? 1 : n;
+  // The first group of a tile can be made longer (its MMAs run while the epilogue warps are still busy with the
+  // previous tile). Measured: no gain (K = 7: 0.130 vs 0.122 ms) and a longer chain costs accuracy, so it stays equal
+  // to the other groups unless forced for an experiment.
+  int nFirst = a.drainN;
+  static const int forceFirst = tuneKnob("LKC_TC_DRAIN_FIRST");
+  if (forceFirst > 0) nFirst = forceFirst < a.drainN ? a.drainN : (forceFirst > nChunks ? nChunks : forceFirst);
+  a.drainFirst = nFirst;
   const int tiles = a.numTTiles * a.numCoBlk;
   *grid = tiles < smCount[dev] ? tiles : smCount[dev];
   static const int forceGrid = tuneKnob("LKC_TC_GRID");
