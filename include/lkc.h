@@ -175,6 +175,21 @@ LKC_API LkcConvState* lkc_convt_state_create(const void* wp, int64_t ci, int64_t
  * ptrs x[n_fft+2,L] | out[hop*(L-1)]; ints x(2) out(1) hop n_fft. Fails when n_fft/2+1 > 64, like the reference. */
 LKC_API int lkc_istft_logits_f32_cuda(const LkcArgs* a, void* stream);
 
+/* harmonic_source_f32_cpu (kernels/cpu/kokoro_signal.cpp:97-190, adapter :370-373; rule python/lokinfer/ops/kokoro.py
+ * :417-426): Kokoro's SourceModuleHnNSF with the noise draw as an operand.
+ * ptrs f0[n] noise[300n,9] w[9] b[1] | out[300n]; ints f0(1) noise(2) w(1) b(1) out(1). n <= 27962 (sample indices are
+ * converted to float32, as in the reference). The float32 operation order of the reference kernel is part of the
+ * contract (the phase reaches ~1e6 rad). Uses a phase table of 9 n floats as scratch between its two kernels: the
+ * library keeps one grow-only buffer per device, so the first call on a device (and any call with a larger n) calls
+ * cudaMalloc and must not be inside a stream capture; calls on one device must not overlap in time.
+ * The in-kernel random variant (harmonic_source_rng_f32_cpu) is not provided. */
+LKC_API int lkc_harmonic_source_f32_cuda(const LkcArgs* a, void* stream);
+
+/* stft_magphase_f32_cpu (kernels/cpu/kokoro_signal.cpp:196-272, adapter :382-385; rule ops/kokoro.py:438-449):
+ * torch.stft(center, reflect, periodic hann(n_fft), onesided) -> cat(abs, angle).
+ * ptrs x[S] | out[n_fft+2, S/hop+1]; ints x(1) out(2) hop n_fft. n_fft even, <= 64; S > n_fft/2. */
+LKC_API int lkc_stft_magphase_f32_cuda(const LkcArgs* a, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

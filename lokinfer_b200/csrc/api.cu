@@ -265,11 +265,13 @@ const Entry kEntries[] = {
     {"convt_poly_pack_f32_cuda", lkc_convt_poly_pack_f32_cuda},
     {"convt_tc_pack_f32_cuda", lkc_convt_tc_pack_f32_cuda},
     {"gemm_bias_f32_cuda", lkc_gemm_bias_f32_cuda},
+    {"harmonic_source_f32_cuda", lkc_harmonic_source_f32_cuda},
     {"istft_logits_f32_cuda", lkc_istft_logits_f32_cuda},
     {"leaky_relu_f32_cuda", lkc_leaky_relu_f32_cuda},
     {"pad_reflect1d_f32_cuda", lkc_pad_reflect1d_f32_cuda},
     {"scale_f32_cuda", lkc_scale_f32_cuda},
     {"snake_f32_cuda", lkc_snake_f32_cuda},
+    {"stft_magphase_f32_cuda", lkc_stft_magphase_f32_cuda},
 };
 constexpr int kNumEntries = static_cast<int>(sizeof(kEntries) / sizeof(kEntries[0]));
 }  // namespace
@@ -283,4 +285,4 @@ extern "C" LKC_API LkcRunFn lkc_find_kernel(const char* name) {
   return nullptr;
 }
 extern "C" LKC_API const char* lkc_last_error(void) { return gError; }
-extern "C" LKC_API const char* lkc_build_info(void) { return "lkc sm_100a: tcgen05 3xTF32 fused conv + cuda-core conv/convT/stats/istft"; }
+extern "C" LKC_API const char* lkc_build_info(void) { return "lkc sm_100a: tcgen05 split-operand fused conv / convT + cuda-core conv/convT/stats/source/stft/istft"; }

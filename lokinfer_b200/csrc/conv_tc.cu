@@ -44,6 +44,7 @@ namespace {
 constexpr int NT = 256;         // time columns per tile (= UMMA N)
 constexpr int MT = 128;         // output channels per tile (= UMMA M)
 constexpr int KC = 16;          // input channels per staged chunk (one weight stage, two K8 steps)
+constexpr int MAX_NB = 4;       // most activation (hi / lo) buffers
 constexpr int NRAW = 2;         // raw-input staging buffers filled by cp.async one chunk ahead
 constexpr int EPI_WARPS = 8, PRO_WARPS = 8;
 constexpr int W_WARP = EPI_WARPS + PRO_WARPS, MMA_WARP = W_WARP + 1, MMA_LO_WARP = W_WARP + 2;
@@ -92,6 +93,8 @@ struct TcArgs {
   float slope, outScale;
   int rows;        // staged time rows per buffer = NT + (k-1)*dilation
   int wStages;     // weight ring depth (slots)
+  int nb;          // activation buffers
+  uint32_t sleepEpi, sleepPro, sleepW, sleepMma;  // nanosleep back-off of each role's barrier polls
   int issuers;     // 1: one thread issues all MMAs; 2: one thread for the hi MMAs, one for the lo MMAs
   int wG;          // taps per weight slot: the k taps of a chunk go in ceil(k / wG) groups of near-equal size
   int drainN;      // 16-channel chunks accumulated in Dhi between two drains into the running sums
@@ -315,7 +318,7 @@ __device__ __forceinline__ void regDec() {
 template <int ACT, bool PROF, bool PARTIAL, int TS, bool F16>
 __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   constexpr int W_STAGE_BYTES = Fmt<F16>::W_STAGE_BYTES, W_STAGE_FLOATS = Fmt<F16>::W_STAGE_FLOATS;
-  constexpr int NB = Fmt<F16>::NB;
+  const int NB = a.nb;  // activation buffers (Fmt<F16>::NB unless overridden for an experiment)
   extern __shared__ __align__(1024) unsigned char smemRaw[];
   const int rows = a.rows;
   const int actBufFloats = Fmt<F16>::ACT_BYTES_PER_ROW / 4 * rows;  // hi + lo
@@ -325,8 +328,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
   float* const sStage = sW + a.wStages * a.wG * W_STAGE_FLOATS;          // EPI_WARPS transpose tiles of [32][STAGE_PITCH]
   float* const sPar = sStage + EPI_WARPS * STAGE_FLOATS;          // [4][ci]: folded prologue constants
   uint64_t* const bFull = reinterpret_cast<uint64_t*>(sPar + 4 * a.ci);
-  uint64_t* const bEmpty = bFull + NB;
-  uint64_t* const wFull = bEmpty + NB;
+  uint64_t* const bEmpty = bFull + MAX_NB;
+  uint64_t* const wFull = bEmpty + MAX_NB;
   uint64_t* const wEmpty = wFull + MAX_W_STAGES;
   uint64_t* const hiFull = wEmpty + MAX_W_STAGES;
   uint64_t* const hiEmpty = hiFull + 1;
@@ -457,7 +460,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       cPre += clock64() - tPre;
       // wait for the chunk's hi chain, add it to the running sums, hand Dhi back
       auto drainChunk = [&]() -> bool {
-        if (!waitT(hiFull, groupIt & 1, wHi, SLEEP_EPI_NS)) {
+        if (!waitT(hiFull, groupIt & 1, wHi, a.sleepEpi)) {
           giveUp(1, 1);
           return false;
         }
@@ -501,7 +504,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         }
       }
       if (dead) break;
-      if (!waitT(loFull, tileIt & 1, wLo, SLEEP_EPI_NS)) {
+      if (!waitT(loFull, tileIt & 1, wLo, a.sleepEpi)) {
         giveUp(1, 2);
         break;
       }
@@ -682,7 +685,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const long long tCp = clock64();
       cpAsyncWait<1>();  // this chunk's copies (the older group) have landed; the next chunk's stay in flight
       wCp += clock64() - tCp;
-      if (!waitT(&bEmpty[buf], bufPar, wB, SLEEP_PRO_NS)) {
+      if (!waitT(&bEmpty[buf], bufPar, wB, a.sleepPro)) {
         giveUp(2, 1);
         break;
       }
@@ -771,7 +774,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
         for (int c = 0; c < nChunks16 && !dead; ++c) {
           for (int gi = 0; gi < nTapGroups; ++gi, ++wIt) {
             const int n = tgBase + (gi < tgExtra ? 1 : 0);
-            if (!waitT(&wEmpty[ws], wPh, wW, SLEEP_W_NS)) {
+            if (!waitT(&wEmpty[ws], wPh, wW, a.sleepW)) {
               giveUp(3, 1);
               dead = true;
               break;
@@ -823,18 +826,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const long long tStart = clock64();
       for (int tile = blockIdx.x; lane == 0 && tile < numTiles && !dead; tile += gridDim.x) {
         for (int c = 0; c < nChunks16 && !dead; ++c) {
-          if (!waitT(&bFull[buf], bufPh, wBf, SLEEP_MMA_NS)) {
+          if (!waitT(&bFull[buf], bufPh, wBf, a.sleepMma)) {
             giveUp(4, 2);
             dead = true;
             break;
           }
           if (isHi) {
-            if (g == 0 && !waitT(hiEmpty, groupPar ^ 1, wHe, SLEEP_MMA_NS)) {  // Dhi drained by the epilogue warps
+            if (g == 0 && !waitT(hiEmpty, groupPar ^ 1, wHe, a.sleepMma)) {  // Dhi drained by the epilogue warps
               giveUp(4, 1);
               dead = true;
               break;
             }
-          } else if (c == 0 && !waitT(loEmpty, tilePar ^ 1, wHe, SLEEP_MMA_NS)) {  // Dlo of the previous tile folded
+          } else if (c == 0 && !waitT(loEmpty, tilePar ^ 1, wHe, a.sleepMma)) {  // Dlo of the previous tile folded
             giveUp(4, 4);
             dead = true;
             break;
@@ -843,7 +846,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           int kk = 0;
           for (int gi = 0; gi < nTapGroups; ++gi) {
             const int gN = tgBase + (gi < tgExtra ? 1 : 0);
-            if (!ready && !waitT(&wFull[slot], slotPh, wWf, SLEEP_MMA_NS)) {
+            if (!ready && !waitT(&wFull[slot], slotPh, wWf, a.sleepMma)) {
               giveUp(4, 3);
               dead = true;
               break;
@@ -934,7 +937,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const long long tStart = clock64();
       for (int tile = blockIdx.x; lane == 0 && tile < numTiles && !dead; tile += gridDim.x) {
         for (int c = 0; c < nChunks16 && !dead; ++c) {
-          if (!waitT(&bFull[buf], bufPh, wBf, SLEEP_MMA_NS)) {
+          if (!waitT(&bFull[buf], bufPh, wBf, a.sleepMma)) {
             giveUp(4, 2);
             dead = true;
             break;
@@ -943,7 +946,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           int kk = 0;
           for (int gi = 0; gi < nTapGroups; ++gi) {
             const int gN = tgBase + (gi < tgExtra ? 1 : 0);
-            if (!ready && !waitT(&wFull[slot], slotPh, wWf, SLEEP_MMA_NS)) {
+            if (!ready && !waitT(&wFull[slot], slotPh, wWf, a.sleepMma)) {
               giveUp(4, 3);
               dead = true;
               break;
@@ -980,7 +983,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
             int nslot = slot + 1;
             uint32_t nph = slotPh;
             if (needLo) {  // first round of a tile: hi, then lo
-              if (needHi && !waitT(hiEmpty, groupPar ^ 1, wHe, SLEEP_MMA_NS)) {
+              if (needHi && !waitT(hiEmpty, groupPar ^ 1, wHe, a.sleepMma)) {
                 giveUp(4, 1);
                 dead = true;
                 break;
@@ -992,7 +995,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
 #pragma unroll
               for (int j = 1; j < TAP_GROUP; ++j)
                 if (j < gN) hiTap(j);
-              if (!waitT(loEmpty, tilePar ^ 1, wLe, SLEEP_MMA_NS)) {
+              if (!waitT(loEmpty, tilePar ^ 1, wLe, a.sleepMma)) {
                 giveUp(4, 4);
                 dead = true;
                 break;
@@ -1009,7 +1012,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
               for (int j = 1; j < TAP_GROUP; ++j)
                 if (j < gN) loTap(j);
               if (needHi) {
-                if (!waitT(hiEmpty, groupPar ^ 1, wHe, SLEEP_MMA_NS)) {
+                if (!waitT(hiEmpty, groupPar ^ 1, wHe, a.sleepMma)) {
                   giveUp(4, 1);
                   dead = true;
                   break;
@@ -1141,10 +1144,16 @@ __global__ void convtTcPackKernel(const float* __restrict__ w, void* __restrict_
 // gives MIN_W_STAGES slots. Returns 0 when even single-tap slots do not fit.
 // Tuning overrides for experiments (environment, read once): LKC_TC_WG = taps per weight slot, LKC_TC_WSTAGES = ring
 // slots (both only honoured when they fit), LKC_TC_ISSUERS = 1 or 2, LKC_TC_GRID = fewer CTAs than SMs,
-// LKC_TC_DRAIN_FIRST = chunks in the first drain group of a tile.
+// LKC_TC_DRAIN_FIRST = chunks in the first drain group of a tile, LKC_TC_NB = activation buffers,
+// LKC_TC_SLEEP_{EPI,PRO,W,MMA} = nanosleep back-off (ns) of a role's barrier polls.
 static int tuneKnob(const char* name) {
   const char* v = std::getenv(name);
   return v ? std::atoi(v) : 0;
+}
+
+static int tunedNb(bool f16) {
+  static const int forceNb = tuneKnob("LKC_TC_NB");
+  return (forceNb >= 2 && forceNb <= MAX_NB) ? forceNb : (f16 ? Fmt<true>::NB : Fmt<false>::NB);
 }
 
 static size_t convTcSmemBytes(int64_t ci, int rows, int k, bool f16, int* wStages, int* wG) {
@@ -1152,7 +1161,7 @@ static size_t convTcSmemBytes(int64_t ci, int rows, int k, bool f16, int* wStage
   const size_t tap = f16 ? Fmt<true>::W_STAGE_BYTES : Fmt<false>::W_STAGE_BYTES;
   const size_t actRow = f16 ? Fmt<true>::ACT_BYTES_PER_ROW : Fmt<false>::ACT_BYTES_PER_ROW;
   const size_t fixed = size_t(EPI_WARPS) * STAGE_FLOATS * 4 + size_t(4) * ci * 4 + 512;
-  const size_t act = size_t(f16 ? Fmt<true>::NB : Fmt<false>::NB) * actRow * rows + size_t(NRAW) * KC * rows * 4;
+  const size_t act = size_t(tunedNb(f16)) * actRow * rows + size_t(NRAW) * KC * rows * 4;
   if (fixed + act > size_t(kMaxSmem)) return 0;
   const size_t avail = size_t(kMaxSmem) - fixed - act;
   // Large groups matter more than a deep ring (measured: two slots of four taps beat four slots of three): the
@@ -1259,6 +1268,11 @@ static int finishArgs(TcArgs& a, bool f16, int* grid, size_t* smem) {
   *smem = convTcSmemBytes(a.ci, a.rows, a.k, f16, &a.wStages, &a.wG);
   static const int forceIssuers = tuneKnob("LKC_TC_ISSUERS");
   a.issuers = forceIssuers == 2 ? 2 : 1;
+  a.nb = tunedNb(f16);
+  static const int sE = tuneKnob("LKC_TC_SLEEP_EPI"), sP = tuneKnob("LKC_TC_SLEEP_PRO"), sW = tuneKnob("LKC_TC_SLEEP_W"),
+                   sM = tuneKnob("LKC_TC_SLEEP_MMA");
+  a.sleepEpi = sE ? uint32_t(sE) : SLEEP_EPI_NS, a.sleepPro = sP ? uint32_t(sP) : SLEEP_PRO_NS;
+  a.sleepW = sW ? uint32_t(sW) : SLEEP_W_NS, a.sleepMma = sM ? uint32_t(sM) : SLEEP_MMA_NS;
   LKC_REQUIRE(*smem != 0, "conv (tensor-core): window too large");
   static int* statusPtr[64] = {};
   static long long* profPtr[64] = {};

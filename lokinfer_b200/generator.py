@@ -100,6 +100,16 @@ class Generator:
 
     # ------------------------------------------------------------------ the graph
 
+    def har_from_f0(self, f0, noise):
+        """The generator's `har` input from the F0 curve, as the reference graph computes it before the generator
+        (models/kokoro/model.py:720-726): harmonic source (9 harmonics, x300, Linear 9 -> 1, tanh) then STFT(n_fft 20,
+        hop 5) -> cat(magnitude, phase). f0 f32[T] (one value per frame of x), noise f32[300 T, 9] (the normal draw the
+        reference takes from its generator; an operand here) -> f32[22, 60 T + 1]."""
+        ops.check("m_source.l_linear.weight" in self.w, "the state dict has no m_source.l_linear weights")
+        w9 = self.w["m_source.l_linear.weight"].reshape(9)
+        src = ops.harmonic_source_f32_cuda(f0, noise, w9, self.w["m_source.l_linear.bias"].reshape(1))
+        return ops.stft_magphase_f32_cuda(src, n_fft=20, hop=5)
+
     def forward(self, x, har, s, fused=True, outputs=("audio",), concurrent=True):
         """x f32[512, T], har f32[22, 60 T + 1], s f32[128] (cuda tensors) -> the named outputs
         ("audio" f32[300 T], "post" f32[22, 60 T + 1]).

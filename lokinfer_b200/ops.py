@@ -317,6 +317,34 @@ def istft_logits_f32_cuda(x, n_fft=20, hop=5):
     return out
 
 
+def harmonic_source_f32_cuda(f0, noise, w, b):
+    """Kokoro SourceModuleHnNSF (SineGen x300, 9 harmonics, Linear 9->1, tanh) in the reference kernel's op order.
+    f0 f32[n] (80 Hz curve), noise f32[300n, 9] (the randn_like draw), w f32[9], b f32[1] -> f32[300n]
+    (python/lokinfer/ops/kokoro.py:417-426)."""
+    _f32(f0, w, b, rank=1)
+    _f32(noise, rank=2)
+    s = f0.shape[0] * 300
+    check(noise.shape[0] == s and noise.shape[1] == 9, f"noise must be f32[300n, 9], got {tuple(noise.shape)}")
+    check(w.shape[0] == 9 and b.shape[0] == 1, "w must be f32[9], b f32[1]")
+    check(1 <= f0.shape[0] <= 27962, "f0 must hold 1..27962 frames")
+    out = _new(f0, (s,))
+    _run("harmonic_source_f32_cuda", [f0, noise, w, b], [out])
+    return out
+
+
+def stft_magphase_f32_cuda(x, n_fft=20, hop=5):
+    """torch.stft(center, reflect, periodic hann(n_fft), onesided) -> cat(abs, angle):
+    f32[S] -> f32[n_fft+2, S//hop+1] (python/lokinfer/ops/kokoro.py:438-449)."""
+    n_fft, hop = _int(n_fft, "n_fft"), _int(hop, "hop")
+    _f32(x, rank=1)
+    check(n_fft >= 2 and n_fft % 2 == 0 and hop >= 1, "n_fft must be even, hop >= 1")
+    check(n_fft <= 64, "n_fft must be <= 64 (the windowed basis is kept in shared memory)")
+    check(x.shape[0] >= n_fft // 2 + 1, "signal must be longer than n_fft/2 (reflect pad)")
+    out = _new(x, (n_fft + 2, x.shape[0] // hop + 1))
+    _run("stft_magphase_f32_cuda", [x], [out], attrs_int=[hop, n_fft])
+    return out
+
+
 # --- fused frame-rate conv -----------------------------------------------------------------------------------
 
 def conv_tile(ci: int, k: int) -> int:

@@ -61,6 +61,10 @@ def generator_weights(seed: int = 0) -> dict[str, np.ndarray]:
     # reaches ~5e4 and an absolute waveform tolerance would mean nothing. This keeps |audio| of order 1.
     sd["conv_post.weight"] = (0.1 * r.standard_normal((N_BINS, 128, 7)) / math.sqrt(128 * 7)).astype(np.float32)
     sd["conv_post.bias"] = (r.standard_normal(N_BINS) * 0.1).astype(np.float32)
+    # Linear(9 -> 1) of the harmonic source that produces `har` (models/kokoro/model.py:720-726); drawn last so that
+    # the weights above do not depend on it
+    sd["m_source.l_linear.weight"] = (r.standard_normal((1, 9)) * 0.5).astype(np.float32)
+    sd["m_source.l_linear.bias"] = (r.standard_normal(1) * 0.1).astype(np.float32)
     return sd
 
 
@@ -104,3 +108,30 @@ def conv_case(ci: int, co: int, l: int, k: int, seed: int, big: bool = True):
     alpha = (r.uniform(0.2, 3.0, ci) if big else r.uniform(0.5, 1.5, ci)).astype(np.float32)
     res = r.standard_normal((co, max(l, 1))).astype(np.float32)
     return x, w, b, affine, alpha, res
+
+
+def f0_curve(n: int, seed: int) -> np.ndarray:
+    """An F0 contour at 80 Hz with the features the reference's test recipe exercises
+    (tests/kernels/test_kokoro_kernels.py:477-488): smooth 70..400 Hz voiced stretches, unvoiced (0) gaps, values
+    below the voicing threshold (10 Hz), first frame unvoiced."""
+    r = np.random.default_rng(seed)
+    t = np.arange(n)
+    f0 = 180 + 90 * np.sin(t / 17.0 + seed) + 40 * np.sin(t / 5.3) + r.normal(0, 5, n)
+    f0 = np.clip(f0, 70, 400)
+    for _ in range(max(1, n // 40)):
+        a = int(r.integers(0, n))
+        f0[a:a + int(r.integers(2, 12))] = 0.0
+    f0[r.integers(0, n, max(1, n // 50))] = r.uniform(0, 10)
+    f0[0] = 0.0
+    return f0.astype(np.float32)
+
+
+def source_case(n: int, seed: int):
+    """Seeded operands of the harmonic source for n frames: f0[n], noise[300n, 9], w[9], b[1]
+    (distributions of tests/kernels/test_kokoro_kernels.py:511-516)."""
+    r = np.random.default_rng(seed)
+    f0 = f0_curve(n, seed)
+    noise = r.standard_normal((300 * n, 9)).astype(np.float32)
+    w = (r.standard_normal(9) * 0.5).astype(np.float32)
+    b = (r.standard_normal(1) * 0.1).astype(np.float32)
+    return f0, noise, w, b

@@ -237,6 +237,126 @@ def istft_logits_torch(x, n_fft=20, hop=5):
 
 # ----------------------------------------------------------------------------- graph (models/kokoro/model.py)
 
+# --- harmonic source + STFT: the producer of the generator's `har` input (kernels/cpu/kokoro_signal.cpp:97-272) ----
+# The reference pins these two ops against the third-party kokoro modules (SourceModuleHnNSF, TorchSTFT), which are
+# absent here. harmonic_source below restates the reference KERNEL's float32 operation sequence (its header comment
+# spells out the torch ops it mirrors); stft_magphase is pinned against torch.stft (tests/test_oracle.py).
+
+SOURCE_UP = 300          # kokoro_signal.cpp:19 (kUp = prod(upsample_rates) * hop)
+SOURCE_HARMONICS = 9     # :18
+SOURCE_RATE = 24000.0    # :20
+SOURCE_VOICED = 10.0     # :21
+SOURCE_SINE_AMP = 0.1    # :22
+SOURCE_NOISE_STD = 0.003  # :23
+
+
+def _fma32(a, b, c):
+    """float32 fused multiply-add of numpy arrays: the product of two float32 is exact in float64."""
+    return (a.astype(np.float64) * b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)
+
+
+def harmonic_phase_table(f0):
+    """p300[j, h] = phase of harmonic h at frame j times 300 (kokoro_signal.cpp:103-115): rad = remainder(f0 (h+1) /
+    24000, 1) in float32, running sum in float64, phase = (float32(sum) * 2) * float32(pi), all in float32."""
+    f0 = np.asarray(f0, np.float32)
+    h = np.arange(1, SOURCE_HARMONICS + 1, dtype=np.float32)
+    fn = f0[:, None] * h[None, :]
+    rad = np.fmod(fn / np.float32(SOURCE_RATE), np.float32(1.0)).astype(np.float32)
+    rad = np.where((rad != 0) & (rad < 0), rad + np.float32(1.0), rad).astype(np.float32)  # torch.remainder (:26-30)
+    acc = np.cumsum(rad.astype(np.float64), axis=0)  # sequential float64 adds, like the reference's loop
+    phase = (acc.astype(np.float32) * np.float32(2.0)) * np.float32(math.pi)
+    return (phase * np.float32(SOURCE_UP)).astype(np.float32)
+
+
+def harmonic_source(f0, noise, w, b):
+    """Kokoro SourceModuleHnNSF as the reference kernel computes it (kokoro_signal.cpp:97-177): f0 f32[n] (one value
+    per 80 Hz frame), noise f32[300 n, 9], w f32[9], b f32[1] -> f32[300 n]. Linear x300 upsampling of the phase table
+    (align_corners = False: source index fma(1/300, i + 0.5, -0.5), value fma(t0, l0, t1 * l1)), sine * 0.1 where
+    voiced (f0 > 10) plus noise * (0.003 voiced | 0.1 / 3 unvoiced), Linear(9 -> 1) accumulated harmonic by harmonic,
+    tanh. numpy float32 throughout (torch tensors in, torch tensor out)."""
+    f0 = np.asarray(f0, np.float32)
+    noise = np.asarray(noise, np.float32)
+    w = np.asarray(w, np.float32)
+    b = np.asarray(b, np.float32)
+    n = f0.shape[0]
+    s = n * SOURCE_UP
+    p300 = harmonic_phase_table(f0)
+    i = np.arange(s, dtype=np.float32)  # exact below 2^24 samples (the reference converts i to float as well)
+    scale = np.float32(1.0 / float(SOURCE_UP))
+    real = np.maximum(_fma32(np.full(s, scale, np.float32), i + np.float32(0.5), np.full(s, -0.5, np.float32)),
+                      np.float32(0.0))
+    i0 = np.minimum(np.floor(real).astype(np.int64), n - 1)
+    l1 = np.clip(real - i0.astype(np.float32), np.float32(0.0), np.float32(1.0)).astype(np.float32)
+    l0 = (np.float32(1.0) - l1).astype(np.float32)
+    i1 = i0 + (i0 < n - 1)
+    voiced = f0[np.arange(s) // SOURCE_UP] > np.float32(SOURCE_VOICED)
+    uv = voiced.astype(np.float32)
+    amp = np.where(voiced, np.float32(SOURCE_NOISE_STD), np.float32(SOURCE_SINE_AMP) / np.float32(3.0)).astype(np.float32)
+    y = np.zeros(s, np.float32)
+    for h in range(SOURCE_HARMONICS):
+        t0, t1 = p300[i0, h], p300[i1, h]
+        phase = _fma32(t0, l0, (t1 * l1).astype(np.float32))
+        sine = (np.sin(phase.astype(np.float64)).astype(np.float32) * np.float32(SOURCE_SINE_AMP)).astype(np.float32)
+        v = ((sine * uv).astype(np.float32) + (amp * noise[:, h]).astype(np.float32)).astype(np.float32)
+        y = (y + (v * w[h]).astype(np.float32)).astype(np.float32)
+    return torch.from_numpy(np.tanh((y + b[0]).astype(np.float64)).astype(np.float32))
+
+
+def harmonic_source_torch(f0, noise, w, b):
+    """The torch-op form the reference kernel says it mirrors (kokoro_signal.cpp:98-103): remainder, cumsum (double),
+    F.interpolate(linear, align_corners=False), sin, Linear, tanh. Agrees with harmonic_source except where this
+    host's interpolate rounds the phase (~1e5 rad) differently by one ulp (no fused multiply-add)."""
+    f0, noise, w, b = (torch.as_tensor(np.asarray(v, np.float32)) for v in (f0, noise, w, b))
+    h = torch.arange(1, SOURCE_HARMONICS + 1, dtype=torch.float32)
+    rad = torch.remainder(f0[:, None] * h[None, :] / SOURCE_RATE, 1.0)
+    phase = (torch.cumsum(rad.double(), 0).float() * 2.0) * torch.tensor(math.pi, dtype=torch.float32)
+    up = F.interpolate((phase * SOURCE_UP).t()[None], scale_factor=SOURCE_UP, mode="linear", align_corners=False)[0].t()
+    uv = (f0.repeat_interleave(SOURCE_UP) > SOURCE_VOICED).float()[:, None]
+    amp = uv * SOURCE_NOISE_STD + (1 - uv) * SOURCE_SINE_AMP / 3
+    v = torch.sin(up) * SOURCE_SINE_AMP * uv + amp * noise
+    return torch.tanh(v @ w + b)
+
+
+def stft_len(s, hop=5):
+    return s // hop + 1
+
+
+def stft_magphase(x, n_fft=20, hop=5):
+    """torch.stft(center, reflect, periodic hann(n_fft), onesided) -> cat(abs, angle): [S] -> [n_fft + 2, S // hop + 1]
+    (python/lokinfer/ops/kokoro.py:447-449; the restated kernel is stft_magphase_explicit)."""
+    win = hann_periodic(n_fft, x.dtype).to(x.device)
+    z = torch.stft(x, n_fft, hop_length=hop, win_length=n_fft, window=win, center=True, pad_mode="reflect",
+                   onesided=True, return_complex=True)
+    return torch.cat([z.abs(), z.angle()], 0)
+
+
+def stft_magphase_explicit(x, n_fft=20, hop=5):
+    """The reference kernel (kokoro_signal.cpp:196-272): reflect-padded frames times a windowed DFT basis built in
+    double and rounded to the working dtype, re / im accumulated over m = 0..n_fft-1 in order, imaginary part exactly 0
+    at DC and Nyquist, mag = sqrt(re^2 + im^2), phase = atan2(im, re)."""
+    s = x.shape[0]
+    bins, pad, frames = n_fft // 2 + 1, n_fft // 2, s // hop + 1
+    win = hann_periodic(n_fft, torch.float64).to(x.dtype).double()
+    m = torch.arange(n_fft, dtype=torch.float64)
+    k = torch.arange(bins, dtype=torch.float64)
+    ang = 2.0 * math.pi * ((k[:, None] * m[None, :]) % n_fft) / n_fft
+    cr = (win[None, :] * torch.cos(ang)).to(x.dtype)
+    ci = (-win[None, :] * torch.sin(ang)).to(x.dtype)
+    q = torch.arange(frames)[:, None] * hop + torch.arange(n_fft)[None, :] - pad
+    q = torch.where(q < 0, -q, q)
+    q = torch.where(q >= s, 2 * (s - 1) - q, q)
+    fr = x[q]  # [frames, n_fft]
+    re = torch.zeros(bins, frames, dtype=x.dtype)
+    im = torch.zeros(bins, frames, dtype=x.dtype)
+    for mm in range(n_fft):
+        re = re + cr[:, mm:mm + 1] * fr[None, :, mm]
+        im = im + ci[:, mm:mm + 1] * fr[None, :, mm]
+    im[0] = 0.0
+    if n_fft % 2 == 0:
+        im[n_fft // 2] = 0.0
+    return torch.cat([torch.sqrt(re * re + im * im), torch.atan2(im, re)], 0)
+
+
 def style_bank(sd, s, names=None):
     """gb = Linear(128 -> 2C)(s) for every `<name>.fc` (models/kokoro/model.py:67-81, 135-144)."""
     names = names or sorted(k[: -len(".weight")] for k in sd if k.endswith(".fc.weight"))

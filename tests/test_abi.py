@@ -62,6 +62,14 @@ def test_shape_rules_raise_op_error():
         ops.istft_logits_f32_cuda(z(22, 1))
     with pytest.raises(ops.OpError, match="reflect padding"):
         ops.pad_reflect1d_f32_cuda(z(2, 1), 1, 0)
+    with pytest.raises(ops.OpError, match="noise must be"):
+        ops.harmonic_source_f32_cuda(z(4), z(1200, 8), z(9), z(1))
+    with pytest.raises(ops.OpError, match="w must be"):
+        ops.harmonic_source_f32_cuda(z(4), z(1200, 9), z(8), z(1))
+    with pytest.raises(ops.OpError, match="longer than n_fft/2"):
+        ops.stft_magphase_f32_cuda(z(10))
+    with pytest.raises(ops.OpError, match="n_fft"):
+        ops.stft_magphase_f32_cuda(z(100), n_fft=128)
     with pytest.raises(ops.OpError, match="must be an int"):
         ops.conv1d_f32_cuda(z(2, 8), z(2, 2, 3), z(2), stride=1.0)
 

@@ -296,6 +296,66 @@ def test_istft_other_sizes(cuda):
         assert np.abs(y - ref).max() <= 1e-5 * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("frames", [1, 3, 30, 119, 300, 1040])
+def test_harmonic_source(cuda, frames):
+    """Reference tolerance for this op: max-abs 2e-6 (tests/kernels/test_kokoro_kernels.py:510-522); the float32
+    operation order is part of the contract, so the GPU tracks the oracle far below that."""
+    from lokinfer_b200 import ops
+    n = 2 * frames
+    f0, noise, w, b = synth.source_case(n, frames)
+    d = dev(cuda, f0, noise, w, b)
+    for _ in range(2):  # second call reuses the per-device phase table
+        out = ops.harmonic_source_f32_cuda(*d).cpu().numpy()
+    ref = O.harmonic_source(f0, noise, w, b).numpy()
+    assert out.shape == ref.shape == (600 * frames,)
+    assert np.abs(out - ref).max() <= 2e-6
+    assert rel_l2(out, ref) <= REL_L2
+    # a shorter call after a longer one (table larger than needed)
+    f0s, noises, ws, bs = synth.source_case(2, 99)
+    outs = ops.harmonic_source_f32_cuda(*dev(cuda, f0s, noises, ws, bs)).cpu().numpy()
+    assert np.abs(outs - O.harmonic_source(f0s, noises, ws, bs).numpy()).max() <= 2e-6
+
+
+@pytest.mark.parametrize("s", [11, 25, 600, 6001, 600 * 300, 624000])
+def test_stft_magphase(cuda, s):
+    """tests/kernels/test_kokoro_kernels.py:529-542: magnitude within 1e-5 * max, wrapped phase within 1e-4 where
+    the bin is significant."""
+    from lokinfer_b200 import ops
+    r = np.random.default_rng(s)
+    t = np.arange(s)
+    x = (0.3 * np.sin(t * 0.05) + 0.2 * np.sin(t * 0.9) + 0.05 * r.standard_normal(s)).astype(np.float32)
+    x[: s // 7] = 0.0
+    out = ops.stft_magphase_f32_cuda(dev(cuda, x)[0]).cpu().numpy()
+    ref = O.stft_magphase(torch.from_numpy(x).double()).numpy()
+    mag, ph = ref[:11], ref[11:]
+    assert out.shape == (22, s // 5 + 1)
+    np.testing.assert_allclose(out[:11], mag, atol=1e-5 * mag.max(), rtol=0)
+    sig = mag > 1e-3 * mag.max()
+    dph = np.angle(np.exp(1j * (out[11:].astype(np.float64) - ph)))
+    assert np.abs(dph[sig]).max() < 1e-4
+    dc = np.abs(out[11])  # imaginary part exactly 0 at DC: the phase is 0 or pi
+    assert np.all((dc == 0) | (dc == np.float32(math.pi)))
+    assert rel_l2(out[:11], O.stft_magphase_explicit(torch.from_numpy(x)).numpy()[:11]) <= REL_L2
+
+
+def test_stft_of_harmonic_source_chain(cuda):
+    """har = STFT(harmonic_source(F0)) as the generator's caller computes it, F = 119
+    (tests/kernels/test_kokoro_kernels.py:556-575)."""
+    from lokinfer_b200 import ops
+    n = 238
+    f0, noise, w, b = synth.source_case(n, 117)
+    d = dev(cuda, f0, noise, w, b)
+    out = ops.stft_magphase_f32_cuda(ops.harmonic_source_f32_cuda(*d)).cpu().numpy()
+    src = O.harmonic_source(f0, noise, w, b)
+    ref = O.stft_magphase(src.double()).numpy()
+    mag, ph = ref[:11], ref[11:]
+    assert out.shape == (22, 60 * n + 1)
+    np.testing.assert_allclose(out[:11], mag, atol=1e-5 * mag.max(), rtol=0)
+    sig = mag > 1e-3 * mag.max()
+    dph = np.angle(np.exp(1j * (out[11:].astype(np.float64) - ph)))
+    assert np.abs(dph[sig]).max() < 1e-3
+
+
 def test_basic_ops(cuda):
     """The unfused parity layer: conv1d (all strides incl. noise_convs[0]), conv_transpose1d, adain1d (mean-100 trap),
     snake, leaky_relu, add, add3_scale, scale, pad_reflect1d (bit-exact data movement), gemm_bias."""

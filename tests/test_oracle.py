@@ -159,6 +159,53 @@ def test_istft_two_restatements_agree(l):
         assert (a - b).abs().max().item() <= tol * max(1.0, b.abs().max().item())
 
 
+@pytest.mark.parametrize("frames", [1, 3, 30, 119, 300])
+def test_harmonic_source_two_restatements_agree(frames):
+    """The float32 operation sequence of the reference kernel (kernels/cpu/kokoro_signal.cpp:97-177) and the torch-op
+    form that kernel documents (remainder, double cumsum, linear interpolate, sin, Linear, tanh) agree within the
+    reference's own tolerance for this op (2e-6, tests/kernels/test_kokoro_kernels.py:522), on its recipe's inputs
+    (n = 2 * frames, the f0 curve with unvoiced gaps)."""
+    n = 2 * frames
+    f0, noise, w, b = synth.source_case(n, frames)
+    a = O.harmonic_source(f0, noise, w, b)
+    t = O.harmonic_source_torch(f0, noise, w, b)
+    assert a.shape == t.shape == (600 * frames,)
+    assert (a - t).abs().max().item() <= 2e-6
+    assert a.abs().max().item() <= 1.0 and a.abs().max().item() > 1e-3
+    # unvoiced first frame: no sine, only noise * 0.1 / 3 through the Linear + tanh
+    uv0 = np.tanh((noise[:150] * (np.float32(0.1) / np.float32(3.0))) @ w + b[0])
+    np.testing.assert_allclose(a[:150].numpy(), uv0, atol=1e-6)
+
+
+@pytest.mark.parametrize("s", [11, 25, 600, 6001, 600 * 300])
+def test_stft_magphase_recipe(s):
+    """tests/kernels/test_kokoro_kernels.py:529-542: magnitude within 1e-5 * max, wrapped phase within 1e-4 where the
+    bin is significant, against torch.stft (what TorchSTFT.transform computes); both the torch form and the explicit
+    restatement of kernels/cpu/kokoro_signal.cpp:196-272."""
+    r = np.random.default_rng(s)
+    t = np.arange(s)
+    x = (0.3 * np.sin(t * 0.05) + 0.2 * np.sin(t * 0.9) + 0.05 * r.standard_normal(s)).astype(np.float32)
+    x[: s // 7] = 0.0  # silent stretch: DC / Nyquist bins with imag == 0
+    ref = O.stft_magphase(torch.from_numpy(x).double()).numpy()
+    mag, ph = ref[:11], ref[11:]
+    for fn in (O.stft_magphase, O.stft_magphase_explicit):
+        out = fn(torch.from_numpy(x)).numpy()
+        assert out.shape == (22, O.stft_len(s)) == (22, s // 5 + 1)
+        np.testing.assert_allclose(out[:11], mag, atol=1e-5 * mag.max(), rtol=0)
+        sig = mag > 1e-3 * mag.max()
+        dph = np.angle(np.exp(1j * (out[11:].astype(np.float64) - ph)))  # wrapped: the +-pi cut is not an error
+        assert np.abs(dph[sig]).max() < 1e-4
+
+
+def test_stft_frame_algebra():
+    """The frame counts the generator relies on: S = 300 T source samples -> 60 T + 1 STFT frames (the length of
+    `har`) -> 300 T waveform samples after the iSTFT."""
+    for t in (1, 7, 320, 2080):
+        s = 300 * t
+        assert O.stft_len(s) == 60 * t + 1
+        assert O.istft_len(O.stft_len(s)) == s
+
+
 def test_basic_ops_recipes():
     """test_kokoro_kernels.py: snake (:333-341), add3_scale (:322-330), pad_reflect1d (:460-464), adain1d with a
     large mean (:437-449), conv1d incl. the noise_convs[0] shape (:347-383), conv_transpose1d (:404-424)."""
