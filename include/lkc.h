@@ -184,6 +184,12 @@ LKC_API int lkc_istft_logits_f32_cuda(const LkcArgs* a, void* stream);
  * cudaMalloc and must not be inside a stream capture; calls on one device must not overlap in time.
  * The in-kernel random variant (harmonic_source_rng_f32_cpu) is not provided. */
 LKC_API int lkc_harmonic_source_f32_cuda(const LkcArgs* a, void* stream);
+/* The same op (same packing, same kernels, bit-identical result) for callers that must not allocate; it has no
+ * counterpart in the reference. The phase table lives in a fixed device array of the library, so no call path
+ * allocates or frees device memory. Limit: n <= 4096 frames (51 s of audio); larger inputs are rejected. The first
+ * call on a device looks the array up and should come before any stream capture; calls on one device share the
+ * array, so calls that overlap in time race on it. Not in the kernel registry. */
+LKC_API int lkc_harmonic_source_noalloc_f32_cuda(const LkcArgs* a, void* stream);
 
 /* stft_magphase_f32_cpu (kernels/cpu/kokoro_signal.cpp:196-272, adapter :382-385; rule ops/kokoro.py:438-449):
  * torch.stft(center, reflect, periodic hann(n_fft), onesided) -> cat(abs, angle).

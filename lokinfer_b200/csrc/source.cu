@@ -193,3 +193,40 @@ extern "C" LKC_API int lkc_stft_magphase_f32_cuda(const LkcArgs* a, void* stream
   stftMagphaseKernel<<<blocks, 256, smem, S(stream)>>>(F(a, 0), O(a, 1), s, int(nfft), int(hop), frames);
   return launched("stft_magphase_f32_cuda");
 }
+
+// ---- the same op for callers that must not allocate --------------------------------------------------------------
+// lkc_harmonic_source_noalloc_f32_cuda runs the two kernels above with the phase table in a fixed array of this
+// module instead of the grow-only cudaMalloc buffer: no cudaMalloc / cudaFree / allocating library call on any path.
+// Limit: kNoAllocMaxFrames frames (51 s of audio at 80 frames/s; the table is 144 KB of device memory that exists
+// whether or not the entry point is used). Larger inputs are rejected. Nothing has to start at zero: the first kernel
+// writes every table element the second one reads. The first call on a device looks the array's address up
+// (cudaGetSymbolAddress) and should come before any stream capture; calls on one device share the array, so two
+// calls that overlap in time (different streams) race on it.
+namespace lkc {
+namespace {
+constexpr int64_t kNoAllocMaxFrames = 4096;
+static __device__ __align__(256) float gPhaseTable[kNoAllocMaxFrames * kHarmonics];
+}  // namespace
+}  // namespace lkc
+
+extern "C" LKC_API int lkc_harmonic_source_noalloc_f32_cuda(const LkcArgs* a, void* stream) {
+  LKC_REQUIRE(a && a->numPtrs == 5 && a->numInts == 6, "harmonic_source_noalloc_f32_cuda: expected f0 noise w b | out");
+  const int64_t n = a->ints[0];
+  LKC_REQUIRE(n >= 1 && n <= kNoAllocMaxFrames, "harmonic_source_noalloc_f32_cuda: f0 must be f32[n], 1 <= n <= 4096");
+  LKC_REQUIRE(a->ints[1] == n * kUp && a->ints[2] == kHarmonics,
+              "harmonic_source_noalloc_f32_cuda: noise must be f32[300n, 9]");
+  LKC_REQUIRE(a->ints[3] == kHarmonics && a->ints[4] == 1, "harmonic_source_noalloc_f32_cuda: w must be f32[9], b f32[1]");
+  LKC_REQUIRE(a->ints[5] == n * kUp, "harmonic_source_noalloc_f32_cuda: out must be f32[300n]");
+  static float* table[64] = {};  // per device, looked up once
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return failCuda("harmonic_source_noalloc_f32_cuda: cudaGetDevice", e);
+  LKC_REQUIRE(dev >= 0 && dev < 64, "harmonic_source_noalloc_f32_cuda: device index out of range");
+  if (!table[dev]) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), gPhaseTable);
+    if (e != cudaSuccess) return failCuda("harmonic_source_noalloc_f32_cuda: cudaGetSymbolAddress", e);
+    table[dev] = ptr;
+  }
+  return harmonicSourceLaunch(F(a, 0), F(a, 1), F(a, 2), F(a, 3), table[dev], O(a, 4), n, S(stream));
+}
