@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -390,6 +391,49 @@ def run_sweep(args):
                           "tc_status": ops.conv_tc_status()}), flush=True)
 
 
+def run_sweep_convt(args):
+    """ConvTranspose sweep: the generator's two upsamplers (512 -> 256, k 20, s 10, p 5) and (256 -> 128, k 12, s 6,
+    p 3) at Lin = 320 and 2080, one conv_transpose1d_poly launch (leaky prologue, residual, pad_left as in the
+    generator) per step on the tensor-core path; one JSON line per point, FLOPs = 2 Ci Co K Lin."""
+    from lokinfer_b200 import ops
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    dev = torch.device("cuda:0")
+    pk = peaks()
+    peak = pk["bf16_tflops"] / 3.0
+    r = np.random.default_rng(11)
+    for ci, co, k, s, p, pl in ((512, 256, 20, 10, 5, 0), (256, 128, 12, 6, 3, 1)):
+        for lin in (320, 2080) if ci == 512 else (3200, 20800):
+            x = r.standard_normal((ci, lin)).astype(np.float32)
+            w = (r.standard_normal((ci, co, k)) * math.sqrt(s / (ci * k))).astype(np.float32)
+            bias = (r.standard_normal(co) * 0.1).astype(np.float32)
+            res = r.standard_normal((co, lin * s + pl)).astype(np.float32)
+            dx, dw, db, dres = [ops.to_cuda(v, dev) for v in (x, w, bias, res)]
+            wp = ops.convt_poly_weights_cuda(dw, s, p)
+            st = ops.conv_transpose1d_prepare_f32_cuda(dw, s, p)
+
+            def step():
+                return ops.conv_transpose1d_poly_f32_cuda(dx, wp, db, dres, stride=s, padding=p, taps=k // s, slope=0.1,
+                                                          pad_left=pl, state=st)
+
+            for _ in range(args.warmup):
+                step()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                step()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            tf = 2.0 * ci * co * k * lin / (ms * 1e-3) / 1e12
+            print(json.dumps({"sweep": "conv_transpose1d_poly_f32_cuda", "ci": ci, "co": co, "K": k, "stride": s,
+                              "Lin": lin, "ms": ms, "tflops": tf, "frac_split_roofline": tf / peak,
+                              "peak_tflops": peak, "peak_source": pk["source"],
+                              "path": "tcgen05" if st is not None else "cuda-core",
+                              "tc_status": ops.conv_tc_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -398,7 +442,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--t", type=int, default=2080, help="generator input frames per utterance (2080 = 26 s, 320 = 4 s)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--sweep", default=None, choices=["conv"], help="run the conv kernel sweep instead of the generator")
+    ap.add_argument("--sweep", default=None, choices=["conv", "convt"],
+                    help="run the conv / ConvTranspose kernel sweep instead of the generator")
     ap.add_argument("--workload", default="single", choices=["single", "batch64"],
                     help="single: one utterance of --t frames per GPU (default, weak scaling); batch64: 64 utterances of "
                          "120..800 frames sharded across the GPUs (strong scaling)")
@@ -410,6 +455,10 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.sweep == "convt":
+        if rank == 0:
+            run_sweep_convt(args)
         return
     if args.sweep:
         if rank == 0:
