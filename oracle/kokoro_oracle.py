@@ -9,7 +9,9 @@ headers, aarch64 intrinsics, a nanobind extension for Python >= 3.14) and the re
 this path; its kernel tests are seeded recipes that compare each op with a torch float64 composition
 (tests/kernels/test_kokoro_conv_fused.py, tests/kernels/test_kokoro_kernels.py). This oracle is pinned per op
 and per AdaINResBlock1 iteration against those same recipes (tests/test_oracle.py). Whole-generator parity is
-UNPINNED: the reference checks it against the third-party `kokoro==0.7.16` PyTorch modules, which are absent.
+UNPINNED: the reference checks it against the third-party `kokoro==0.7.16` PyTorch modules, which are absent; the
+same holds for harmonic_source (parity unpinned: two independent restatements are checked against each other), while
+stft_magphase is pinned against torch.stft.
 
 Every function takes/returns torch CPU tensors and works in the dtype of its inputs (float32 = the reference's
 precision, float64 = golden).
