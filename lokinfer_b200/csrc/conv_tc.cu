@@ -546,32 +546,51 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
           __syncwarp();
+          if (warp == 0) trace(2, 12, nTr, b);
           // partial statistics of the valid columns of this lane's channel (two passes)
           const float* row = tile + lane * STAGE_PITCH;
-          float s0 = 0.f, s1 = 0.f;
+          // eight shared-memory loads in flight per step: these loops are bound by the load latency, not by issue
+          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
           int j = 0;
-#pragma unroll 2
-          for (; j + 1 < nb; j += 2) s0 += row[j], s1 += row[j + 1];
-          if (j < nb) s0 += row[j];
-          const float m = nb > 0 ? (s0 + s1) / float(nb) : 0.f;
-          float q0 = 0.f, q1 = 0.f;
-          j = 0;
-#pragma unroll 2
-          for (; j + 1 < nb; j += 2) {
-            const float d0 = row[j] - m, d1 = row[j + 1] - m;
-            q0 = fmaf(d0, d0, q0), q1 = fmaf(d1, d1, q1);
+#pragma unroll 1
+          for (; j + 8 <= nb; j += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = row[j + e];
+            s0 += v[0] + v[4], s1 += v[1] + v[5], s2 += v[2] + v[6], s3 += v[3] + v[7];
           }
-          if (j < nb) {
+          for (; j < nb; ++j) s0 += row[j];
+          const float m = nb > 0 ? ((s0 + s1) + (s2 + s3)) / float(nb) : 0.f;
+          float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+          j = 0;
+#pragma unroll 1
+          for (; j + 8 <= nb; j += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = row[j + e] - m;
+            q0 = fmaf(v[0], v[0], q0), q1 = fmaf(v[1], v[1], q1), q2 = fmaf(v[2], v[2], q2), q3 = fmaf(v[3], v[3], q3);
+            q0 = fmaf(v[4], v[4], q0), q1 = fmaf(v[5], v[5], q1), q2 = fmaf(v[6], v[6], q2), q3 = fmaf(v[7], v[7], q3);
+          }
+          for (; j < nb; ++j) {
             const float d = row[j] - m;
             q0 = fmaf(d, d, q0);
           }
-          pMean[b] = m, pM2[b] = q0 + q1;
+          pMean[b] = m, pM2[b] = (q0 + q1) + (q2 + q3);
+          if (warp == 0) trace(2, 13, nTr, b);
           // store with lanes along time
           if (lane < nb && !(dbg & 8)) {
             float* op = a.out + int64_t(coBase) * a.outPitch + tChunk + b * 32 + lane;
             const float* col = tile + lane;
-#pragma unroll 4
-            for (int i = 0; i < rowsValid; ++i) op[int64_t(i) * a.outPitch] = col[i * STAGE_PITCH];
+            int i = 0;
+#pragma unroll 1
+            for (; i + 8 <= rowsValid; i += 8) {
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = col[(i + e) * STAGE_PITCH];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) op[int64_t(i + e) * a.outPitch] = v[e];
+            }
+            for (; i < rowsValid; ++i) op[int64_t(i) * a.outPitch] = col[i * STAGE_PITCH];
           }
           __syncwarp();
           if (warp == 0) trace(2, 10, nTr, b);
@@ -937,11 +956,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
       const long long tStart = clock64();
       for (int tile = blockIdx.x; lane == 0 && tile < numTiles && !dead; tile += gridDim.x) {
         for (int c = 0; c < nChunks16 && !dead; ++c) {
+          trace(0, 10, nTr);
           if (!waitT(&bFull[buf], bufPh, wBf, a.sleepMma)) {
             giveUp(4, 2);
             dead = true;
             break;
           }
+          trace(0, 8, nTr);
           const uint64_t dBc = dB0 + uint32_t(buf) * bufU;
           int kk = 0;
           for (int gi = 0; gi < nTapGroups; ++gi) {
@@ -951,6 +972,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
               dead = true;
               break;
             }
+            trace(0, 9, nTr);
             tcFenceAfter();
             trace(0, kk == 0 ? 1 : 4, nTr, tapIt);
             const uint64_t dA = dA0 + uint32_t(slot) * slotU, dB = dBc + uint32_t(kk * dil);
@@ -1033,6 +1055,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           const bool lastChunk = c == nChunks16 - 1;
           // the hi chain of a drain group (drainN chunks, or what is left of the tile) is complete
           if (g == grpLen - 1 || lastChunk) mmaCommit(hiFull);
+          trace(0, 11, nTr);
           if (lastChunk) mmaCommit(loFull);
           mmaCommit(&bEmpty[buf]);  // activation buffer free once the MMAs have read it
           trace(0, 3, nTr);
