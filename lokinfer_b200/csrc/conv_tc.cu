@@ -203,6 +203,19 @@ __device__ __forceinline__ void mmaF16(uint32_t dTmem, uint64_t descA, uint64_t 
       "l"(descA), "l"(descB), "r"(idesc), "r"(accum)
       : "memory");
 }
+// The same MMA with the descriptors given as (low word, high word): only the low word (address and leading-dimension
+// fields) changes between taps, so the issuing thread does its descriptor arithmetic in 32 bits.
+__device__ __forceinline__ void mmaF16W(uint32_t dTmem, uint32_t aLo, uint32_t aHi, uint32_t bLo, uint32_t bHi,
+                                        uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(dTmem),
+      "r"(aLo), "r"(aHi), "r"(bLo), "r"(bHi), "r"(idesc), "r"(accum)
+      : "memory");
+}
 __device__ __forceinline__ void mmaCommit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar))
                : "memory");
@@ -978,11 +991,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
             const uint64_t dA = dA0 + uint32_t(slot) * slotU, dB = dBc + uint32_t(kk * dil);
             const uint32_t accHi = (kk | g) == 0 ? 0u : 1u, accLo = (kk | c) == 0 ? 0u : 1u;
             const bool needHi = (kk | g) == 0, needLo = (kk | c) == 0;  // Dhi drained / Dlo of the last tile folded
+            const uint32_t aLo = uint32_t(dA), aHi = uint32_t(dA >> 32), bLo = uint32_t(dB), bHi = uint32_t(dB >> 32);
             auto hiTap = [&](int j) {
               const uint64_t dAh = dA + uint32_t(j) * kStageU, dBh = dB + uint32_t(j * dil);
               const uint32_t acc = j == 0 ? accHi : 1u;
               if constexpr (F16) {
-                mmaF16(tmemHi, dAh, dBh, kIdescF16, acc);
+                mmaF16W(tmemHi, aLo + uint32_t(j) * kStageU, aHi, bLo + uint32_t(j * dil), bHi, kIdescF16, acc);
               } else {
                 mmaTf32(tmemHi, dAh, dBh, kIdesc, acc);
                 mmaTf32(tmemHi, dAh + kKsAU, dBh + ksBU, kIdesc, 1u);
@@ -993,8 +1007,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
               const uint64_t dAl = dAh + kLoAU, dBl = dBh + loBU;
               const uint32_t acc = j == 0 ? accLo : 1u;
               if constexpr (F16) {
-                mmaF16(tmemLo, dAl, dBh, kIdescF16, acc);
-                mmaF16(tmemLo, dAh, dBl, kIdescF16, 1u);
+                const uint32_t aj = aLo + uint32_t(j) * kStageU, bj = bLo + uint32_t(j * dil);
+                mmaF16W(tmemLo, aj + kLoAU, aHi, bj, bHi, kIdescF16, acc);
+                mmaF16W(tmemLo, aj, aHi, bj + loBU, bHi, kIdescF16, 1u);
               } else {
                 mmaTf32(tmemLo, dAl, dBh, kIdesc, acc);
                 mmaTf32(tmemLo, dAh, dBl, kIdesc, 1u);
@@ -1030,9 +1045,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
               loTap(0);
               if (nslot == wStages) nslot = 0, nph ^= 1;
               ready = mbarTryWait(&wFull[nslot], nph);
-#pragma unroll
-              for (int j = 1; j < TAP_GROUP; ++j)
-                if (j < gN) loTap(j);
+              static_assert(TAP_GROUP == 4, "the switches below spell out group sizes 1..4");
+              switch (gN) {  // exact tap counts: a predicated-off tap still costs the issuing thread its slots
+                case 4: loTap(1), loTap(2), loTap(3); break;
+                case 3: loTap(1), loTap(2); break;
+                case 2: loTap(1); break;
+                default: break;
+              }
               if (needHi) {
                 if (!waitT(hiEmpty, groupPar ^ 1, wHe, a.sleepMma)) {
                   giveUp(4, 1);
@@ -1041,9 +1060,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
                 }
                 tcFenceAfter();
               }
-#pragma unroll
-              for (int j = 0; j < TAP_GROUP; ++j)
-                if (j < gN) hiTap(j);
+              switch (gN) {
+                case 4: hiTap(0), hiTap(1), hiTap(2), hiTap(3); break;
+                case 3: hiTap(0), hiTap(1), hiTap(2); break;
+                case 2: hiTap(0), hiTap(1); break;
+                default: hiTap(0); break;
+              }
             }
             mmaCommit(&wEmpty[slot]);  // weight slot free once the MMAs have read it
             tapIt += gN;
