@@ -1044,7 +1044,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
             } else {
               loTap(0);
               if (nslot == wStages) nslot = 0, nph ^= 1;
-              ready = mbarTryWait(&wFull[nslot], nph);
               static_assert(TAP_GROUP == 4, "the switches below spell out group sizes 1..4");
               switch (gN) {  // exact tap counts: a predicated-off tap still costs the issuing thread its slots
                 case 4: loTap(1), loTap(2), loTap(3); break;
@@ -1066,6 +1065,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
                 case 2: hiTap(0), hiTap(1); break;
                 default: hiTap(0); break;
               }
+              // first poll of the next slot's barrier, with the whole round queued behind it: a poll of a barrier
+              // that is not complete yet parks the thread for a while, which is free here and was not after the
+              // round's first MMA (with two slots the next one is still being refilled at that point)
+              ready = mbarTryWait(&wFull[nslot], nph);
             }
             mmaCommit(&wEmpty[slot]);  // weight slot free once the MMAs have read it
             tapIt += gN;
