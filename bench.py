@@ -251,7 +251,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     # DRAM bytes (read + written) of ONE launch of the dominant shape (C = 128, L = 124801, K = 11, with
                     # residual) from its ncu capture (summary kept with the other profile summaries); algorithmic: 192 MB
-                    "traffic": 130396416 + 28590336,
+                    "traffic": 130409984 + 26507776,
                     "kernel": "conv1d_{snake,leaky}[_res]_f32_cuda (all fused conv launches of one "
                     "forward)", "peak_source": f"{pk['source']}: bf16 {pk['bf16_tflops']} TF/s / 3 (f16 hi/lo split: 3 MMA products per f32 "
                     "product)",
