@@ -562,31 +562,45 @@ __global__ void __launch_bounds__(NTHREADS, 1) convTcKernel(const TcArgs a) {
           if (warp == 0) trace(2, 12, nTr, b);
           // partial statistics of the valid columns of this lane's channel (two passes)
           const float* row = tile + lane * STAGE_PITCH;
-          // eight shared-memory loads in flight per step: these loops are bound by the load latency, not by issue
-          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-          int j = 0;
-#pragma unroll 1
-          for (; j + 8 <= nb; j += 8) {
-            float v[8];
+          float m, q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+          if (nb == 32) {
+            // full batch: both passes straight from the registers (no shared-memory loads, four independent chains)
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = row[j + e];
-            s0 += v[0] + v[4], s1 += v[1] + v[5], s2 += v[2] + v[6], s3 += v[3] + v[7];
-          }
-          for (; j < nb; ++j) s0 += row[j];
-          const float m = nb > 0 ? ((s0 + s1) + (s2 + s3)) / float(nb) : 0.f;
-          float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
-          j = 0;
-#pragma unroll 1
-          for (; j + 8 <= nb; j += 8) {
-            float v[8];
+            for (int j = 0; j < 32; j += 4)
+              s0 += S[b * 32 + j], s1 += S[b * 32 + j + 1], s2 += S[b * 32 + j + 2], s3 += S[b * 32 + j + 3];
+            m = ((s0 + s1) + (s2 + s3)) * (1.f / 32.f);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = row[j + e] - m;
-            q0 = fmaf(v[0], v[0], q0), q1 = fmaf(v[1], v[1], q1), q2 = fmaf(v[2], v[2], q2), q3 = fmaf(v[3], v[3], q3);
-            q0 = fmaf(v[4], v[4], q0), q1 = fmaf(v[5], v[5], q1), q2 = fmaf(v[6], v[6], q2), q3 = fmaf(v[7], v[7], q3);
-          }
-          for (; j < nb; ++j) {
-            const float d = row[j] - m;
-            q0 = fmaf(d, d, q0);
+            for (int j = 0; j < 32; j += 4) {
+              const float d0 = S[b * 32 + j] - m, d1 = S[b * 32 + j + 1] - m, d2 = S[b * 32 + j + 2] - m,
+                          d3 = S[b * 32 + j + 3] - m;
+              q0 = fmaf(d0, d0, q0), q1 = fmaf(d1, d1, q1), q2 = fmaf(d2, d2, q2), q3 = fmaf(d3, d3, q3);
+            }
+          } else {  // ragged end of a row: rolled loops over the tile, eight loads in flight per step
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+            int j = 0;
+#pragma unroll 1
+            for (; j + 8 <= nb; j += 8) {
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = row[j + e];
+              s0 += v[0] + v[4], s1 += v[1] + v[5], s2 += v[2] + v[6], s3 += v[3] + v[7];
+            }
+            for (; j < nb; ++j) s0 += row[j];
+            m = nb > 0 ? ((s0 + s1) + (s2 + s3)) / float(nb) : 0.f;
+            j = 0;
+#pragma unroll 1
+            for (; j + 8 <= nb; j += 8) {
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = row[j + e] - m;
+              q0 = fmaf(v[0], v[0], q0), q1 = fmaf(v[1], v[1], q1), q2 = fmaf(v[2], v[2], q2), q3 = fmaf(v[3], v[3], q3);
+              q0 = fmaf(v[4], v[4], q0), q1 = fmaf(v[5], v[5], q1), q2 = fmaf(v[6], v[6], q2), q3 = fmaf(v[7], v[7], q3);
+            }
+            for (; j < nb; ++j) {
+              const float d = row[j] - m;
+              q0 = fmaf(d, d, q0);
+            }
           }
           pMean[b] = m, pM2[b] = (q0 + q1) + (q2 + q3);
           if (warp == 0) trace(2, 13, nTr, b);
