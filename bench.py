@@ -15,7 +15,11 @@ data-path collective -> weak scaling; time = max over ranks.
             the split-operand tensor roofline = measured dense bf16 peak / 3 (the kernel spends three f16 MMA products,
             which run at the bf16 rate, per f32 multiply-add: hi*hi, lo*hi, hi*lo).
 `cpu_baseline` / --impl reference: the CPU oracle (torch f32, the basic-op graph the reference's eager PyTorch
-            modules run) on the host cores, on a bounded sample (a shorter utterance of the same model).
+            modules run) on all host cores, one utterance of the same T per step.
+Extra keys on the same line (the other BASELINE configs): `cfg0` one AdaINResBlock1 per kernel size at C = 128,
+L = 19200 / 19201; `cfg1` the 4 s sentence case (T = 320); `sweep` the conv / ConvTranspose kernel sweep of config 4;
+`batch64` config 3 (64 utterances of 120..800 frames, sharded by utterance over the ranks: strong scaling);
+`time_sharded` (N > 1) config 2 with one utterance cut along time over the ranks.
 """
 from __future__ import annotations
 
@@ -36,6 +40,12 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 from lokinfer_b200 import synth  # noqa: E402
+
+# DRAM traffic of one launch of the dominant conv shape (ncu capture, summary under profiles/); algorithmic bytes =
+# x + residual read, out written = 3 * 4 * C * L.
+TRAFFIC = {"bytes": 130409984 + 26507776, "algorithmic": 3 * 4 * 128 * 124801,
+           "kernel": "convTcKernel, conv1d_snake_res, Ci = Co = 128, L = 124801, K = 11, dilation 5 (one launch)",
+           "source": "profiles/conv_tc_c128_k11_L124801.md"}
 
 METRIC = "kokoro_generator_audio_seconds_per_second"
 UNIT = "audio-s/s"
@@ -126,6 +136,166 @@ def cpu_generator_rate(t_sample: int, reps: int, warmup: int, threads: int | Non
     return 300.0 * t_sample / SAMPLE_RATE / sec, sec, cores
 
 
+def _event_ms(fn, reps: int, warmup: int) -> float:
+    """Average milliseconds of fn() over reps calls after warmup calls (CUDA events on the current stream)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def measure_cfg1(gen, dev, steps: int) -> dict:
+    """BASELINE config 1: the 4 s sentence case (T = 320), one CUDA-graph replay per step, inputs resident."""
+    t = 320
+    inp = synth.generator_inputs(t, 7)
+    bufs = gen.capture(t)
+    for k in ("x", "har", "s"):
+        bufs[k].copy_(torch.from_numpy(inp[k]))
+    ms = _event_ms(lambda: bufs["graph"].replay(), max(steps, 10), 3)
+    audio_s = synth.shapes(t)["S"] / SAMPLE_RATE
+    return {"workload": "kokoro_generator_T320", "ms_per_step": ms, "value": audio_s / (ms * 1e-3), "unit": UNIT,
+            "conv_gflop": conv_flops_per_t() * t / 1e9,
+            "conv_tflops_step_bound": conv_flops_per_t() * t / (ms * 1e-3) / 1e12}
+
+
+def measure_cfg0(dev, peak: float) -> dict:
+    """BASELINE config 0: one AdaINResBlock1 (six fused convs + their AdaIN affines) per kernel size at C = 128,
+    L = 19200 and L = 19201 (the generator's stage-1 length for T = 320), rows padded to 16 bytes as in the generator;
+    FLOPs = 6 * 2 * C^2 * k * L per block."""
+    from lokinfer_b200 import Generator, ops
+
+    out = {"workload": "adain_resblock1 C=128 k in (3, 7, 11), dilations (1, 3, 5)", "blocks": []}
+    for l in (19200, 19201):
+        tot_ms, tot_fl = 0.0, 0.0
+        for k in (3, 7, 11):
+            sd, x, s = synth.resblock_case(128, l, k, 300 + k)
+            g = Generator(sd, dev)
+            with ops.padded_rows():
+                dx = ops.to_cuda(x, dev, rows=True)
+                gb = g.style(ops.to_cuda(s, dev))
+                ms = _event_ms(lambda: g.adain_resblock1_fused(dx, gb, "rb", k), 20, 3)
+            fl = 6 * 2.0 * 128 * 128 * k * l
+            tf = fl / (ms * 1e-3) / 1e12
+            out["blocks"].append({"L": l, "k": k, "ms": ms, "tflops": tf, "frac": tf / peak})
+            tot_ms += ms
+            tot_fl += fl
+        out[f"sum_L{l}"] = {"ms": tot_ms, "tflops": tot_fl / (tot_ms * 1e-3) / 1e12,
+                            "frac": tot_fl / (tot_ms * 1e-3) / 1e12 / peak}
+    return out
+
+
+def measure_sweep(dev, peak: float) -> dict:
+    """BASELINE config 4: fused conv1d_snake_res at Cin = Cout in {128, 256, 512}, K in {3, 7, 11}, dilation in
+    {1, 3, 5}, L in {320, 3200, 19200, 124800} (rows 16-byte aligned: every L is a multiple of 4), and the two
+    ConvTranspose upsamplers at Lin in {320, 2080} (x10) / {3200, 20800} (x6). Inputs are seeded normal draws made on
+    the device; 5 launches per point after 2 warm-ups. Rows: [C, L, K, dilation, ms, TFLOP/s, fraction of the
+    split-operand tensor roofline]."""
+    from lokinfer_b200 import ops
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(4)
+    rows = []
+    for c in (128, 256, 512):
+        affine = torch.stack([torch.zeros(c, device=dev), torch.ones(c, device=dev), torch.zeros(c, device=dev)])
+        alpha = torch.rand(c, device=dev, generator=g) + 0.5
+        bias = torch.randn(c, device=dev, generator=g) * 0.01
+        for k in (3, 7, 11):
+            w = torch.randn(c, c, k, device=dev, generator=g) / math.sqrt(c * k)
+            st = ops.conv1d_prepare_f32_cuda(w)
+            for l in (320, 3200, 19200, 124800):
+                x = torch.randn(c, l, device=dev, generator=g)
+                res = torch.randn(c, l, device=dev, generator=g)
+                for d in (1, 3, 5):
+                    pad = d * (k - 1) // 2
+                    ms = _event_ms(lambda: ops.conv1d_snake_f32_cuda(x, w, bias, affine, alpha, residual=res,
+                                                                     padding=pad, dilation=d, state=st), 5, 2)
+                    tf = 2.0 * c * c * k * l / (ms * 1e-3) / 1e12
+                    rows.append([c, l, k, d, round(ms, 5), round(tf, 2), round(tf / peak, 4)])
+                del x, res
+    convt = []
+    for ci, co, k, s, p, pl, lins in ((512, 256, 20, 10, 5, 0, (320, 2080)), (256, 128, 12, 6, 3, 1, (3200, 20800))):
+        w = torch.randn(ci, co, k, device=dev, generator=g) * math.sqrt(s / (ci * k))
+        bias = torch.randn(co, device=dev, generator=g) * 0.1
+        wp = ops.convt_poly_weights_cuda(w, s, p)
+        st = ops.conv_transpose1d_prepare_f32_cuda(w, s, p)
+        for lin in lins:
+            x = torch.randn(ci, lin, device=dev, generator=g)
+            with ops.padded_rows():
+                res = ops.to_cuda(torch.randn(co, lin * s + pl, device=dev, generator=g), dev, rows=True)
+                ms = _event_ms(lambda: ops.conv_transpose1d_poly_f32_cuda(x, wp, bias, res, stride=s, padding=p,
+                                                                          taps=k // s, slope=0.1, pad_left=pl,
+                                                                          state=st), 5, 2)
+            tf = 2.0 * ci * co * k * lin / (ms * 1e-3) / 1e12
+            convt.append([ci, co, k, s, lin, round(ms, 5), round(tf, 2), round(tf / peak, 4)])
+    status = ops.conv_tc_status()
+    by_l = {}
+    for c, l, k, d, ms, tf, fr in rows:
+        by_l.setdefault(l, []).append(fr)
+    return {"conv1d_snake_res": {"columns": ["C", "L", "K", "dilation", "ms", "tflops", "frac"], "rows": rows,
+                                 "mean_frac_by_L": {str(l): round(float(np.mean(v)), 4) for l, v in by_l.items()}},
+            "conv_transpose1d_poly": {"columns": ["Ci", "Co", "K", "stride", "Lin", "ms", "tflops", "frac"],
+                                      "rows": convt},
+            "peak_tflops": peak, "tc_status": status}
+
+
+def measure_batch64(gen, dev, rank: int, world: int, steps: int, warmup: int) -> dict | None:
+    """BASELINE config 3: 64 independent utterances with T ~ U{120..800} (seeded), sharded by utterance across the
+    ranks (longest-processing-time-first on T, lokinfer_b200/sharding.py), no inter-GPU communication. One step =
+    every utterance once (each rank replays the CUDA graphs of its own utterances back to back); strong scaling:
+    the total work is fixed as N grows. Aggregate audio-seconds/sec = all audio seconds / max-over-ranks time.
+    Returns the record on rank 0, None elsewhere."""
+    import torch.distributed as dist
+
+    from lokinfer_b200 import sharding
+
+    lengths = np.random.default_rng(64).integers(120, 801, 64).tolist()
+    plan = sharding.assign(lengths, world)
+    graphs = []
+    for i in plan[rank]:  # one graph per distinct length; inputs are resident in HBM
+        t = lengths[i]
+        inp = synth.generator_inputs(t, 100 + i)
+        bufs = gen.capture(t)
+        for k in ("x", "har", "s"):
+            bufs[k].copy_(torch.from_numpy(inp[k]))
+        graphs.append(bufs["graph"])
+    torch.cuda.synchronize()
+
+    def step():
+        for g in graphs:
+            g.replay()
+
+    for _ in range(max(warmup, 3)):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        step()
+    b.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank != 0:
+        return None
+    total_audio = sharding.audio_seconds(lengths)
+    return {"workload": "kokoro_generator_batch64", "value": total_audio * steps / (float(ms.item()) * 1e-3),
+            "unit": UNIT, "ms_per_step": float(ms.item()) / steps, "scaling": "strong", "utterances": 64,
+            "T_range": [120, 800], "audio_seconds_per_step": total_audio,
+            "sharding": "by utterance, longest first, no communication",
+            "rank_loads_T": sharding.loads(lengths, plan)}
+
+
 def init_nccl(dev):
     """Process group over NCCL (rank / world size / master address from the torchrun environment). NCCL prints its
     version banner on stdout when the communicator is created: stdout is pointed at stderr until the first
@@ -148,7 +318,7 @@ def init_nccl(dev):
 def run_reference(args, rank: int):
     if rank != 0:
         return
-    t_sample = min(args.t, 520)
+    t_sample = args.t
     rate, sec, cores = cpu_generator_rate(t_sample, args.steps, args.warmup, None)
     sample = (f"CPU oracle (torch f32, basic-op graph = what the reference's eager PyTorch modules run), one "
               f"utterance of T={t_sample} ({300 * t_sample / SAMPLE_RATE:.1f} s audio) per step, median of {args.steps}")
@@ -223,6 +393,8 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     h2d = sum(h.numel() * 4 for h in host)
     d2h = audio_host.numel() * 4
 
+    # config 3 on every rank (strong scaling), before the single-rank extras
+    batch64 = None if args.no_extras else measure_batch64(gen, dev, rank, world, 3, 3)
     roofline, cpu_base, kernels = None, None, None
     if rank == 0:
         # per-launch timing of the fused conv kernels (eager pass, CUDA event pair around every launch)
@@ -249,15 +421,19 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         kernels = {n: {"launches": v[0], "ms": round(v[1], 4), "share": round(v[1] / total_ms, 4)}
                    for n, v in sorted(agg.items(), key=lambda kv: -kv[1][1])}
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    # DRAM bytes (read + written) of ONE launch of the dominant shape (C = 128, L = 124801, K = 11, with
-                    # residual) from its ncu capture (summary kept with the other profile summaries); algorithmic: 192 MB
-                    "traffic": 130409984 + 26507776,
+                    # DRAM bytes (read + written) of ONE launch of ONE shape, from its ncu capture: not an aggregate
+                    "traffic": TRAFFIC["bytes"], "traffic_kernel": TRAFFIC["kernel"],
+                    "traffic_source": TRAFFIC["source"], "traffic_algorithmic": TRAFFIC["algorithmic"],
                     "kernel": "conv1d_{snake,leaky}[_res]_f32_cuda (all fused conv launches of one "
                     "forward)", "peak_source": f"{pk['source']}: bf16 {pk['bf16_tflops']} TF/s / 3 (f16 hi/lo split: 3 MMA products per f32 "
                     "product)",
-                    "conv_ms_per_step": conv_ms, "conv_flops_per_step": conv_flops}
+                    "conv_ms_per_step": conv_ms, "conv_flops_per_step": conv_flops,
+                    "note": "conv_ms_per_step sums the launches timed one at a time on one stream (each alone on the "
+                            "GPU); ms_per_step is the captured graph, where independent branches run on side streams "
+                            "and the tail of one persistent conv overlaps the start of another, so it can be smaller "
+                            "than conv_ms_per_step"}
         if world == 1 and not args.no_cpu:
-            t_sample = min(t, 520)
+            t_sample = t
             rate, sec, cores = cpu_generator_rate(t_sample, 3, 1, None)
             cpu_base = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
                         "sample": f"CPU oracle (torch f32, basic-op graph), one utterance of T={t_sample} "
@@ -279,6 +455,11 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         }
         if cpu_base:
             line["cpu_baseline"] = cpu_base
+        if not args.no_extras:
+            line["batch64"] = batch64
+            line["cfg1"] = measure_cfg1(gen, dev, args.steps)
+            line["cfg0"] = measure_cfg0(dev, peak)
+            line["sweep"] = measure_sweep(dev, peak)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -286,62 +467,26 @@ def run_ours(args, rank: int, local_rank: int, world: int):
 
 
 def run_batch(args, rank: int, local_rank: int, world: int):
-    """Config 3: 64 independent utterances with T ~ U{120..800} (seeded), sharded by utterance across the ranks
-    (longest-processing-time-first on T, lokinfer_b200/sharding.py), no inter-GPU communication. One step = every
-    utterance once (each rank replays the CUDA graphs of its own utterances back to back); strong scaling: the total
-    work is fixed as N grows. Reports aggregate audio-seconds/sec = all audio seconds / max-over-ranks time."""
+    """Config 3 alone (see measure_batch64): prints one JSON line with the batch as the workload."""
     import torch.distributed as dist
 
-    from lokinfer_b200 import Generator, sharding
+    from lokinfer_b200 import Generator
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     dev = torch.device(f"cuda:{local_rank}")
     torch.cuda.set_device(dev)
     if world > 1:
         init_nccl(dev)
-    lengths = np.random.default_rng(64).integers(120, 801, 64).tolist()
-    plan = sharding.assign(lengths, world)
-    mine = plan[rank]
     gen = Generator(synth.generator_weights(0), dev)
-    graphs = []
-    for i in mine:  # one graph per distinct length; inputs are resident in HBM
-        t = lengths[i]
-        inp = synth.generator_inputs(t, 100 + i)
-        bufs = gen.capture(t)
-        for k in ("x", "har", "s"):
-            bufs[k].copy_(torch.from_numpy(inp[k]))
-        graphs.append(bufs["graph"])
-    torch.cuda.synchronize()
-
-    def step():
-        for g in graphs:
-            g.replay()
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(args.steps):
-        step()
-    b.record()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    rec = measure_batch64(gen, dev, rank, world, args.steps, args.warmup)
     if rank == 0:
-        total_audio = sharding.audio_seconds(lengths)
         line = {
-            "metric": METRIC, "value": total_audio * args.steps / (float(ms.item()) * 1e-3), "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": float(ms.item()) / args.steps,
+            "metric": METRIC, "value": rec["value"], "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": rec["ms_per_step"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "kokoro_generator_batch64", "utterances": 64, "T_range": [120, 800],
-                       "audio_seconds_per_step": total_audio, "sharding": "by utterance, longest first, no communication",
-                       "rank_loads_T": sharding.loads(lengths, plan)},
+                       "audio_seconds_per_step": rec["audio_seconds_per_step"], "sharding": rec["sharding"],
+                       "rank_loads_T": rec["rank_loads_T"]},
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -366,12 +511,17 @@ def run_sweep(args):
                   for l in (320, 3200, 19200, 124800)]
     for ci, co, l, k, d in points:
         x, w, b, affine, alpha, res = synth.conv_case(ci, co, l, k, 7, big=False)
-        dx, dw, db, daf, dal, dres = [ops.to_cuda(v, dev) for v in (x, w, b, affine, alpha, res)]
+        dw, db, daf, dal = [ops.to_cuda(v, dev) for v in (w, b, affine, alpha)]
+        padded = not args.plain_rows  # rows padded to 16 bytes, as the generator keeps its intermediates
+        with ops.padded_rows(padded):
+            dx, dres = ops.to_cuda(x, dev, rows=True), ops.to_cuda(res, dev, rows=True)
         st = ops.conv1d_prepare_f32_cuda(dw)
         pad = d * (k - 1) // 2
 
         def step():
-            return ops.conv1d_snake_f32_cuda(dx, dw, db, daf, dal, residual=dres, padding=pad, dilation=d, state=st)
+            with ops.padded_rows(padded):
+                return ops.conv1d_snake_f32_cuda(dx, dw, db, daf, dal, residual=dres, padding=pad, dilation=d,
+                                                 state=st)
 
         for _ in range(args.warmup):
             step()
@@ -388,6 +538,7 @@ def run_sweep(args):
         print(json.dumps({"sweep": "conv1d_snake_res_f32_cuda", "ci": ci, "co": co, "L": l, "K": k, "dilation": d,
                           "ms": ms, "tflops": tf, "frac_split_roofline": tf / peak, "peak_tflops": peak,
                           "peak_source": pk["source"], "path": "tcgen05" if st is not None else "cuda-core",
+                          "rows": "padded to 16 bytes (TMA route)" if padded else "contiguous (4-byte route when L is odd)",
                           "tc_status": ops.conv_tc_status()}), flush=True)
 
 
@@ -442,12 +593,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--t", type=int, default=2080, help="generator input frames per utterance (2080 = 26 s, 320 = 4 s)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the other BASELINE configs (cfg0, cfg1, sweep, batch64) carried as extra keys")
     ap.add_argument("--sweep", default=None, choices=["conv", "convt"],
                     help="run the conv / ConvTranspose kernel sweep instead of the generator")
     ap.add_argument("--workload", default="single", choices=["single", "batch64"],
                     help="single: one utterance of --t frames per GPU (default, weak scaling); batch64: 64 utterances of "
                          "120..800 frames sharded across the GPUs (strong scaling)")
     ap.add_argument("--point", default=None, help="single sweep point Ci,Co,L,K,dilation")
+    ap.add_argument("--plain-rows", action="store_true",
+                    help="conv sweep: contiguous rows instead of rows padded to 16 bytes")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -11,8 +11,16 @@
  *   state  : result of the matching *_prepare call, or NULL
  *
  * Layout: frame-rate tensors are channel-first [C, L], row-major, like the reference CPU path.
- * Ownership: the caller owns every buffer; no entry point allocates or frees device memory, and all work is
- * queued on the caller's stream (a cudaStream_t passed as void*) without a host synchronisation.
+ * Row pitch (an extension with no counterpart in the reference, whose tensors are always contiguous): the entry
+ * points that say so accept, after their regular ints, one more int per [C, L] activation tensor = its row pitch in
+ * floats (>= L). Without them rows are L floats apart. A caller that owns its intermediates can round the pitch up
+ * to a multiple of 4 floats and keep base pointers 16-byte aligned: the tensor-core kernels then move those
+ * tensors with the TMA unit (tiled bulk loads and stores) instead of 4-byte accesses. Results do not depend on
+ * the pitch.
+ * Ownership: the caller owns every buffer and all work is queued on the caller's stream (a cudaStream_t passed as
+ * void*). No entry point allocates or frees device memory or synchronises the host, with these exceptions, each
+ * stated at its declaration: lkc_harmonic_source_f32_cuda (grow-only scratch: cudaMalloc when n grows), and the
+ * host-side readers lkc_conv1d_tc_status / lkc_conv1d_tc_profile (they synchronise the device).
  * Errors: every function returns 0 on success and non-zero on failure; lkc_last_error() then returns a
  * message (thread-local, valid until the next failing call on the thread). Nothing throws or aborts.
  * The stats tensors are f32[C, ceil(L / 128), 2] = per-(channel, 128-sample chunk) (mean, M2).
@@ -56,9 +64,11 @@ LKC_API const char* lkc_build_info(void);
 /* ---- basic (unfused) layer ------------------------------------------------------------------------------ */
 
 /* conv1d_f32_cpu (kernels/cpu/kokoro_conv.cpp:32-69, adapter :276-280).
- * ptrs x[Ci,L] w[Co,Ci,K] b[Co] | out[Co,Lo]; ints x(2) w(3) b(1) out(2) dilation padding stride. */
+ * ptrs x[Ci,L] w[Co,Ci,K] b[Co] | out[Co,Lo]; ints x(2) w(3) b(1) out(2) dilation padding stride
+ * [x_pitch out_pitch]. */
 LKC_API int lkc_conv1d_f32_cuda(const LkcArgs* a, void* stream);
-/* conv1d_nobias_f32_cpu (kokoro_conv.cpp:282-286). ptrs x w | out; ints x(2) w(3) out(2) dilation padding stride. */
+/* conv1d_nobias_f32_cpu (kokoro_conv.cpp:282-286). ptrs x w | out; ints x(2) w(3) out(2) dilation padding stride
+ * [x_pitch out_pitch]. */
 LKC_API int lkc_conv1d_nobias_f32_cuda(const LkcArgs* a, void* stream);
 /* conv_transpose1d_f32_cpu (kokoro_conv.cpp:71-95, adapter :288-292).
  * ptrs x[Ci,L] w[Ci,Co,K] b[Co] | out[Co,Lo]; ints x(2) w(3) b(1) out(2) output_padding padding stride. */
@@ -86,7 +96,7 @@ LKC_API int lkc_gemm_bias_f32_cuda(const LkcArgs* a, void* stream);
 /* ---- fused layer ---------------------------------------------------------------------------------------- */
 
 /* channel_stats_f32_cpu (kernels/cpu/kokoro_conv_fused.cpp:631-639, adapter :775-777).
- * ptrs x[C,L] | stats[C,ceil(L/128),2]; ints x(2) stats(3). */
+ * ptrs x[C,L] | stats[C,ceil(L/128),2]; ints x(2) stats(3) [x_pitch]. */
 LKC_API int lkc_channel_stats_f32_cuda(const LkcArgs* a, void* stream);
 /* adain_affine_f32_cpu (kokoro_conv_fused.cpp:641-664, adapter :780-783).
  * ptrs stats[C,S,2] gb[2C] | affine[3,C]; ints stats(3) gb(1) affine(2) length; floats eps. */
@@ -96,9 +106,9 @@ LKC_API int lkc_adain_affine_f32_cuda(const LkcArgs* a, void* stream);
  *   out = (conv1d(act((x - mean) * scale + beta), w) + b [+ res]) [* oscale], stride 1, zero padding applied
  *   after act; stats = chunk stats of out.
  * ptrs x[Ci,L] w[Co,Ci,K] b[Co] affine[3,Ci] [alpha[Ci]] [res[Co,Lo]] | out[Co,Lo] stats[Co,S,2]
- * ints x(2) w(3) b(1) affine(2) [alpha(1)] [res(2)] out(2) stats(3) dilation padding tile
+ * ints x(2) w(3) b(1) affine(2) [alpha(1)] [res(2)] out(2) stats(3) dilation padding tile [x_pitch [res_pitch] out_pitch]
  * floats (name order) [oscale (leaky_res only)] [slope (leaky only)]. `tile` is accepted and ignored.
- * state: NULL, or the LkcConvState returned by lkc_conv1d_prepare_f32_cuda for this weight (tensor-core path). */
+ * state: NULL, or the LkcConvState returned by lkc_conv1d_state_create for this weight (tensor-core path). */
 LKC_API int lkc_conv1d_snake_f32_cuda(const LkcArgs* a, void* stream);
 LKC_API int lkc_conv1d_snake_res_f32_cuda(const LkcArgs* a, void* stream);
 LKC_API int lkc_conv1d_leaky_f32_cuda(const LkcArgs* a, void* stream);
@@ -110,7 +120,7 @@ LKC_API int lkc_conv1d_affine_f32_cuda(const LkcArgs* a, void* stream);
  * ints x(2) x2(2) x3(2) w(3) b(1) affine(2) out(2) stats(3) dilation padding tile; floats in_scale slope. */
 LKC_API int lkc_conv1d_leaky_mean3_f32_cuda(const LkcArgs* a, void* stream);
 
-/* Tensor-core path of the fused conv family (tcgen05, TMEM accumulators, 3xTF32): the counterpart of the
+/* Tensor-core path of the fused conv family (tcgen05, TMEM accumulators, split operands): the counterpart of the
  * reference's prepare / destroy hooks (PrepareFn / DestroyFn, include/lokinfer/runtime/kernel.h:56-58) and of its
  * build-time weight packing (models/kokoro/model.py:60-65). Run once per constant weight:
  *   n = lkc_conv1d_tc_pack_floats(Co, Ci, K)       floats of the pack; 0 = shape not eligible (needs Ci % 16 == 0,
@@ -118,11 +128,15 @@ LKC_API int lkc_conv1d_leaky_mean3_f32_cuda(const LkcArgs* a, void* stream);
  *                                                  multiple of 128 with zero rows inside the pack
  *   lkc_conv1d_tc_pack_f32_cuda: ptrs w[Co,Ci,K] | wp[n]; ints w(3) wp(1)     hi / lo operand split in the UMMA layout
  *   st = lkc_conv1d_state_create(wp, Co, Ci, K)    host-side handle; pass it as LkcArgs.state of the conv1d_* calls
- * A conv call with a state whose shape is eligible ((K - 1) * dilation <= 50, no mean3 input) runs on the tensor
- * cores; anything else runs on the CUDA-core kernel with identical semantics. lkc_conv1d_tc_status reads (and
- * optionally clears) the device status word the kernel sets if one of its bounded waits gave up (0 = ok); it
- * synchronises the device; bit 0x10000 of the word means an activation exceeded the f16 range (65504) under the
- * f16 operand split and was clamped. lkc_set_conv_path chooses the path and the operand format of packs made
+ * A conv call with a state whose shape is eligible ((K - 1) * dilation <= 50, K <= 24 for an f16 pack and <= 12 for
+ * a tf32 pack, no mean3 input) runs on the tensor cores; anything else runs on the CUDA-core kernel with identical
+ * semantics. lkc_conv1d_tc_status waits for all work queued on the current device (cudaDeviceSynchronize; do not call
+ * it inside a stream capture), then reads (and optionally clears) the device status word: low 16 bits = role << 8 |
+ * code of the first bounded wait that gave up (0 = none); bit 0x10000 = an activation exceeded the f16 range (65504)
+ * under the f16 operand split and was clamped; bit 0x20000 = a weight exceeded that range when an f16 pack was made
+ * (pack it again after lkc_set_conv_path(2): the tf32 format has the range of f32). lkc_set_conv_io(1) makes later
+ * launches use 4-byte accesses even for aligned rows, lkc_set_conv_io(0) (default) the TMA unit where rows are
+ * 16-byte aligned (A/B testing). lkc_set_conv_path chooses the path and the operand format of packs made
  * AFTER the call: 0 (default) tensor cores with operands split into f16 hi + f16 lo * 2^-11 (3 kind::f16 MMAs per
  * 16 channels and tap), 2 tensor cores with tf32 hi + tf32 lo (6 kind::tf32 MMAs), 1 the CUDA-core kernel only
  * (A/B testing). lkc_*_pack_floats report sizes for the current format; a state remembers the format of its pack. */
@@ -133,16 +147,13 @@ LKC_API LkcConvState* lkc_conv1d_state_create(const void* wp, int64_t co, int64_
 LKC_API void lkc_conv1d_state_destroy(LkcConvState* st);
 LKC_API int lkc_conv1d_tc_status(int* status, int reset);
 LKC_API int lkc_set_conv_path(int mode);
+LKC_API int lkc_set_conv_io(int mode);
 /* Role-level cycle counters of the tensor-core kernel (the counterpart of the reference's per-kernel profiler,
- * include/lokinfer/runtime/runtime.h:69-74): enable != 0 turns recording on for later launches; counters16 (may be
- * NULL) receives the 16 sums recorded so far (MMA / epilogue / producer / weight-producer wait and phase cycles, see
- * conv_tc.cu) and the counters are cleared. Synchronises the device. */
+ * include/lokinfer/runtime/runtime.h:69-74), present only in a library built with -DLKC_TC_PROF=1 (the product
+ * build returns an error): enable != 0 turns recording on for later launches; counters16 (may be NULL) receives
+ * the 16 sums recorded so far (MMA / epilogue / producer / weight-producer wait and phase cycles, see conv_tc.cu)
+ * and the counters are cleared. Synchronises the device. */
 LKC_API int lkc_conv1d_tc_profile(int enable, int64_t* counters16);
-/* Event timeline of one CTA of the last profiled launch (recorded when enable carries debug flag 16, that is
- * enable = 1 | (16 << 4)): events (may be NULL) receives 6 roles x 512 entries, each clock << 16 | index << 4 | tag, 0 = unused;
- * roles are hi issuer, lo issuer, epilogue warp 0, producer warp 0, weight producer, weight-stage arrival. reset != 0 clears the buffer.
- * Synchronises the device. */
-LKC_API int lkc_conv1d_tc_trace(int64_t* events, int reset);
 
 /* conv_transpose1d_poly[_mean3]_f32_cpu (kernels/cpu/kokoro_conv.cpp:139-229, adapters :294-309):
  *   out = reflect_pad_left(conv_transpose1d(leaky(xin, slope), w, b, stride, padding), pad_left) + res,
@@ -150,7 +161,7 @@ LKC_API int lkc_conv1d_tc_trace(int64_t* events, int reset);
  * wp is this library's polyphase weight pack f32[Ci, stride, taps, Co] made by lkc_convt_poly_pack_f32_cuda
  * (the counterpart of ops.convt_poly_weights_cpu, python/lokinfer/ops/kokoro.py:289-314).
  * ptrs x[Ci,L] wp b[Co] res[Co,L*s+pad_left] | out;  ints x(2) wp(4) b(1) res(2) out(2) pad_left padding stride
- * taps; floats slope.   mean3: ptrs x x2 x3 wp b res | out; ints x(2) x2(2) x3(2) wp(4) b(1) res(2) out(2)
+ * taps [x_pitch res_pitch out_pitch] (padded rows: tensor-core route only); floats slope.   mean3: ptrs x x2 x3 wp b res | out; ints x(2) x2(2) x3(2) wp(4) b(1) res(2) out(2)
  * pad_left padding stride taps; floats in_scale slope. */
 LKC_API int lkc_conv_transpose1d_poly_f32_cuda(const LkcArgs* a, void* stream);
 LKC_API int lkc_conv_transpose1d_poly_mean3_f32_cuda(const LkcArgs* a, void* stream);
@@ -164,15 +175,16 @@ LKC_API int lkc_convt_poly_pack_f32_cuda(const LkcArgs* a, void* stream);
  *   lkc_convt_tc_pack_f32_cuda: ptrs w[Ci,Co,K] | wp[n]; ints w(3) wp(1) padding stride
  *   st = lkc_convt_state_create(wp, Ci, Co, K, stride, padding)   pass as LkcArgs.state of the poly call (the `wp`
  *        operand of that call stays the CUDA-core pack); destroy with lkc_conv1d_state_destroy.
- * The left reflect column is computed as (sum - res[co, 2]) + res[co, 0] here, one rounding more than the CUDA-core
- * kernel's (sum) + res[co, 0]. */
+ * The left reflect column is unpadded[co, 1] + res[co, 0] with the plain conv sum, as in the reference
+ * (kokoro_conv.cpp:226). */
 LKC_API int64_t lkc_convt_tc_pack_floats(int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding);
 LKC_API int lkc_convt_tc_pack_f32_cuda(const LkcArgs* a, void* stream);
 LKC_API LkcConvState* lkc_convt_state_create(const void* wp, int64_t ci, int64_t co, int64_t k, int64_t stride,
                                              int64_t padding);
 
 /* istft_logits_f32_cpu (kernels/cpu/kokoro_signal.cpp:275-359, adapter :388-391).
- * ptrs x[n_fft+2,L] | out[hop*(L-1)]; ints x(2) out(1) hop n_fft. Fails when n_fft/2+1 > 64, like the reference. */
+ * ptrs x[n_fft+2,L] | out[hop*(L-1)]; ints x(2) out(1) hop n_fft [x_pitch]. Fails when n_fft/2+1 > 64, like the
+ * reference. */
 LKC_API int lkc_istft_logits_f32_cuda(const LkcArgs* a, void* stream);
 
 /* harmonic_source_f32_cpu (kernels/cpu/kokoro_signal.cpp:97-190, adapter :370-373; rule python/lokinfer/ops/kokoro.py

@@ -61,8 +61,8 @@ def lib():
         l.lkc_conv1d_tc_status.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_int]
         l.lkc_conv1d_tc_profile.restype = ctypes.c_int
         l.lkc_conv1d_tc_profile.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int64)]
-        l.lkc_conv1d_tc_trace.restype = ctypes.c_int
-        l.lkc_conv1d_tc_trace.argtypes = [ctypes.POINTER(ctypes.c_int64), ctypes.c_int]
+        l.lkc_set_conv_io.restype = ctypes.c_int
+        l.lkc_set_conv_io.argtypes = [ctypes.c_int]
         l.lkc_set_conv_path.restype = ctypes.c_int
         l.lkc_set_conv_path.argtypes = [ctypes.c_int]
         _lib = l

@@ -1,6 +1,9 @@
 """Builds liblkc.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
-    python -m lokinfer_b200.build [--force] [--verbose]
+    python -m lokinfer_b200.build [--force] [--verbose] [--prof]
+
+--prof compiles the tensor-core conv with its role-level cycle counters (-DLKC_TC_PROF=1, lkc_conv1d_tc_profile);
+the default (product) build leaves them out.
 
 One object per .cu (compiled in parallel, rebuilt when the source or a header is newer), linked into
 lokinfer_b200/liblkc.so with the CUDA runtime linked statically, so the library loads on a machine without a
@@ -34,8 +37,8 @@ def _stale(target: Path, deps) -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def _compile(src: Path, obj: Path, verbose: bool):
-    cmd = [NVCC, *ARCH, *FLAGS, "-c", str(src), "-o", str(obj)]
+def _compile(src: Path, obj: Path, verbose: bool, prof: bool = False):
+    cmd = [NVCC, *ARCH, *FLAGS, *(["-DLKC_TC_PROF=1"] if prof else []), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     r = subprocess.run(cmd, capture_output=True, text=True)
@@ -44,17 +47,17 @@ def _compile(src: Path, obj: Path, verbose: bool):
     return src.name, r.stderr
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, prof: bool = False) -> Path:
     headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list((ROOT / "include").glob("*.h"))
     objdir = PKG / "build"
     objdir.mkdir(exist_ok=True)
     jobs = []
     for src in _sources():
         obj = objdir / (src.stem + ".o")
-        if force or verbose or _stale(obj, [src, *headers]):
+        if force or verbose or prof or _stale(obj, [src, *headers]):
             jobs.append((src, obj))
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
-        for name, log in ex.map(lambda j: _compile(j[0], j[1], verbose), jobs):
+        for name, log in ex.map(lambda j: _compile(j[0], j[1], verbose, prof), jobs):
             if verbose and log:
                 print(f"--- {name}\n{log}", file=sys.stderr)
     objs = [objdir / (s.stem + ".o") for s in _sources()]
@@ -67,4 +70,4 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, prof="--prof" in sys.argv))

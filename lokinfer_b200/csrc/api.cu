@@ -30,8 +30,10 @@ int runConvFused(const LkcArgs* a, void* stream, Act act, bool res, const char* 
   const bool hasAlpha = act == Act::Snake;
   const uint32_t nptr = 4 + (hasAlpha ? 1 : 0) + (res ? 1 : 0) + 2;
   const uint32_t nint = 8 + (hasAlpha ? 1 : 0) + (res ? 2 : 0) + 2 + 3 + 3;
-  if (!a || a->numPtrs != nptr || a->numInts != nint) {
-    std::snprintf(gError, sizeof gError, "%s: expected %u pointers and %u ints", name, nptr, nint);
+  const uint32_t npitch = res ? 3 : 2;  // optional trailing ints: row pitches of x, [res,] out (see lkc.h)
+  if (!a || a->numPtrs != nptr || (a->numInts != nint && a->numInts != nint + npitch)) {
+    std::snprintf(gError, sizeof gError, "%s: expected %u pointers and %u ints (+ %u row pitches)", name, nptr, nint,
+                  npitch);
     return 1;
   }
   const int64_t* n = a->ints;
@@ -66,7 +68,14 @@ int runConvFused(const LkcArgs* a, void* stream, Act act, bool res, const char* 
   LKC_REQUIRE(stDims[0] == p.co && stDims[1] == statChunks(p.lo) && stDims[2] == 2,
               "conv1d fused: stats must be f32[Co, ceil(Lo/128), 2]");
   if (res) LKC_REQUIRE(resDims[0] == p.co && resDims[1] == p.lo, "conv1d fused: residual must match the output");
+  if (a->numInts == nint + npitch) {
+    const int64_t* pt = n + nint;
+    p.xPitch = pt[0], p.resPitch = res ? pt[1] : 0, p.outPitch = pt[npitch - 1];
+    LKC_REQUIRE(p.xPitch >= p.l && p.outPitch >= p.lo && (!res || p.resPitch >= p.lo),
+                "conv1d fused: a row pitch is smaller than the row");
+  }
   int fi = 0;
+  if (act == Act::Leaky) LKC_REQUIRE(a->floats, "conv1d fused: missing float attributes");
   if (res && act == Act::Leaky) p.outScale = static_cast<float>(a->floats[fi++]);
   if (act == Act::Leaky) p.slope = static_cast<float>(a->floats[fi++]);
   p.state = a->state;
@@ -75,7 +84,8 @@ int runConvFused(const LkcArgs* a, void* stream, Act act, bool res, const char* 
 
 int runConv1d(const LkcArgs* a, void* stream, bool bias) {
   const uint32_t nptr = bias ? 4 : 3, nint = bias ? 11 : 10;
-  LKC_REQUIRE(a && a->numPtrs == nptr && a->numInts == nint, "conv1d_f32_cuda: bad operand count");
+  LKC_REQUIRE(a && a->numPtrs == nptr && (a->numInts == nint || a->numInts == nint + 2),
+              "conv1d_f32_cuda: bad operand count");
   const int64_t* n = a->ints;
   ConvFusedParams p;
   p.x = F(a, 0), p.w = F(a, 1);
@@ -93,6 +103,10 @@ int runConv1d(const LkcArgs* a, void* stream, bool bias) {
   LKC_REQUIRE(span >= 0, "conv1d_f32_cuda: empty conv output");
   p.lo = span / stride + 1;
   LKC_REQUIRE(n[at - 2] == p.co && n[at - 1] == p.lo, "conv1d_f32_cuda: out must be f32[Co, Lo]");
+  if (a->numInts == nint + 2) {  // optional trailing ints: row pitches of x and out
+    p.xPitch = n[nint], p.outPitch = n[nint + 1];
+    LKC_REQUIRE(p.xPitch >= p.l && p.outPitch >= p.lo, "conv1d_f32_cuda: a row pitch is smaller than the row");
+  }
   return convSimt(p, stride, S(stream));
 }
 
@@ -112,11 +126,11 @@ bool convPathForcedSimt() { return gConvPath == 1; }
 bool convPackF16() { return gConvPath != 2; }
 
 int convFused(const ConvFusedParams& p, cudaStream_t s) {
-  if (gConvPath != 1 && convTcEligible(p)) {
+  if (gConvPath != 1 && p.state != nullptr) {
     const ConvState* st = static_cast<const ConvState*>(p.state);
     LKC_REQUIRE(st->wp && st->stride == 0 && st->co == p.co && st->ci == p.ci && st->k == p.k,
                 "conv1d fused: the prepared state does not match the weight shape");
-    return convTc(p, st->wp, st->f16, s);
+    if (convTcEligible(p, st->f16)) return convTc(p, st->wp, st->f16, s);
   }
   return convSimt(p, 1, s);
 }
@@ -232,9 +246,7 @@ extern "C" LKC_API int lkc_conv1d_tc_profile(int enable, int64_t* counters16) {
   return convTcProfile(enable, reinterpret_cast<long long*>(counters16));
 }
 
-extern "C" LKC_API int lkc_conv1d_tc_trace(int64_t* events, int reset) {
-  return convTcTrace(reinterpret_cast<long long*>(events), reset);
-}
+extern "C" LKC_API int lkc_set_conv_io(int mode) { return convTcSetIo(mode); }
 
 extern "C" LKC_API int lkc_set_conv_path(int mode) {
   LKC_REQUIRE(mode >= 0 && mode <= 2, "set_conv_path: mode must be 0 (f16 split), 1 (CUDA cores only) or 2 (tf32 split)");
@@ -285,4 +297,4 @@ extern "C" LKC_API LkcRunFn lkc_find_kernel(const char* name) {
   return nullptr;
 }
 extern "C" LKC_API const char* lkc_last_error(void) { return gError; }
-extern "C" LKC_API const char* lkc_build_info(void) { return "lkc sm_100a: tcgen05 split-operand fused conv / convT + cuda-core conv/convT/stats/source/stft/istft"; }
+extern "C" LKC_API const char* lkc_build_info(void) { return "lkc sm_100a: tcgen05 split-operand fused conv / convT with TMA tile I/O + cuda-core conv/convT/stats/source/stft/istft"; }

@@ -20,6 +20,7 @@ struct SimtArgs {
   float *out, *stats;
   int ci, co, k, dilation, padding, stride;
   int64_t l, lo, nchunks;
+  int64_t xPitch, resPitch, outPitch;  // row pitches in floats
   float slope, outScale, inScale;
   int win;  // staged window length per input channel
 };
@@ -27,7 +28,7 @@ struct SimtArgs {
 template <int ACT, bool MEAN3>
 __device__ __forceinline__ float loadTransformed(const SimtArgs& p, int c, int64_t pos, float mean, float scale,
                                                  float beta, float alpha, float inv) {
-  const int64_t i = int64_t(c) * p.l + pos;
+  const int64_t i = int64_t(c) * p.xPitch + pos;
   float v = p.x[i];
   if (MEAN3) v = __fmul_rn(__fadd_rn(__fadd_rn(v, p.x2[i]), p.x3[i]), p.inScale);
   v = (v - mean) * scale + beta;
@@ -106,9 +107,9 @@ __global__ void __launch_bounds__(NTHREADS) convSimtKernel(const SimtArgs p) {
       const int tl = tx + 16 * j;
       float v = acc[i][j] + b;
       if (cok && tl < n) {
-        const int64_t o = int64_t(co) * p.lo + t0 + tl;
+        const int64_t o = int64_t(co) * p.outPitch + t0 + tl;
         if (p.residual) {
-          v += p.residual[o];
+          v += p.residual[int64_t(co) * p.resPitch + t0 + tl];
           if (p.outScale != 1.f) v *= p.outScale;
         }
         p.out[o] = v;
@@ -166,6 +167,8 @@ int convSimt(const ConvFusedParams& p, int64_t stride, cudaStream_t s) {
   a.ci = int(p.ci), a.co = int(p.co), a.k = int(p.k), a.dilation = int(p.dilation), a.padding = int(p.padding);
   a.stride = int(stride);
   a.l = p.l, a.lo = p.lo, a.nchunks = statChunks(p.lo);
+  a.xPitch = p.xPitch ? p.xPitch : p.l, a.resPitch = p.resPitch ? p.resPitch : p.lo;
+  a.outPitch = p.outPitch ? p.outPitch : p.lo;
   a.slope = p.slope, a.outScale = p.outScale, a.inScale = p.inScale;
   a.win = (BT - 1) * a.stride + (a.k - 1) * a.dilation + 1;
   const size_t smem = sizeof(float) * (size_t(CIC) * a.win + size_t(CIC) * a.k * BCO);

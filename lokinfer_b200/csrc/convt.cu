@@ -200,7 +200,10 @@ int runPoly(const LkcArgs* a, void* stream, bool mean3) {
   p.bias = F(a, 2 + base);
   p.res = F(a, 3 + base);
   p.out = O(a, 4 + base);
-  LKC_REQUIRE(a->numInts == uint32_t(2 + sh + 4 + 1 + 2 + 2 + 4), "conv_transpose1d_poly: bad ints count");
+  const uint32_t nint = uint32_t(2 + sh + 4 + 1 + 2 + 2 + 4);
+  // optional trailing ints (not with mean3): row pitches of x, res, out; served by the tensor-core route only
+  const bool pitched = !mean3 && a->numInts == nint + 3;
+  LKC_REQUIRE(a->numInts == nint || pitched, "conv_transpose1d_poly: bad ints count");
   const int64_t ci = n[0], l = n[1];
   if (mean3)
     LKC_REQUIRE(n[2] == ci && n[3] == l && n[4] == ci && n[5] == l, "conv_transpose1d_poly_mean3: x2 / x3 must match x");
@@ -231,9 +234,16 @@ int runPoly(const LkcArgs* a, void* stream, bool mean3) {
                 "conv_transpose1d_poly: the prepared state does not match the weight shape");
     if (convtTcEligible(ci, co, taps * s, s, pad)) {
       ConvtParams cp{p.x, p.bias, p.res, p.out, ci, l, co, s, padLeft, p.slope};
+      if (pitched) {
+        cp.xPitch = n[nint], cp.resPitch = n[nint + 1], cp.outPitch = n[nint + 2];
+        LKC_REQUIRE(cp.xPitch >= l && cp.resPitch >= lo && cp.outPitch >= lo,
+                    "conv_transpose1d_poly: a row pitch is smaller than the row");
+      }
       return convtTc(cp, cs->wp, cs->f16, st);
     }
   }
+  LKC_REQUIRE(!pitched || (n[nint] == l && n[nint + 1] == lo && n[nint + 2] == lo),
+              "conv_transpose1d_poly: padded rows need the tensor-core route (a prepared state of an eligible shape)");
   if (taps == 2 && ceilDiv(co, BCO) <= 65535) {
     switch (s) {
       case 2: return launchPoly<2, 2>(p, st);

@@ -19,7 +19,7 @@ constexpr int FB = 128, NTHREADS = 256;
 struct IstftArgs {
   const float* x;
   float* out;
-  int64_t l, len;
+  int64_t l, len, pitch;
   int nfft, hop, bins, nfMax;
 };
 
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(NTHREADS) istftKernel(const IstftArgs a) {
   }
   for (int idx = tid; idx < bins * nf; idx += NTHREADS) {
     const int k = idx / nf, f = idx - k * nf;
-    const float lm = a.x[int64_t(k) * a.l + fLo + f], lp = a.x[int64_t(bins + k) * a.l + fLo + f];
+    const float lm = a.x[int64_t(k) * a.pitch + fLo + f], lp = a.x[int64_t(bins + k) * a.pitch + fLo + f];
     const float mag = expf(lm), ph = sinf(lp);
     float sn, cs;
     sincosf(ph, &sn, &cs);
@@ -91,7 +91,8 @@ __global__ void __launch_bounds__(NTHREADS) istftKernel(const IstftArgs a) {
 using namespace lkc;
 
 extern "C" LKC_API int lkc_istft_logits_f32_cuda(const LkcArgs* a, void* stream) {
-  LKC_REQUIRE(a && a->numPtrs == 2 && a->numInts == 5, "istft_logits_f32_cuda: expected x | out, hop, n_fft");
+  LKC_REQUIRE(a && a->numPtrs == 2 && (a->numInts == 5 || a->numInts == 6),
+              "istft_logits_f32_cuda: expected x | out, hop, n_fft");
   const int64_t rows = a->ints[0], l = a->ints[1], len = a->ints[2], hop = a->ints[3], nfft = a->ints[4];
   LKC_REQUIRE(nfft >= 2 && nfft % 2 == 0 && hop >= 1, "istft_logits_f32_cuda: n_fft must be even, hop >= 1");
   LKC_REQUIRE(nfft / 2 + 1 <= 64, "istft_logits_f32_cuda: n_fft too large (at most 126)");
@@ -100,6 +101,8 @@ extern "C" LKC_API int lkc_istft_logits_f32_cuda(const LkcArgs* a, void* stream)
   LKC_REQUIRE(hop <= 4096, "istft_logits_f32_cuda: hop out of range");
   IstftArgs p;
   p.x = F(a, 0), p.out = O(a, 1), p.l = l, p.len = len;
+  p.pitch = a->numInts == 6 ? a->ints[5] : l;  // optional trailing int: row pitch of x
+  LKC_REQUIRE(p.pitch >= l, "istft_logits_f32_cuda: the row pitch is smaller than the row");
   p.nfft = int(nfft), p.hop = int(hop), p.bins = int(nfft / 2 + 1);
   p.nfMax = int(FB + (nfft + hop - 1) / hop + 2);
   const size_t smem = sizeof(float) * (size_t(2) * p.bins * p.nfft + p.nfft + size_t(2) * p.bins * p.nfMax +

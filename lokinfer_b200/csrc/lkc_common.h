@@ -52,6 +52,8 @@ struct ConvFusedParams {
   float* out = nullptr;
   float* stats = nullptr;  // may be null
   int64_t ci = 0, l = 0, co = 0, k = 0, dilation = 1, padding = 0, lo = 0;
+  // Row pitches in floats of the [C, L] tensors x (x2, x3 share it), residual and out; 0 = contiguous rows.
+  int64_t xPitch = 0, resPitch = 0, outPitch = 0;
   Act act = Act::None;
   float slope = 0.f, outScale = 1.f, inScale = 1.f;
   const void* state = nullptr;
@@ -62,7 +64,7 @@ int convFused(const ConvFusedParams& p, cudaStream_t s);
 // CUDA-core implicit-GEMM conv for any shape (conv_simt.cu). stride > 1 only for the plain conv1d.
 int convSimt(const ConvFusedParams& p, int64_t stride, cudaStream_t s);
 
-// Tensor-core (tcgen05, 3xTF32) fused conv (conv_tc.cu). `state` of ConvFusedParams is an LkcConvState.
+// Tensor-core (tcgen05, split operands) fused conv (conv_tc.cu). `state` of ConvFusedParams is an LkcConvState.
 struct ConvState {
   const float* wp;  // packed weights (convTcPack / convtTcPack)
   int64_t co, ci, k;
@@ -75,6 +77,7 @@ struct ConvtParams {
   float* out;
   int64_t ci, l, co, stride, padLeft;
   float slope;
+  int64_t xPitch = 0, resPitch = 0, outPitch = 0;  // row pitches in floats; 0 = contiguous rows
 };
 bool convtTcEligible(int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding);
 int64_t convtTcPackFloats(int64_t ci, int64_t co, int64_t stride, bool f16);
@@ -83,12 +86,12 @@ int convtTcPack(const float* w, float* wp, int64_t ci, int64_t co, int64_t k, in
 int convtTc(const ConvtParams& p, const float* wp, bool f16, cudaStream_t s);
 bool convPathForcedSimt();
 bool convPackF16();  // operand format new packs are made in (lkc_set_conv_path)
-bool convTcEligible(const ConvFusedParams& p);
+bool convTcEligible(const ConvFusedParams& p, bool f16);
 int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k, bool f16);
 int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, bool f16, cudaStream_t s);
 int convTc(const ConvFusedParams& p, const float* wp, bool f16, cudaStream_t s);
 int convTcStatus(int* out, bool reset);
-int convTcTrace(long long* out, int reset);
+int convTcSetIo(int mode);
 int convTcProfile(int enable, long long* out16);
 
 }  // namespace lkc

@@ -110,9 +110,10 @@ class Generator:
         src = ops.harmonic_source_f32_cuda(f0, noise, w9, self.w["m_source.l_linear.bias"].reshape(1))
         return ops.stft_magphase_f32_cuda(src, n_fft=20, hop=5)
 
-    def forward(self, x, har, s, fused=True, outputs=("audio",), concurrent=True):
+    def forward(self, x, har, s, fused=True, outputs=("audio",), concurrent=True, pad_rows=True):
         """x f32[512, T], har f32[22, 60 T + 1], s f32[128] (cuda tensors) -> the named outputs
-        ("audio" f32[300 T], "post" f32[22, 60 T + 1]).
+        ("audio" f32[300 T], "post" f32[22, 60 T + 1]; with pad_rows the 2-D outputs are [:, :L] views of buffers
+        whose rows are padded to a multiple of 4 floats).
 
         The op sequence is the reference's (model.py:735-781). With concurrent=True (fused graph only) the branches
         that do not depend on each other are queued on side streams, forked from and joined back to torch's current
@@ -123,6 +124,11 @@ class Generator:
         ops.check(x.dim() == 2 and x.shape[0] == 512, "x must be f32[512, T]")
         sh = shapes(int(x.shape[1]))
         ops.check(tuple(har.shape) == (22, sh["L1"]), f"har must be f32[22, {sh['L1']}]")
+        if fused and pad_rows and not ops._pad_rows:
+            # the generator owns every intermediate: rows padded to 16 bytes, so that the tensor-core kernels move
+            # them with the TMA unit (values do not depend on the pitch)
+            with ops.padded_rows():
+                return self.forward(x, har, s, fused, outputs, concurrent, pad_rows)
         gb = self.style(s)
         cur = torch.cuda.current_stream(self.device)
         par = fused and concurrent
@@ -164,7 +170,7 @@ class Generator:
                     xin, self.ups_wp[i], w[f"ups.{i}.bias"], noise[i], stride=u, padding=(k_up - u) // 2,
                     taps=k_up // u, slope=0.1, pad_left=1 if i == 1 else 0, state=self.ups_state[i])
                 xst = ops.channel_stats_f32_cuda(x)
-                keep += [x, xst, rb]
+                keep += [x, xst, *(rb or [])]
                 new_rb = [None, None, None]
                 if par:
                     side[2].wait_stream(cur)
@@ -225,7 +231,8 @@ class Generator:
             return self._graphs[t]
         sh = shapes(t)
         dev = self.device
-        bufs = {"x": torch.zeros(512, t, device=dev), "har": torch.zeros(22, sh["L1"], device=dev),
+        pitch = -(-t // ops.ROW_ALIGN) * ops.ROW_ALIGN  # rows of x start on 16-byte boundaries for any t
+        bufs = {"x": torch.zeros(512, pitch, device=dev)[:, :t], "har": torch.zeros(22, sh["L1"], device=dev),
                 "s": torch.zeros(128, device=dev)}
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))

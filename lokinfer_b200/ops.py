@@ -6,8 +6,17 @@ and error messages, under the name `<op>_f32_cuda` instead of `<op>_f32_cpu`. Op
 torch tensors on a CUDA device; results are new tensors (the wrapper plays the runtime's role of allocating the
 outs, src/runtime/executable.cpp:583-654) and every launch goes to torch's current stream through the C-ABI in
 include/lkc.h. Shape errors raise OpError before anything is launched (python/lokinfer/ops/_def.py:12-19).
+
+Padded rows (no counterpart in the reference, whose tensors are always contiguous): inside `with padded_rows():`
+every [C, L] result is allocated with its row pitch rounded up to 4 floats and returned as the [:, :L] view, and the
+ops that take a row pitch (the conv family, channel_stats, conv_transpose1d_poly, istft_logits, add3_scale) accept
+such views as operands. Rows then start on 16-byte boundaries, which lets the tensor-core kernels move them with
+the TMA unit; values never depend on the pitch. Outs come from `allocator` (default: torch.empty), the hook a
+planned arena plugs into.
 """
 from __future__ import annotations
+
+import contextlib
 
 import torch
 
@@ -35,10 +44,15 @@ def _int(v, name):
     return int(v)
 
 
+def _row_pitched(x) -> bool:
+    """[C, L] view of a [C, pitch] buffer: unit stride along time, rows at least L apart."""
+    return x.dim() == 2 and x.stride(1) == 1 and x.stride(0) >= x.shape[1]
+
+
 def _f32(*xs, rank=None):
     for x in xs:
         check(isinstance(x, torch.Tensor) and x.dtype == torch.float32, "expected f32 tensor operands")
-        check(x.is_contiguous(), "expected contiguous tensors")
+        check(x.is_contiguous() or _row_pitched(x), "expected contiguous tensors (or [C, L] views with padded rows)")
         if rank is not None:
             check(x.dim() == rank, f"expected rank-{rank} operands, got {tuple(x.shape)}")
 
@@ -82,11 +96,26 @@ class Profile:
 _profile = None
 
 
+# Kernels that take row pitches: positions (in operands + outs order) of their [C, L] activation tensors. The
+# pitches are appended to the ints only when one of them differs from the row length.
+_PITCHED = {
+    "conv1d_f32_cuda": (0, 3), "conv1d_nobias_f32_cuda": (0, 2), "channel_stats_f32_cuda": (0,),
+    "conv1d_snake_f32_cuda": (0, 5), "conv1d_snake_res_f32_cuda": (0, 5, 6),
+    "conv1d_leaky_f32_cuda": (0, 4), "conv1d_leaky_res_f32_cuda": (0, 4, 5), "conv1d_affine_f32_cuda": (0, 4),
+    "conv_transpose1d_poly_f32_cuda": (0, 3, 4), "istft_logits_f32_cuda": (0,),
+}
+
+
 def _run(name, operands, outs, attrs_int=(), attrs_float=(), state=None):
     ts = list(operands) + list(outs)
     check(all(t.is_cuda and t.device == ts[0].device for t in ts),
           f"{name}: operands must live on one cuda device (use to_cuda); there is no CPU path")
     ints = [d for t in ts for d in t.shape] + list(attrs_int)
+    pitched = _PITCHED.get(name, ())
+    for i, t in enumerate(ts):
+        check(t.is_contiguous() or i in pitched, f"{name}: operand {i} must be contiguous")
+    if any(not ts[i].is_contiguous() for i in pitched):
+        ints += [int(ts[i].stride(0)) for i in pitched]
     with torch.cuda.device(ts[0].device):
         prof = _profile
         if prof is None:
@@ -106,14 +135,73 @@ def _run(name, operands, outs, attrs_int=(), attrs_float=(), state=None):
         prof.calls.append((name, ints, a, b))
 
 
-def _new(like, shape):
+ROW_ALIGN = 4  # floats: 16-byte rows
+
+
+def _torch_alloc(shape, device):
+    return torch.empty(shape, dtype=torch.float32, device=device)
+
+
+allocator = _torch_alloc  # (shape, device) -> contiguous f32 tensor; replaced by a planned arena (see arena.py)
+_pad_rows = False
+
+
+@contextlib.contextmanager
+def padded_rows(enable=True):
+    """Inside the block [C, L] results get a row pitch rounded up to ROW_ALIGN floats (see the module docstring)."""
+    global _pad_rows
+    prev, _pad_rows = _pad_rows, bool(enable)
+    try:
+        yield
+    finally:
+        _pad_rows = prev
+
+
+@contextlib.contextmanager
+def use_allocator(fn):
+    """Routes the allocation of every result inside the block through fn(shape, device)."""
+    global allocator
+    prev, allocator = allocator, fn
+    try:
+        yield
+    finally:
+        allocator = prev
+
+
+def empty_rows(c, l, device):
+    """f32[c, l] with padded rows when padded_rows() is active (else contiguous)."""
+    if _pad_rows:
+        pitch = ceildiv(int(l), ROW_ALIGN) * ROW_ALIGN
+        return allocator((int(c), pitch), device)[:, :int(l)]
+    return allocator((int(c), int(l)), device)
+
+
+def _new(like, shape, rows=False):
+    """Storage of one result. rows=True marks a [C, L] activation of an op that takes row pitches: it gets padded
+    rows inside padded_rows()."""
     # Shape rules run on any device (so they can be exercised without a GPU); storage is only made on cuda.
-    return torch.empty(shape, dtype=torch.float32, device=like.device if like.is_cuda else "meta")
+    if not like.is_cuda:
+        return torch.empty(tuple(shape), dtype=torch.float32, device="meta")
+    if rows:
+        return empty_rows(shape[0], shape[1], like.device)
+    return allocator(tuple(int(d) for d in shape), like.device)
 
 
-def to_cuda(a, device="cuda"):
-    """Host array / tensor -> contiguous f32 tensor on the cuda device (the `sync cpu_to_cuda` copy)."""
+def _full_rows(x):
+    """The [C, pitch] buffer behind a [C, L] view with padded rows (the view must start at its first element)."""
+    c, pitch = int(x.shape[0]), int(x.stride(0))
+    check(x.untyped_storage().nbytes() >= (x.storage_offset() + c * pitch) * 4, "padded view without its full rows")
+    return torch.as_strided(x, (c, pitch), (pitch, 1))
+
+
+def to_cuda(a, device="cuda", rows=False):
+    """Host array / tensor -> contiguous f32 tensor on the cuda device (the `sync cpu_to_cuda` copy). rows=True: a
+    [C, L] array goes into a buffer with padded rows when padded_rows() is active."""
     t = torch.as_tensor(a, dtype=torch.float32)
+    if rows and t.dim() == 2 and _pad_rows:
+        out = empty_rows(t.shape[0], t.shape[1], torch.device(device))
+        out.copy_(t)
+        return out
     return t.to(device).contiguous()
 
 
@@ -149,10 +237,17 @@ def add_f32_cuda(a, b):
 
 
 def add3_scale_f32_cuda(a, b, c, scale):
-    """(a + b + c) * scale, any shape."""
+    """(a + b + c) * scale, any shape. [C, L] views with padded rows of one pitch are processed with their padding
+    (the op is elementwise, so the padding columns only cost their bandwidth)."""
     _f32(a, b, c)
     check(a.shape == b.shape and a.shape == c.shape,
           f"shape mismatch: {tuple(a.shape)}, {tuple(b.shape)}, {tuple(c.shape)}")
+    if a.is_cuda and not (a.is_contiguous() and b.is_contiguous() and c.is_contiguous()):
+        check(a.stride() == b.stride() == c.stride(), "padded operands must share one row pitch")
+        fa, fb, fc = _full_rows(a), _full_rows(b), _full_rows(c)
+        out = allocator(tuple(fa.shape), a.device)
+        _run("add3_scale_f32_cuda", [fa, fb, fc], [out], attrs_float=[_float(scale, "scale")])
+        return out[:, :a.shape[1]]
     out = _new(a, a.shape)
     _run("add3_scale_f32_cuda", [a, b, c], [out], attrs_float=[_float(scale, "scale")])
     return out
@@ -190,7 +285,7 @@ def conv1d_f32_cuda(x, w, b, stride=1, padding=0, dilation=1):
     shape = _conv_rule(x, w, dilation=dilation, padding=padding, stride=stride)
     _f32(b, rank=1)
     check(b.shape[0] == w.shape[0], "bias must be f32[Co]")
-    out = _new(x, shape)
+    out = _new(x, shape, rows=True)
     _run("conv1d_f32_cuda", [x, w, b], [out], attrs_int=[dilation, padding, stride])
     return out
 
@@ -199,7 +294,7 @@ def conv1d_nobias_f32_cuda(x, w, stride=1, padding=0, dilation=1):
     """F.conv1d without bias."""
     stride, padding, dilation = _int(stride, "stride"), _int(padding, "padding"), _int(dilation, "dilation")
     shape = _conv_rule(x, w, dilation=dilation, padding=padding, stride=stride)
-    out = _new(x, shape)
+    out = _new(x, shape, rows=True)
     _run("conv1d_nobias_f32_cuda", [x, w], [out], attrs_int=[dilation, padding, stride])
     return out
 
@@ -255,7 +350,8 @@ def conv_transpose1d_poly_f32_cuda(x, wp, b, res, stride, padding, taps, slope, 
     check(pad_left in (0, 1), "pad_left must be 0 or 1")
     lo = x.shape[1] * stride + pad_left
     check(res.shape[0] == b.shape[0] and res.shape[1] == lo, "residual must be f32[Co, L*s + pad_left]")
-    out = _new(x, (b.shape[0], lo))
+    # padded rows only on the tensor-core route (the CUDA-core kernels of this op take contiguous rows)
+    out = _new(x, (b.shape[0], lo), rows=state is not None and mean3 is None)
     at = [pad_left, padding, stride, taps]
     if mean3 is not None:
         x2, x3, sc = mean3
@@ -371,11 +467,12 @@ def _fused_attrs(x, w, padding, dilation, tile):
 
 
 class ConvState:
-    """Prepared state of one constant conv weight for the tensor-core kernel: the hi / lo TF32 pack in the UMMA
+    """Prepared state of one constant conv weight for the tensor-core kernel: the hi / lo operand pack in the UMMA
     layout plus the host handle passed as `state` (the reference's prepare hook result, kernel.h:56-58)."""
 
     def __init__(self, handle, wp, shape):
         self.handle, self.wp, self.shape = handle, wp, shape
+        self.fmt = "tf32" if _conv_path == "tf32" else "f16"  # operand format of the pack
 
     def __del__(self):
         try:
@@ -391,16 +488,21 @@ def conv1d_prepare_f32_cuda(w):
     hoisted weight preparation, docs/passes/hoist-init.md). Returns None when the shape is served by the CUDA-core
     kernel instead (Ci % 16 != 0 or K > 64)."""
     _f32(w, rank=3)
+    check(w.is_contiguous(), "w must be contiguous")
     co, ci, k = (int(d) for d in w.shape)
-    n = int(_lib.lib().lkc_conv1d_tc_pack_floats(co, ci, k))
-    if n == 0:
-        return None
-    wp = _new(w, (n,))
-    _run("conv1d_tc_pack_f32_cuda", [w], [wp])
-    handle = _lib.lib().lkc_conv1d_state_create(wp.data_ptr(), co, ci, k)
-    if not handle:
-        raise _lib.LkcError(_lib.last_error())
-    return ConvState(handle, wp, (co, ci, k))
+
+    def pack():
+        n = int(_lib.lib().lkc_conv1d_tc_pack_floats(co, ci, k))
+        if n == 0:
+            return None
+        wp = torch.empty((n,), dtype=torch.float32, device=w.device)
+        _run("conv1d_tc_pack_f32_cuda", [w], [wp])
+        handle = _lib.lib().lkc_conv1d_state_create(wp.data_ptr(), co, ci, k)
+        if not handle:
+            raise _lib.LkcError(_lib.last_error())
+        return ConvState(handle, wp, (co, ci, k))
+
+    return _pack_checked(pack)
 
 
 def conv_transpose1d_prepare_f32_cuda(w, stride, padding):
@@ -409,21 +511,51 @@ def conv_transpose1d_prepare_f32_cuda(w, stride, padding):
     tensor-core path takes stride 6 or 10 with K = 2 stride, 2 padding = stride, Ci % 16 == 0)."""
     _f32(w, rank=3)
     s, p = _int(stride, "stride"), _int(padding, "padding")
+    check(w.is_contiguous(), "w must be contiguous")
     ci, co, k = (int(d) for d in w.shape)
-    n = int(_lib.lib().lkc_convt_tc_pack_floats(ci, co, k, s, p))
-    if n == 0:
-        return None
-    wp = _new(w, (n,))
-    _run("convt_tc_pack_f32_cuda", [w], [wp], attrs_int=[p, s])
-    handle = _lib.lib().lkc_convt_state_create(wp.data_ptr(), ci, co, k, s, p)
-    if not handle:
-        raise _lib.LkcError(_lib.last_error())
-    return ConvState(handle, wp, (ci, co, k, s))
+
+    def pack():
+        n = int(_lib.lib().lkc_convt_tc_pack_floats(ci, co, k, s, p))
+        if n == 0:
+            return None
+        wp = torch.empty((n,), dtype=torch.float32, device=w.device)
+        _run("convt_tc_pack_f32_cuda", [w], [wp], attrs_int=[p, s])
+        handle = _lib.lib().lkc_convt_state_create(wp.data_ptr(), ci, co, k, s, p)
+        if not handle:
+            raise _lib.LkcError(_lib.last_error())
+        return ConvState(handle, wp, (ci, co, k, s))
+
+    return _pack_checked(pack)
+
+
+STATUS_F16_ACT, STATUS_F16_WEIGHTS = 0x10000, 0x20000
+_conv_path = "auto"
+
+
+def _pack_checked(pack):
+    """Runs a weight pack and, if the f16 split reported a weight beyond the f16 range (status bit 0x20000: the value
+    was clamped), packs the weight again in the tf32 format, which has the range of f32. Reads the status word, so it
+    synchronises the device: packing is init-time work."""
+    with torch.cuda.device(torch.cuda.current_device()):
+        st = pack()
+        if st is None or _conv_path != "auto":
+            return st
+        status = conv_tc_status()
+        if status & ~STATUS_F16_WEIGHTS:
+            raise RuntimeError(f"tensor-core conv kernels reported status {status:#x} before this weight was packed")
+        if status & STATUS_F16_WEIGHTS:
+            set_conv_path("tf32")
+            try:
+                st = pack()
+            finally:
+                set_conv_path("auto")
+        return st
 
 
 def conv_tc_status(reset=True) -> int:
-    """Status word of the tensor-core conv kernel on the current device (0 = every bounded wait completed).
-    Synchronises the device."""
+    """Status word of the tensor-core conv kernels on the current device after everything queued on it has finished
+    (the call synchronises the device): 0 = ok; low 16 bits = the first bounded wait that gave up; 0x10000 = an
+    activation beyond the f16 range was clamped; 0x20000 = a weight beyond the f16 range was clamped in a pack."""
     import ctypes
     v = ctypes.c_int(0)
     if _lib.lib().lkc_conv1d_tc_status(ctypes.byref(v), 1 if reset else 0) != 0:
@@ -433,12 +565,13 @@ def conv_tc_status(reset=True) -> int:
 
 TC_PROFILE_FIELDS = ("mma_wait_act", "mma_wait_drain", "mma_wait_weights", "mma_wait_lofold", "mma_total",
                      "epi_wait_hi", "epi_wait_lo", "epi_preload", "epi_final", "epi_total",
-                     "pro_wait_free", "pro_wait_cpasync", "pro_transform", "pro_total", "wpro_wait_free", "wpro_total")
+                     "pro_wait_free", "pro_wait_raw", "pro_transform", "pro_total", "wpro_wait_free", "wpro_total")
 
 
 def conv_tc_profile(enable: bool) -> dict:
     """Turns the tensor-core kernel's role-level cycle counters on / off and returns (then clears) what was recorded:
-    cycles summed over CTAs and launches, one representative warp per role. Synchronises the device."""
+    cycles summed over CTAs and launches, one representative warp per role. Synchronises the device. Only in a
+    library built with LKC_TC_PROF=1 (python -m lokinfer_b200.build --prof); the product build raises."""
     import ctypes
     buf = (ctypes.c_int64 * 16)()
     if _lib.lib().lkc_conv1d_tc_profile(1 if enable else 0, buf) != 0:
@@ -451,9 +584,20 @@ def set_conv_path(mode: str) -> None:
     split into f16 hi/lo halves; "tf32" = the same with tf32 hi/lo halves; "simt" = CUDA cores only. The operand
     format is fixed when a state is prepared, so states made under "auto" keep the f16 split after a switch to
     "tf32" and the other way round."""
+    global _conv_path
     modes = {"auto": 0, "simt": 1, "tf32": 2}
     check(mode in modes, "mode must be 'auto', 'simt' or 'tf32'")
     if _lib.lib().lkc_set_conv_path(modes[mode]) != 0:
+        raise _lib.LkcError(_lib.last_error())
+    _conv_path = mode
+
+
+def set_conv_io(mode: str) -> None:
+    """Global-memory route of the tensor-core kernels: "tma" (default) = tiled bulk loads / stores for every tensor
+    whose rows are 16-byte aligned, "plain" = 4-byte accesses for all (the A/B partner of the parity tests)."""
+    modes = {"tma": 0, "plain": 1}
+    check(mode in modes, "mode must be 'tma' or 'plain'")
+    if _lib.lib().lkc_set_conv_io(modes[mode]) != 0:
         raise _lib.LkcError(_lib.last_error())
 
 
@@ -472,7 +616,7 @@ def conv1d_snake_f32_cuda(x, w, b, affine, alpha, residual=None, padding=0, dila
     _f32(alpha, rank=1) if isinstance(alpha, torch.Tensor) else check(False, "alpha must be f32[Ci]")
     check(alpha.shape[0] == x.shape[0], "alpha must be f32[Ci]")
     oshape, sshape = _fused_rule(x, w, b, affine, [alpha], **at)
-    out, stats = _new(x, oshape), _new(x, sshape)
+    out, stats = _new(x, oshape, rows=True), _new(x, sshape)
     ai = [at["dilation"], at["padding"], at["tile"]]
     if residual is None:
         _run("conv1d_snake_f32_cuda", [x, w, b, affine, alpha], [out, stats], attrs_int=ai, state=_state_of(w, state))
@@ -490,7 +634,7 @@ def conv1d_leaky_f32_cuda(x, w, b, affine, slope=0.1, residual=None, out_scale=1
     at = _fused_attrs(x, w, padding, dilation, tile)
     slope, out_scale = _float(slope, "slope"), _float(out_scale, "out_scale")
     oshape, sshape = _fused_rule(x, w, b, affine, [], **at)
-    out, stats = _new(x, oshape), _new(x, sshape)
+    out, stats = _new(x, oshape, rows=True), _new(x, sshape)
     ai = [at["dilation"], at["padding"], at["tile"]]
     if residual is None:
         check(out_scale == 1.0, "out_scale needs a residual")
@@ -508,7 +652,7 @@ def conv1d_affine_f32_cuda(x, w, b, affine, padding=0, dilation=1, tile=None, st
     """conv1d((x - mean) * scale + beta, w) + b -> (out, stats)."""
     at = _fused_attrs(x, w, padding, dilation, tile)
     oshape, sshape = _fused_rule(x, w, b, affine, [], **at)
-    out, stats = _new(x, oshape), _new(x, sshape)
+    out, stats = _new(x, oshape, rows=True), _new(x, sshape)
     _run("conv1d_affine_f32_cuda", [x, w, b, affine], [out, stats],
          attrs_int=[at["dilation"], at["padding"], at["tile"]], state=_state_of(w, state))
     return out, stats

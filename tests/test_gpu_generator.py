@@ -67,6 +67,81 @@ def test_generator_vs_oracle(cuda, gen, t, fused):
     assert np.abs(audio - ref64).max() <= WAVE_MAXABS
 
 
+def _oracle_stages(inp, dt, fused=True):
+    sd = synth.generator_weights(0)
+    return O.generator(sd, O.T(inp["x"], dt), O.T(inp["har"], dt), O.T(inp["s"], dt), fused=fused, stages=True)
+
+
+@pytest.mark.parametrize("t", [320, 333, 797])
+def test_generator_baseline_configs_vs_oracle(cuda, gen, t):
+    """BASELINE config 1 (the 4 s sentence case, T = 320) and two utterance lengths of config 3 (T in 120..800, one
+    odd: odd T makes every row pitch of stage 0 odd as well) against the CPU oracle in float32 and float64:
+    the eager forward with concurrent streams, the same forward on one stream, and the captured-graph path with
+    host buffers (Generator.synthesize). Bars: waveform max-abs <= 1e-4, conv_post logits rel-L2, and the GPU's
+    error against float64 within 2x the float32 oracle's own."""
+    inp, d = _inputs(cuda, t, seed=40 + t)
+    post, audio = gen.forward(*d, outputs=("post", "audio"))
+    audio_1s = gen.forward(*d, concurrent=False)
+    host = [torch.from_numpy(inp[k]).pin_memory() for k in ("x", "har", "s")]
+    audio_graph = gen.synthesize(*host).numpy().copy()
+    sh = synth.shapes(t)
+    assert tuple(audio.shape) == (sh["S"],) and tuple(post.shape) == (22, sh["L1"])
+    r32, r64 = _oracle_stages(inp, torch.float32), _oracle_stages(inp, torch.float64)
+    a32, a64 = r32["audio"].numpy(), r64["audio"].numpy()
+    got = audio.cpu().numpy()
+    assert np.abs(got - a32).max() <= WAVE_MAXABS
+    assert np.abs(got - a64).max() <= WAVE_MAXABS
+    np.testing.assert_array_equal(audio_1s.cpu().numpy(), got)
+    np.testing.assert_array_equal(audio_graph, got)
+    p = post.cpu().numpy()
+    e_gpu, e_cpu = rel_l2(p, r64["post"].numpy()), rel_l2(r32["post"].numpy(), r64["post"].numpy())
+    assert rel_l2(p, r32["post"].numpy()) <= 48 * REL_L2  # 48 chained fused convs
+    assert e_gpu <= 2 * e_cpu + 1e-6
+    assert rel_l2(got, a64) <= 2 * rel_l2(a32, a64) + 1e-6
+    from lokinfer_b200 import ops
+    assert ops.conv_tc_status() == 0
+
+
+@pytest.mark.parametrize("k", [3, 7, 11])
+@pytest.mark.parametrize("l", [19200, 19201])
+def test_resblock_config0_full_length(cuda, k, l):
+    """BASELINE config 0 at its full length: one AdaINResBlock1 at C = 128, L = 19200 (and 19201, the generator's
+    real stage-1 length for T = 320) for each kernel size, against the float32 and float64 oracle."""
+    from lokinfer_b200 import Generator, ops
+    sd, x, s = synth.resblock_case(128, l, k, 300 + k)
+    g = Generator(sd, cuda)
+    with ops.padded_rows():
+        out, st = g.adain_resblock1_fused(ops.to_cuda(x, cuda, rows=True), g.style(ops.to_cuda(s, cuda)), "rb", k)
+    plain, st_plain = g.adain_resblock1_fused(ops.to_cuda(x, cuda), g.style(ops.to_cuda(s, cuda)), "rb", k)
+    assert torch.equal(out, plain) and torch.equal(st, st_plain)  # padded rows (TMA) and contiguous rows agree
+    sd32 = {n: O.T(v) for n, v in sd.items()}
+    ref, rst = O.adain_resblock1_fused(O.T(x), O.style_bank(sd32, O.T(s)), sd32, "rb", k)
+    sd64 = {n: O.T(v, torch.float64) for n, v in sd.items()}
+    ref64, _ = O.adain_resblock1_fused(O.T(x, torch.float64), O.style_bank(sd64, O.T(s, torch.float64)), sd64, "rb", k)
+    got = out.cpu().numpy()
+    assert got.shape == (128, l)
+    assert rel_l2(got, ref.numpy()) <= 6 * REL_L2
+    assert rel_l2(got, ref64.numpy()) <= 2 * rel_l2(ref.numpy(), ref64.numpy()) + 1e-6
+    np.testing.assert_allclose(st.cpu().numpy()[..., 0], rst.numpy()[..., 0], atol=1e-4, rtol=1e-4)
+    assert ops.conv_tc_status() == 0
+
+
+def test_generator_config2_stages_vs_oracle(cuda, gen):
+    """BASELINE config 2 (the 26 s paragraph case, T = 2080) against the float32 oracle run once on the CPU: the
+    three resblock outputs of each stage, the conv_post logits and the waveform."""
+    t = 2080
+    inp, d = _inputs(cuda, t, seed=5)
+    post, audio, s0, s1 = gen.forward(*d, outputs=("post", "audio", "stage0", "stage1"))
+    ref = _oracle_stages(inp, torch.float32)
+    for name, got_rb in (("stage0", s0), ("stage1", s1)):
+        for j in range(3):
+            assert rel_l2(got_rb[j].cpu().numpy(), ref[name][j].numpy()) <= 24 * REL_L2, (name, j)
+    assert rel_l2(post.cpu().numpy(), ref["post"].numpy()) <= 48 * REL_L2
+    assert np.abs(audio.cpu().numpy() - ref["audio"].numpy()).max() <= WAVE_MAXABS
+    from lokinfer_b200 import ops
+    assert ops.conv_tc_status() == 0
+
+
 def test_graph_replay_matches_eager(cuda, gen):
     inp, d = _inputs(cuda, 9, seed=21)
     eager = gen.forward(*d).cpu().numpy()

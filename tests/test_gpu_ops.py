@@ -43,7 +43,10 @@ TC_CASES = [(128, 128, 1201, 3, 1), (128, 128, 1201, 7, 3), (128, 128, 5000, 11,
             (256, 256, 333, 3, 5), (128, 128, 256, 3, 1), (128, 128, 257, 7, 1), (128, 128, 128, 11, 1),
             (128, 128, 20, 11, 5), (128, 128, 1, 3, 1), (16, 128, 700, 7, 3), (48, 128, 300, 5, 2),
             (256, 128, 900, 3, 3), (128, 256, 900, 7, 5), (128, 128, 45000, 3, 1), (256, 256, 20800, 7, 1),
-            (128, 128, 19201, 11, 3), (128, 22, 5000, 7, 1), (32, 200, 700, 3, 1), (16, 129, 300, 5, 1)]
+            (128, 128, 19201, 11, 3), (128, 22, 5000, 7, 1), (32, 200, 700, 3, 1), (16, 129, 300, 5, 1),
+            # K beyond the 12-MMA drain bound: one chunk's 13 hi MMAs form the chain (tensor cores); K = 25 has more
+            # than the kernel accepts and runs on the CUDA cores although it has a state
+            (32, 128, 400, 13, 1), (32, 128, 300, 25, 2)]
 
 
 @pytest.mark.parametrize("ci,co,l,k,d", CONV_CASES + TC_CASES)
@@ -109,6 +112,110 @@ def test_conv1d_fused(cuda, ci, co, l, k, d, variant):
         finally:
             ops.set_conv_path("auto")
         assert rel_l2(out, o2.cpu().numpy()) <= REL_L2
+
+
+# Shapes for the padded-row (TMA) route: partial last tile, exact tile multiples, windows that start before the row
+# and end after it, odd lengths (pitch = L rounded up to 4), both stage shapes of the 26 s case, several tiles per CTA.
+TMA_CASES = [(128, 128, 1201, 3, 1), (128, 128, 1203, 7, 3), (128, 128, 5000, 11, 5), (256, 256, 641, 11, 5),
+             (128, 128, 256, 3, 1), (128, 128, 257, 7, 1), (128, 128, 20, 11, 5), (128, 128, 1, 3, 1),
+             (16, 128, 702, 7, 3), (256, 128, 900, 3, 3), (128, 256, 901, 7, 5), (128, 128, 45001, 3, 1),
+             (256, 256, 20800, 7, 1), (128, 128, 124801, 11, 5), (128, 22, 5001, 7, 1), (32, 128, 400, 13, 1)]
+
+
+@pytest.mark.parametrize("ci,co,l,k,d", TMA_CASES)
+@pytest.mark.parametrize("variant", ["snake", "snake_res", "leaky_res"])
+def test_conv1d_fused_padded_rows(cuda, ci, co, l, k, d, variant):
+    """The same op on [C, L] views whose rows are padded to 16 bytes: the tensor-core kernel then loads the raw
+    windows and the residual and stores the output with the TMA unit. The arithmetic does not depend on the route:
+    results are bit-identical to the contiguous call (4-byte accesses), which the other tests hold to the oracle;
+    small cases are also compared with the oracle directly, and the padding columns stay untouched."""
+    from lokinfer_b200 import ops
+    x, w, b, affine, alpha, res = synth.conv_case(ci, co, l, k, ci * 31 + l + k, big=l < 6000)
+    pad = d * (k - 1) // 2
+    dx, dw, db, daf, dal, dres = dev(cuda, x, w, b, affine, alpha, res)
+    state = ops.conv1d_prepare_f32_cuda(dw)
+    assert state is not None
+
+    def call(xx, rr):
+        kw = dict(padding=pad, dilation=d, state=state)
+        if variant == "snake":
+            return ops.conv1d_snake_f32_cuda(xx, dw, db, daf, dal, **kw)
+        if variant == "snake_res":
+            return ops.conv1d_snake_f32_cuda(xx, dw, db, daf, dal, residual=rr, **kw)
+        return ops.conv1d_leaky_f32_cuda(xx, dw, db, daf, slope=0.2, residual=rr, out_scale=0.7071067811865476, **kw)
+
+    ref_out, ref_stats = call(dx, dres)
+    with ops.padded_rows():
+        px, pres = ops.to_cuda(x, cuda, rows=True), ops.to_cuda(res, cuda, rows=True)
+        pitch = -(-l // 4) * 4
+        assert px.stride(0) == pitch and pres.stride(0) == pitch
+        out, stats = call(px, pres)
+    assert out.stride(0) == pitch and tuple(out.shape) == (co, l)
+    assert ops.conv_tc_status() == 0
+    assert torch.equal(out, ref_out)
+    assert torch.equal(stats, ref_stats)
+    if l <= 6000:
+        a = [O.T(v) for v in (x, w, b, affine, alpha, res)]
+        if variant.startswith("snake"):
+            ref32 = O.conv1d_fused(a[0], a[1], a[2], a[3], "snake", alpha=a[4],
+                                   residual=a[5] if variant == "snake_res" else None, padding=pad, dilation=d)[0]
+        else:
+            ref32 = O.conv1d_fused(a[0], a[1], a[2], a[3], "leaky", slope=0.2, residual=a[5],
+                                   out_scale=0.7071067811865476, padding=pad, dilation=d)[0]
+        assert rel_l2(out.cpu().numpy(), ref32.numpy()) <= REL_L2
+    # the same padded operands through 4-byte accesses (route switch): still identical
+    ops.set_conv_io("plain")
+    try:
+        with ops.padded_rows():
+            out3, stats3 = call(px, pres)
+    finally:
+        ops.set_conv_io("tma")
+    assert torch.equal(out3, out) and torch.equal(stats3, stats)
+
+
+def test_conv1d_padded_rows_leave_padding_untouched(cuda):
+    """A bulk tensor store is clipped at the end of the row: the padding columns of the output keep their contents."""
+    from lokinfer_b200 import ops
+    ci = co = 128
+    l, k, d = 1201, 7, 1
+    x, w, b, affine, alpha, res = synth.conv_case(ci, co, l, k, 77)
+    dw, db, daf, dal = dev(cuda, w, b, affine, alpha)
+    state = ops.conv1d_prepare_f32_cuda(dw)
+    marker = torch.full((co, 1204), 123.0, device=cuda)
+
+    def alloc(shape, device):
+        return marker if tuple(shape) == (co, 1204) else torch.empty(shape, dtype=torch.float32, device=device)
+
+    with ops.padded_rows():
+        px = ops.to_cuda(x, cuda, rows=True)
+        with ops.use_allocator(alloc):
+            out, _ = ops.conv1d_snake_f32_cuda(px, dw, db, daf, dal, padding=3, dilation=1, state=state)
+    assert out.data_ptr() == marker.data_ptr()
+    assert torch.all(marker[:, l:] == 123.0)
+    assert not torch.any(marker[:, :l] == 123.0)
+
+
+def test_conv1d_weights_beyond_f16_range_fall_back_to_tf32_pack(cuda):
+    """A weight beyond the f16 range (65504) cannot go into the f16 hi/lo pack: the pack kernel reports it and the
+    prepare step packs the weight in the tf32 format instead, silently correct."""
+    from lokinfer_b200 import ops
+    ci = co = 128
+    l, k, d = 700, 3, 1
+    x, w, b, affine, alpha, res = synth.conv_case(ci, co, l, k, 9)
+    w = w.copy()
+    w[5, 17, 1] = 1.0e5
+    dx, dw, db, daf, dal = dev(cuda, x, w, b, affine, alpha)
+    st = ops.conv1d_prepare_f32_cuda(dw)
+    assert st is not None and st.fmt == "tf32"
+    assert ops.conv_tc_status() == 0
+    out, _ = ops.conv1d_snake_f32_cuda(dx, dw, db, daf, dal, padding=1, dilation=1, state=st)
+    assert ops.conv_tc_status() == 0
+    a = [O.T(v) for v in (x, w, b, affine, alpha)]
+    ref = O.conv1d_fused(a[0], a[1], a[2], a[3], "snake", alpha=a[4], padding=1, dilation=1)[0].numpy()
+    assert rel_l2(out.cpu().numpy(), ref) <= REL_L2
+    w2 = w.copy()
+    w2[5, 17, 1] = 0.5
+    assert ops.conv1d_prepare_f32_cuda(dev(cuda, w2)[0]).fmt == "f16"
 
 
 TF32_CASES = [(128, 128, 1201, 3, 1), (128, 128, 1201, 7, 3), (256, 256, 640, 11, 5), (128, 128, 257, 7, 1),
@@ -266,6 +373,23 @@ def test_conv_transpose1d_poly(cuda, ci, co, l, k, s, pl, mean3):
         np.testing.assert_allclose(got_tc, oracle(torch.float64), atol=1e-4, rtol=1e-4)
         e_tc, e_cpu = rel_l2(got_tc, oracle(torch.float64)), rel_l2(oracle(torch.float32), oracle(torch.float64))
         assert e_tc <= 2 * e_cpu + 2e-7
+        # the same call with padded rows (x, res, out): identical values
+        with ops.padded_rows():
+            px, pres = ops.to_cuda(xs[0], cuda, rows=True), ops.to_cuda(res, cuda, rows=True)
+            got_p = ops.conv_transpose1d_poly_f32_cuda(px, wp, d[4], pres, stride=s, padding=p, taps=k // s,
+                                                       slope=0.1, pad_left=pl, state=st)
+        assert ops.conv_tc_status() == 0
+        np.testing.assert_array_equal(got_p.cpu().numpy(), got_tc)
+        if pl == 1 and l * s > 2:
+            # left reflect column, reference order (kokoro_conv.cpp:226): out[:, 0] = unpadded[:, 1] + res[:, 0] with
+            # the plain conv sum. With a zero residual the column is an exact copy of out[:, 2].
+            zres = torch.zeros_like(d[5])
+            z = ops.conv_transpose1d_poly_f32_cuda(d[0], wp, d[4], zres, stride=s, padding=p, taps=k // s, slope=0.1,
+                                                   pad_left=pl, state=st)
+            assert torch.equal(z[:, 0], z[:, 2])
+            # and with the residual: out[:, 0] - res[:, 0] and out[:, 2] - res[:, 2] round the same sum
+            c0 = z[:, 0] + d[5][:, 0]
+            assert torch.equal(torch.from_numpy(got_tc[:, 0]).to(cuda), c0)
     if mean3:  # bit-identical to add3_scale followed by the op (test_kokoro_conv_fused.py:252-264)
         m = ops.add3_scale_f32_cuda(d[0], d[1], d[2], 1.0 / 3.0)
         exp = ops.conv_transpose1d_poly_f32_cuda(m, wp, d[4], d[5], stride=s, padding=p, taps=k // s, slope=0.1,
