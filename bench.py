@@ -179,7 +179,14 @@ def measure_cfg0(dev, peak: float) -> dict:
             with ops.padded_rows():
                 dx = ops.to_cuda(x, dev, rows=True)
                 gb = g.style(ops.to_cuda(s, dev))
-                ms = _event_ms(lambda: g.adain_resblock1_fused(dx, gb, "rb", k), 20, 3)
+                for _ in range(2):  # warm-up outside the capture
+                    g.adain_resblock1_fused(dx, gb, "rb", k)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()  # one replay per block: the 13 launches are not host-bound
+                with torch.cuda.graph(graph):
+                    keep = g.adain_resblock1_fused(dx, gb, "rb", k)
+                ms = _event_ms(graph.replay, 20, 3)
+                del keep
             fl = 6 * 2.0 * 128 * 128 * k * l
             tf = fl / (ms * 1e-3) / 1e12
             out["blocks"].append({"L": l, "k": k, "ms": ms, "tflops": tf, "frac": tf / peak})

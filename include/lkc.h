@@ -16,7 +16,7 @@
  * floats (>= L). Without them rows are L floats apart. A caller that owns its intermediates can round the pitch up
  * to a multiple of 4 floats and keep base pointers 16-byte aligned: the tensor-core kernels then move those
  * tensors with the TMA unit (tiled bulk loads and stores) instead of 4-byte accesses. Results do not depend on
- * the pitch.
+ * the pitch; the padding columns of an output row (between L and the pitch) may be overwritten.
  * Ownership: the caller owns every buffer and all work is queued on the caller's stream (a cudaStream_t passed as
  * void*). No entry point allocates or frees device memory or synchronises the host, with these exceptions, each
  * stated at its declaration: lkc_harmonic_source_f32_cuda (grow-only scratch: cudaMalloc when n grows), and the

@@ -124,7 +124,7 @@ class Generator:
         ops.check(x.dim() == 2 and x.shape[0] == 512, "x must be f32[512, T]")
         sh = shapes(int(x.shape[1]))
         ops.check(tuple(har.shape) == (22, sh["L1"]), f"har must be f32[22, {sh['L1']}]")
-        if fused and pad_rows and not ops._pad_rows:
+        if fused and pad_rows and not ops._pad_rows and ops._conv_path != "simt":
             # the generator owns every intermediate: rows padded to 16 bytes, so that the tensor-core kernels move
             # them with the TMA unit (values do not depend on the pitch)
             with ops.padded_rows():

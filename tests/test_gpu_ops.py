@@ -173,26 +173,29 @@ def test_conv1d_fused_padded_rows(cuda, ci, co, l, k, d, variant):
     assert torch.equal(out3, out) and torch.equal(stats3, stats)
 
 
-def test_conv1d_padded_rows_leave_padding_untouched(cuda):
-    """A bulk tensor store is clipped at the end of the row: the padding columns of the output keep their contents."""
+def test_conv1d_padded_rows_stay_inside_their_buffer(cuda):
+    """A bulk tensor store is clipped at the end of the row (at 16-byte granularity: the padding columns of a row may
+    be overwritten, they belong to the output buffer): nothing before the first row or after the last one is
+    touched, and every valid column is written."""
     from lokinfer_b200 import ops
     ci = co = 128
     l, k, d = 1201, 7, 1
     x, w, b, affine, alpha, res = synth.conv_case(ci, co, l, k, 77)
     dw, db, daf, dal = dev(cuda, w, b, affine, alpha)
     state = ops.conv1d_prepare_f32_cuda(dw)
-    marker = torch.full((co, 1204), 123.0, device=cuda)
+    guard = torch.full((co + 2, 1204), 123.0, device=cuda)
 
     def alloc(shape, device):
-        return marker if tuple(shape) == (co, 1204) else torch.empty(shape, dtype=torch.float32, device=device)
+        return guard[1:co + 1] if tuple(shape) == (co, 1204) else torch.empty(shape, dtype=torch.float32, device=device)
 
     with ops.padded_rows():
         px = ops.to_cuda(x, cuda, rows=True)
         with ops.use_allocator(alloc):
             out, _ = ops.conv1d_snake_f32_cuda(px, dw, db, daf, dal, padding=3, dilation=1, state=state)
-    assert out.data_ptr() == marker.data_ptr()
-    assert torch.all(marker[:, l:] == 123.0)
-    assert not torch.any(marker[:, :l] == 123.0)
+    assert out.data_ptr() == guard[1].data_ptr() and out.stride(0) == 1204
+    assert ops.conv_tc_status() == 0
+    assert torch.all(guard[0] == 123.0) and torch.all(guard[co + 1] == 123.0)
+    assert not torch.any(guard[1:co + 1, :l] == 123.0)
 
 
 def test_conv1d_weights_beyond_f16_range_fall_back_to_tf32_pack(cuda):
