@@ -17,10 +17,17 @@
  * to a multiple of 4 floats and keep base pointers 16-byte aligned: the tensor-core kernels then move those
  * tensors with the TMA unit (tiled bulk loads and stores) instead of 4-byte accesses. Results do not depend on
  * the pitch; the padding columns of an output row (between L and the pitch) may be overwritten.
+ * Window extension (likewise no counterpart in the reference; used for time-sharded tensors, see the shard section):
+ * after the row pitches the conv entry points accept further ints that describe x as a window into a longer row:
+ * x_origin (output column t reads x columns x_origin + t * stride - padding + kk * dilation), valid_lo / valid_hi (x
+ * columns outside [valid_lo, valid_hi) count as the zero padding, applied after the activation, as at the ends of an
+ * unsharded row), and for the fused family stats_chunks (row stride of `stats` in chunks, so the chunk statistics can
+ * land in a slice of the whole utterance's statistics row). With a window the output length is taken from `out`.
  * Ownership: the caller owns every buffer and all work is queued on the caller's stream (a cudaStream_t passed as
  * void*). No entry point allocates or frees device memory or synchronises the host, with these exceptions, each
- * stated at its declaration: lkc_harmonic_source_f32_cuda (grow-only scratch: cudaMalloc when n grows), and the
- * host-side readers lkc_conv1d_tc_status / lkc_conv1d_tc_profile (they synchronise the device).
+ * stated at its declaration: lkc_harmonic_source_f32_cuda (grow-only scratch: cudaMalloc when n grows), the
+ * host-side readers lkc_conv1d_tc_status / lkc_conv1d_tc_profile (they synchronise the device), and the lkc_peer_*
+ * set-up calls of the time-sharding section.
  * Errors: every function returns 0 on success and non-zero on failure; lkc_last_error() then returns a
  * message (thread-local, valid until the next failing call on the thread). Nothing throws or aborts.
  * The stats tensors are f32[C, ceil(L / 128), 2] = per-(channel, 128-sample chunk) (mean, M2).
@@ -65,7 +72,7 @@ LKC_API const char* lkc_build_info(void);
 
 /* conv1d_f32_cpu (kernels/cpu/kokoro_conv.cpp:32-69, adapter :276-280).
  * ptrs x[Ci,L] w[Co,Ci,K] b[Co] | out[Co,Lo]; ints x(2) w(3) b(1) out(2) dilation padding stride
- * [x_pitch out_pitch]. */
+ * [x_pitch out_pitch [x_origin valid_lo valid_hi]]. */
 LKC_API int lkc_conv1d_f32_cuda(const LkcArgs* a, void* stream);
 /* conv1d_nobias_f32_cpu (kokoro_conv.cpp:282-286). ptrs x w | out; ints x(2) w(3) out(2) dilation padding stride
  * [x_pitch out_pitch]. */
@@ -96,7 +103,7 @@ LKC_API int lkc_gemm_bias_f32_cuda(const LkcArgs* a, void* stream);
 /* ---- fused layer ---------------------------------------------------------------------------------------- */
 
 /* channel_stats_f32_cpu (kernels/cpu/kokoro_conv_fused.cpp:631-639, adapter :775-777).
- * ptrs x[C,L] | stats[C,ceil(L/128),2]; ints x(2) stats(3) [x_pitch]. */
+ * ptrs x[C,L] | stats[C,ceil(L/128),2]; ints x(2) stats(3) [x_pitch [stats_chunks]]. */
 LKC_API int lkc_channel_stats_f32_cuda(const LkcArgs* a, void* stream);
 /* adain_affine_f32_cpu (kokoro_conv_fused.cpp:641-664, adapter :780-783).
  * ptrs stats[C,S,2] gb[2C] | affine[3,C]; ints stats(3) gb(1) affine(2) length; floats eps. */
@@ -106,7 +113,8 @@ LKC_API int lkc_adain_affine_f32_cuda(const LkcArgs* a, void* stream);
  *   out = (conv1d(act((x - mean) * scale + beta), w) + b [+ res]) [* oscale], stride 1, zero padding applied
  *   after act; stats = chunk stats of out.
  * ptrs x[Ci,L] w[Co,Ci,K] b[Co] affine[3,Ci] [alpha[Ci]] [res[Co,Lo]] | out[Co,Lo] stats[Co,S,2]
- * ints x(2) w(3) b(1) affine(2) [alpha(1)] [res(2)] out(2) stats(3) dilation padding tile [x_pitch [res_pitch] out_pitch]
+ * ints x(2) w(3) b(1) affine(2) [alpha(1)] [res(2)] out(2) stats(3) dilation padding tile [x_pitch [res_pitch] out_pitch
+ *      [stats_chunks x_origin valid_lo valid_hi]]
  * floats (name order) [oscale (leaky_res only)] [slope (leaky only)]. `tile` is accepted and ignored.
  * state: NULL, or the LkcConvState returned by lkc_conv1d_state_create for this weight (tensor-core path). */
 LKC_API int lkc_conv1d_snake_f32_cuda(const LkcArgs* a, void* stream);
@@ -161,7 +169,9 @@ LKC_API int lkc_conv1d_tc_profile(int enable, int64_t* counters16);
  * wp is this library's polyphase weight pack f32[Ci, stride, taps, Co] made by lkc_convt_poly_pack_f32_cuda
  * (the counterpart of ops.convt_poly_weights_cpu, python/lokinfer/ops/kokoro.py:289-314).
  * ptrs x[Ci,L] wp b[Co] res[Co,L*s+pad_left] | out;  ints x(2) wp(4) b(1) res(2) out(2) pad_left padding stride
- * taps [x_pitch res_pitch out_pitch] (padded rows: tensor-core route only); floats slope.   mean3: ptrs x x2 x3 wp b res | out; ints x(2) x2(2) x3(2) wp(4) b(1) res(2) out(2)
+ * taps [x_pitch res_pitch out_pitch [halo_left halo_right]] (tensor-core route only; halo_* in {0, 1}: x holds that
+ * many real columns before / after the L - halo_left - halo_right columns that produce output, instead of the zero
+ * padding of an unsharded row); floats slope.   mean3: ptrs x x2 x3 wp b res | out; ints x(2) x2(2) x3(2) wp(4) b(1) res(2) out(2)
  * pad_left padding stride taps; floats in_scale slope. */
 LKC_API int lkc_conv_transpose1d_poly_f32_cuda(const LkcArgs* a, void* stream);
 LKC_API int lkc_conv_transpose1d_poly_mean3_f32_cuda(const LkcArgs* a, void* stream);
@@ -183,8 +193,9 @@ LKC_API LkcConvState* lkc_convt_state_create(const void* wp, int64_t ci, int64_t
                                              int64_t padding);
 
 /* istft_logits_f32_cpu (kernels/cpu/kokoro_signal.cpp:275-359, adapter :388-391).
- * ptrs x[n_fft+2,L] | out[hop*(L-1)]; ints x(2) out(1) hop n_fft [x_pitch]. Fails when n_fft/2+1 > 64, like the
- * reference. */
+ * ptrs x[n_fft+2,L] | out[hop*(L-1)]; ints x(2) out(1) hop n_fft [x_pitch [frames frame0 i0]]. Fails when
+ * n_fft/2+1 > 64, like the reference. Shard form: x holds frames frame0 .. frame0 + L of a signal of `frames` frames
+ * and out receives its samples i0 .. i0 + len(out); x must hold every frame those samples overlap. */
 LKC_API int lkc_istft_logits_f32_cuda(const LkcArgs* a, void* stream);
 
 /* harmonic_source_f32_cpu (kernels/cpu/kokoro_signal.cpp:97-190, adapter :370-373; rule python/lokinfer/ops/kokoro.py
@@ -207,6 +218,45 @@ LKC_API int lkc_harmonic_source_noalloc_f32_cuda(const LkcArgs* a, void* stream)
  * torch.stft(center, reflect, periodic hann(n_fft), onesided) -> cat(abs, angle).
  * ptrs x[S] | out[n_fft+2, S/hop+1]; ints x(1) out(2) hop n_fft. n_fft even, <= 64; S > n_fft/2. */
 LKC_API int lkc_stft_magphase_f32_cuda(const LkcArgs* a, void* stream);
+
+/* ---- time sharding of one utterance across GPUs ------------------------------------------------------------
+ * No counterpart in the reference (it has no multi-GPU path). One rank owns a contiguous time range of every
+ * activation tensor, with a margin of halo columns on both sides, in memory that its peers have mapped (CUDA IPC).
+ * lkc_shard_push copies 2-D blocks of f32 (boundary columns into the neighbours' margins, this rank's slice of the
+ * chunk statistics into every rank's statistics row) with plain stores, peer pointers included, and then
+ * release-stores *epoch into every flag; lkc_shard_wait blocks the stream until every flag is >= *epoch + delta, for
+ * at most limit_ns nanoseconds per flag: after that it sets *status = 1 << 24 | flag index (if it was 0) and returns,
+ * so that nothing hangs when a peer is gone. lkc_shard_epoch_bump adds 1 to *epoch (one forward = one epoch, which
+ * makes a captured launch sequence replayable). flags, epoch, ticket (one unsigned per call site, zero at start)
+ * and status are device pointers; flags usually point into a peer's memory. */
+#define LKC_SHARD_MAX_COPIES 16
+#define LKC_SHARD_MAX_FLAGS 16
+typedef struct LkcShardCopy {
+  const void* src; /* f32, rows x cols, row pitch src_pitch floats */
+  void* dst;
+  int64_t src_pitch, dst_pitch, rows, cols;
+} LkcShardCopy;
+typedef struct LkcShardPush {
+  LkcShardCopy copies[LKC_SHARD_MAX_COPIES];
+  int32_t num_copies;
+  void* flags[LKC_SHARD_MAX_FLAGS];
+  int32_t num_flags;
+  const void* epoch;
+  void* ticket;
+} LkcShardPush;
+LKC_API int lkc_shard_push(const LkcShardPush* desc, void* stream);
+LKC_API int lkc_shard_wait(void* const* flags, int num_flags, const void* epoch, int delta, uint64_t limit_ns,
+                           void* status, void* stream);
+LKC_API int lkc_shard_epoch_bump(void* epoch, void* stream);
+/* Set-up of the peer-mapped memory the calls above work on (the only entry points that allocate device memory on
+ * purpose; none of them is on the data path): lkc_peer_alloc = cudaMalloc + zero fill of one arena, lkc_peer_handle
+ * exports it (64-byte CUDA IPC handle, to be sent to the other ranks by any host channel), lkc_peer_open maps a
+ * peer's arena into this process (peer access enabled on demand), lkc_peer_close / lkc_peer_free undo them. */
+LKC_API int lkc_peer_alloc(uint64_t bytes, void** ptr);
+LKC_API int lkc_peer_free(void* ptr);
+LKC_API int lkc_peer_handle(void* ptr, unsigned char handle[64]);
+LKC_API int lkc_peer_open(const unsigned char handle[64], void** ptr);
+LKC_API int lkc_peer_close(void* ptr);
 
 #ifdef __cplusplus
 }

@@ -30,10 +30,13 @@ int runConvFused(const LkcArgs* a, void* stream, Act act, bool res, const char* 
   const bool hasAlpha = act == Act::Snake;
   const uint32_t nptr = 4 + (hasAlpha ? 1 : 0) + (res ? 1 : 0) + 2;
   const uint32_t nint = 8 + (hasAlpha ? 1 : 0) + (res ? 2 : 0) + 2 + 3 + 3;
-  const uint32_t npitch = res ? 3 : 2;  // optional trailing ints: row pitches of x, [res,] out (see lkc.h)
-  if (!a || a->numPtrs != nptr || (a->numInts != nint && a->numInts != nint + npitch)) {
-    std::snprintf(gError, sizeof gError, "%s: expected %u pointers and %u ints (+ %u row pitches)", name, nptr, nint,
-                  npitch);
+  // optional trailing ints: row pitches of x, [res,] out; then the window extension stats_chunks, x_origin, valid_lo,
+  // valid_hi (see lkc.h)
+  const uint32_t npitch = res ? 3 : 2, nwin = 4;
+  if (!a || a->numPtrs != nptr ||
+      (a->numInts != nint && a->numInts != nint + npitch && a->numInts != nint + npitch + nwin)) {
+    std::snprintf(gError, sizeof gError, "%s: expected %u pointers and %u ints (+ %u row pitches (+ %u window ints))",
+                  name, nptr, nint, npitch, nwin);
     return 1;
   }
   const int64_t* n = a->ints;
@@ -62,13 +65,25 @@ int runConvFused(const LkcArgs* a, void* stream, Act act, bool res, const char* 
   LKC_REQUIRE(n[5] == p.co, "conv1d fused: bias must be f32[Co]");
   LKC_REQUIRE(n[6] == 3 && n[7] == p.ci, "conv1d fused: affine must be f32[3, Ci]");
   LKC_REQUIRE(p.dilation >= 1 && p.padding >= 0 && p.k >= 1, "conv1d fused: invalid padding/dilation");
-  p.lo = p.l + 2 * p.padding - p.dilation * (p.k - 1);
+  const bool window = a->numInts == nint + npitch + nwin;
+  if (window) {
+    // x is a window into a longer row: the output length is given by `out`, x columns outside [valid_lo, valid_hi)
+    // are the zero padding
+    const int64_t* wn = n + nint + npitch;
+    p.statsStride = wn[0], p.xOrigin = wn[1], p.validLo = wn[2], p.validHi = wn[3];
+    p.lo = outDims[1];
+    LKC_REQUIRE(p.xOrigin >= 0 && p.xOrigin <= p.l && p.validLo >= 0 && p.validHi <= p.l && p.validLo <= p.validHi,
+                "conv1d fused: window out of range");
+    LKC_REQUIRE(p.statsStride >= statChunks(p.lo), "conv1d fused: stats row stride is smaller than the row");
+  } else {
+    p.lo = p.l + 2 * p.padding - p.dilation * (p.k - 1);
+  }
   LKC_REQUIRE(p.lo >= 1, "conv1d fused: empty conv output");
   LKC_REQUIRE(outDims[0] == p.co && outDims[1] == p.lo, "conv1d fused: out must be f32[Co, Lo]");
   LKC_REQUIRE(stDims[0] == p.co && stDims[1] == statChunks(p.lo) && stDims[2] == 2,
               "conv1d fused: stats must be f32[Co, ceil(Lo/128), 2]");
   if (res) LKC_REQUIRE(resDims[0] == p.co && resDims[1] == p.lo, "conv1d fused: residual must match the output");
-  if (a->numInts == nint + npitch) {
+  if (a->numInts >= nint + npitch) {
     const int64_t* pt = n + nint;
     p.xPitch = pt[0], p.resPitch = res ? pt[1] : 0, p.outPitch = pt[npitch - 1];
     LKC_REQUIRE(p.xPitch >= p.l && p.outPitch >= p.lo && (!res || p.resPitch >= p.lo),
@@ -84,7 +99,7 @@ int runConvFused(const LkcArgs* a, void* stream, Act act, bool res, const char* 
 
 int runConv1d(const LkcArgs* a, void* stream, bool bias) {
   const uint32_t nptr = bias ? 4 : 3, nint = bias ? 11 : 10;
-  LKC_REQUIRE(a && a->numPtrs == nptr && (a->numInts == nint || a->numInts == nint + 2),
+  LKC_REQUIRE(a && a->numPtrs == nptr && (a->numInts == nint || a->numInts == nint + 2 || a->numInts == nint + 5),
               "conv1d_f32_cuda: bad operand count");
   const int64_t* n = a->ints;
   ConvFusedParams p;
@@ -99,11 +114,18 @@ int runConv1d(const LkcArgs* a, void* stream, bool bias) {
   if (bias) LKC_REQUIRE(n[5] == p.co, "conv1d_f32_cuda: bias must be f32[Co]");
   LKC_REQUIRE(stride >= 1 && p.dilation >= 1 && p.padding >= 0 && p.k >= 1,
               "conv1d_f32_cuda: invalid stride/padding/dilation");
-  const int64_t span = p.l + 2 * p.padding - p.dilation * (p.k - 1) - 1;
-  LKC_REQUIRE(span >= 0, "conv1d_f32_cuda: empty conv output");
-  p.lo = span / stride + 1;
+  if (a->numInts == nint + 5) {  // window extension: x_origin, valid_lo, valid_hi; the output length is given by `out`
+    p.xOrigin = n[nint + 2], p.validLo = n[nint + 3], p.validHi = n[nint + 4];
+    p.lo = n[at - 1];
+    LKC_REQUIRE(p.xOrigin >= 0 && p.validLo >= 0 && p.validHi <= p.l && p.validLo <= p.validHi && p.lo >= 1,
+                "conv1d_f32_cuda: window out of range");
+  } else {
+    const int64_t span = p.l + 2 * p.padding - p.dilation * (p.k - 1) - 1;
+    LKC_REQUIRE(span >= 0, "conv1d_f32_cuda: empty conv output");
+    p.lo = span / stride + 1;
+  }
   LKC_REQUIRE(n[at - 2] == p.co && n[at - 1] == p.lo, "conv1d_f32_cuda: out must be f32[Co, Lo]");
-  if (a->numInts == nint + 2) {  // optional trailing ints: row pitches of x and out
+  if (a->numInts >= nint + 2) {  // optional trailing ints: row pitches of x and out
     p.xPitch = n[nint], p.outPitch = n[nint + 1];
     LKC_REQUIRE(p.xPitch >= p.l && p.outPitch >= p.lo, "conv1d_f32_cuda: a row pitch is smaller than the row");
   }

@@ -21,6 +21,7 @@ struct SimtArgs {
   int ci, co, k, dilation, padding, stride;
   int64_t l, lo, nchunks;
   int64_t xPitch, resPitch, outPitch;  // row pitches in floats
+  int64_t validLo, validHi;            // x columns outside [validLo, validHi) are zero padding (after the activation)
   float slope, outScale, inScale;
   int win;  // staged window length per input channel
 };
@@ -62,7 +63,7 @@ __global__ void __launch_bounds__(NTHREADS) convSimtKernel(const SimtArgs p) {
       const int cc = idx / p.win, q = idx - cc * p.win, c = c0 + cc;
       const int64_t pos = p0 + q;
       float v = 0.f;
-      if (c < p.ci && pos >= 0 && pos < p.l) {
+      if (c < p.ci && pos >= p.validLo && pos < p.validHi) {
         float mean = 0.f, scale = 1.f, beta = 0.f, alpha = 0.f, inv = 0.f;
         if (p.affine) mean = p.affine[c], scale = p.affine[p.ci + c], beta = p.affine[2 * p.ci + c];
         if (ACT == 1) alpha = p.alpha[c], inv = 1.f / alpha;
@@ -162,11 +163,13 @@ int convSimt(const ConvFusedParams& p, int64_t stride, cudaStream_t s) {
   a.x = p.x, a.x2 = p.x2, a.x3 = p.x3, a.w = p.w, a.bias = p.bias, a.affine = p.affine, a.alpha = p.alpha;
   a.residual = p.residual, a.out = p.out, a.stats = p.stats;
   LKC_REQUIRE(p.ci <= (1 << 20) && p.co <= (1 << 20) && p.k <= 4096 && p.dilation <= 4096 && p.padding <= (1 << 24) &&
-                  stride <= 4096,
+                  stride <= 4096 && p.xOrigin >= 0 && p.xOrigin <= (1 << 24),
               "conv: shape out of range");
   a.ci = int(p.ci), a.co = int(p.co), a.k = int(p.k), a.dilation = int(p.dilation), a.padding = int(p.padding);
   a.stride = int(stride);
-  a.l = p.l, a.lo = p.lo, a.nchunks = statChunks(p.lo);
+  a.l = p.l, a.lo = p.lo, a.nchunks = p.statsStride ? p.statsStride : statChunks(p.lo);
+  a.padding = int(p.padding - p.xOrigin);  // window slot 0 of output column t is x column t * stride - padding + xOrigin
+  a.validLo = p.validLo < 0 ? 0 : p.validLo, a.validHi = (p.validHi < 0 || p.validHi > p.l) ? p.l : p.validHi;
   a.xPitch = p.xPitch ? p.xPitch : p.l, a.resPitch = p.resPitch ? p.resPitch : p.lo;
   a.outPitch = p.outPitch ? p.outPitch : p.lo;
   a.slope = p.slope, a.outScale = p.outScale, a.inScale = p.inScale;

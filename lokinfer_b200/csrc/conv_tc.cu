@@ -124,6 +124,7 @@ struct TcArgs {
   float *out, *stats;
   int ci, co, k, dilation, padding;
   int64_t l, lo, nchunks;
+  int64_t validLo, validHi;            // x columns outside [validLo, validHi) are zero padding (after the activation)
   int64_t xPitch, resPitch, outPitch;  // row pitches in floats
   int padLeft;       // ConvTranspose: 1 = one-sample left reflect pad
   float slope, outScale;
@@ -866,7 +867,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const int r = r0 + sl * 32 + lane;
         if (r < r1) {
           const int64_t pos = pos0 + r;
-          const bool ok = pos >= 0 && pos < a.l;
+          const bool ok = pos >= a.validLo && pos < a.validHi;
           float2 v01 = make_float2(0.f, 0.f), v23 = v01;
           if (ok) {
             const float* sp = src + r + (r + delta >= half ? runSkip : 0);
@@ -1443,7 +1444,9 @@ int convTc(const ConvFusedParams& p, const float* wp, bool f16, cudaStream_t s) 
   a.x = p.x, a.wp = wp, a.bias = p.bias, a.affine = p.affine, a.alpha = p.alpha, a.residual = p.residual;
   a.out = p.out, a.stats = p.stats;
   a.ci = int(p.ci), a.co = int(p.co), a.k = int(p.k), a.dilation = int(p.dilation), a.padding = int(p.padding);
-  a.l = p.l, a.lo = p.lo, a.nchunks = statChunks(p.lo), a.padLeft = 0;
+  a.l = p.l, a.lo = p.lo, a.nchunks = p.statsStride ? p.statsStride : statChunks(p.lo), a.padLeft = 0;
+  a.padding = int(p.padding - p.xOrigin);  // window row 0 of output column t is x column t - padding + xOrigin
+  a.validLo = p.validLo, a.validHi = p.validHi < 0 ? p.l : p.validHi;
   a.xPitch = p.xPitch ? p.xPitch : p.l, a.resPitch = p.resPitch ? p.resPitch : p.lo;
   a.outPitch = p.outPitch ? p.outPitch : p.lo;
   a.slope = p.slope, a.outScale = p.outScale;
@@ -1495,10 +1498,13 @@ int convtTc(const ConvtParams& p, const float* wp, bool f16, cudaStream_t s) {
   TcMaps m;
   a.x = p.x, a.wp = wp, a.bias = p.bias, a.affine = nullptr, a.alpha = nullptr, a.residual = p.res;
   a.out = p.out, a.stats = nullptr;
-  a.ci = int(p.ci), a.co = int(p.co), a.k = 3, a.dilation = 1, a.padding = 1;
+  // x holds haloLeft + l + haloRight columns; output (input-rate) column j reads x columns j + haloLeft + {-1, 0, 1}
+  const int64_t lx = p.haloLeft + p.l + p.haloRight;
+  a.ci = int(p.ci), a.co = int(p.co), a.k = 3, a.dilation = 1, a.padding = int(1 - p.haloLeft);
   const int64_t lo = p.l * p.stride + p.padLeft;
-  a.l = p.l, a.lo = p.l, a.nchunks = 0, a.padLeft = int(p.padLeft);
-  a.xPitch = p.xPitch ? p.xPitch : p.l, a.resPitch = p.resPitch ? p.resPitch : lo, a.outPitch = p.outPitch ? p.outPitch : lo;
+  a.l = lx, a.lo = p.l, a.nchunks = 0, a.padLeft = int(p.padLeft);
+  a.validLo = 0, a.validHi = lx;
+  a.xPitch = p.xPitch ? p.xPitch : lx, a.resPitch = p.resPitch ? p.resPitch : lo, a.outPitch = p.outPitch ? p.outPitch : lo;
   a.slope = p.slope, a.outScale = 1.f;
   a.rows = NT + 2;
   const int64_t tTiles = ceilDiv(p.l, NT), coBlk = ceilDiv(p.co, 4 * (32 / p.stride));

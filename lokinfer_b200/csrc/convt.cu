@@ -202,9 +202,15 @@ int runPoly(const LkcArgs* a, void* stream, bool mean3) {
   p.out = O(a, 4 + base);
   const uint32_t nint = uint32_t(2 + sh + 4 + 1 + 2 + 2 + 4);
   // optional trailing ints (not with mean3): row pitches of x, res, out; served by the tensor-core route only
-  const bool pitched = !mean3 && a->numInts == nint + 3;
+  // then (window extension, time-sharded tensors) halo_left, halo_right: x holds that many real columns before / after
+  // the columns that produce output
+  const bool windowed = !mean3 && a->numInts == nint + 5;
+  const bool pitched = !mean3 && (a->numInts == nint + 3 || windowed);
   LKC_REQUIRE(a->numInts == nint || pitched, "conv_transpose1d_poly: bad ints count");
-  const int64_t ci = n[0], l = n[1];
+  const int64_t haloL = windowed ? n[nint + 3] : 0, haloR = windowed ? n[nint + 4] : 0;
+  LKC_REQUIRE(haloL >= 0 && haloL <= 1 && haloR >= 0 && haloR <= 1 && n[1] > haloL + haloR,
+              "conv_transpose1d_poly: halos must be 0 or 1 column");
+  const int64_t ci = n[0], l = n[1] - haloL - haloR;  // columns that produce output
   if (mean3)
     LKC_REQUIRE(n[2] == ci && n[3] == l && n[4] == ci && n[5] == l, "conv_transpose1d_poly_mean3: x2 / x3 must match x");
   const int64_t* wd = n + 2 + sh;  // wp dims (Ci, s, taps, Co)
@@ -236,13 +242,14 @@ int runPoly(const LkcArgs* a, void* stream, bool mean3) {
       ConvtParams cp{p.x, p.bias, p.res, p.out, ci, l, co, s, padLeft, p.slope};
       if (pitched) {
         cp.xPitch = n[nint], cp.resPitch = n[nint + 1], cp.outPitch = n[nint + 2];
-        LKC_REQUIRE(cp.xPitch >= l && cp.resPitch >= lo && cp.outPitch >= lo,
+        cp.haloLeft = haloL, cp.haloRight = haloR;
+        LKC_REQUIRE(cp.xPitch >= n[1] && cp.resPitch >= lo && cp.outPitch >= lo,
                     "conv_transpose1d_poly: a row pitch is smaller than the row");
       }
       return convtTc(cp, cs->wp, cs->f16, st);
     }
   }
-  LKC_REQUIRE(!pitched || (n[nint] == l && n[nint + 1] == lo && n[nint + 2] == lo),
+  LKC_REQUIRE(!pitched || (!windowed && n[nint] == l && n[nint + 1] == lo && n[nint + 2] == lo),
               "conv_transpose1d_poly: padded rows need the tensor-core route (a prepared state of an eligible shape)");
   if (taps == 2 && ceilDiv(co, BCO) <= 65535) {
     switch (s) {

@@ -114,7 +114,7 @@ __global__ void adain1dKernel(const float* __restrict__ x, const float* __restri
 
 // One warp per (channel, 128-sample chunk): mean, then M2 = sum (v - mean)^2 from registers.
 __global__ void channelStatsKernel(const float* __restrict__ x, float* __restrict__ stats, int64_t l,
-                                   int64_t nchunks, int64_t pitch) {
+                                   int64_t nchunks, int64_t pitch, int64_t statsStride) {
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int64_t chunk = blockIdx.x * int64_t(blockDim.x >> 5) + wid, ch = blockIdx.y;
   if (chunk >= nchunks) return;
@@ -139,7 +139,7 @@ __global__ void channelStatsKernel(const float* __restrict__ x, float* __restric
   }
   q = warpSum(q);
   if (lane == 0) {
-    float* st = stats + (ch * nchunks + chunk) * 2;
+    float* st = stats + (ch * statsStride + chunk) * 2;
     st[0] = mean;
     st[1] = q;
   }
@@ -305,17 +305,18 @@ extern "C" LKC_API int lkc_adain1d_f32_cuda(const LkcArgs* a, void* stream) {
 }
 
 extern "C" LKC_API int lkc_channel_stats_f32_cuda(const LkcArgs* a, void* stream) {
-  LKC_REQUIRE(a && a->numPtrs == 2 && (a->numInts == 5 || a->numInts == 6), "channel_stats_f32_cuda: expected x | stats");
+  LKC_REQUIRE(a && a->numPtrs == 2 && a->numInts >= 5 && a->numInts <= 7, "channel_stats_f32_cuda: expected x | stats");
   const int64_t c = a->ints[0], l = a->ints[1], nchunks = statChunks(l);
-  const int64_t pitch = a->numInts == 6 ? a->ints[5] : l;  // optional trailing int: row pitch of x
-  LKC_REQUIRE(pitch >= l, "channel_stats_f32_cuda: the row pitch is smaller than the row");
+  const int64_t pitch = a->numInts >= 6 ? a->ints[5] : l;  // optional trailing ints: row pitch of x, row stride of stats in chunks
+  const int64_t statsStride = a->numInts == 7 ? a->ints[6] : nchunks;
+  LKC_REQUIRE(pitch >= l && statsStride >= nchunks, "channel_stats_f32_cuda: a row pitch is smaller than the row");
   LKC_REQUIRE(l >= 1, "channel_stats_f32_cuda: empty sequence");
   LKC_REQUIRE(a->ints[2] == c && a->ints[3] == nchunks && a->ints[4] == 2,
               "channel_stats_f32_cuda: stats must be f32[C, ceil(L/128), 2]");
   LKC_REQUIRE(c <= 65535, "channel_stats_f32_cuda: too many channels");
   if (c == 0) return 0;
   dim3 grid(static_cast<unsigned>(ceilDiv(nchunks, kThreads / 32)), static_cast<unsigned>(c));
-  channelStatsKernel<<<grid, kThreads, 0, S(stream)>>>(F(a, 0), O(a, 1), l, nchunks, pitch);
+  channelStatsKernel<<<grid, kThreads, 0, S(stream)>>>(F(a, 0), O(a, 1), l, nchunks, pitch, statsStride);
   return launched("channel_stats_f32_cuda");
 }
 

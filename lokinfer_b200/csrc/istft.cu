@@ -20,6 +20,7 @@ struct IstftArgs {
   const float* x;
   float* out;
   int64_t l, len, pitch;
+  int64_t frame0, i0;  // shard: x column 0 is frame frame0 of the l frames, out[0] is sample i0 (len samples from there)
   int nfft, hop, bins, nfMax;
 };
 
@@ -33,8 +34,9 @@ __global__ void __launch_bounds__(NTHREADS) istftKernel(const IstftArgs a) {
   float* im = re + bins * nfMax;         // [bins][nfMax]
   float* fr = im + bins * nfMax;         // [nfft][nfMax]
   const int tid = threadIdx.x;
-  const int64_t i0 = int64_t(blockIdx.x) * FB * hop;
-  const int64_t i1 = (i0 + int64_t(FB) * hop < a.len) ? i0 + int64_t(FB) * hop : a.len;
+  const int64_t iEnd = a.i0 + a.len;
+  const int64_t i0 = a.i0 + int64_t(blockIdx.x) * FB * hop;
+  const int64_t i1 = (i0 + int64_t(FB) * hop < iEnd) ? i0 + int64_t(FB) * hop : iEnd;
   const int64_t pad = nfft / 2;
   const int64_t pMin = pad + i0, pMax = pad + i1 - 1;
   const int64_t fLo = pMin >= nfft ? (pMin - nfft) / hop + 1 : 0;
@@ -55,7 +57,8 @@ __global__ void __launch_bounds__(NTHREADS) istftKernel(const IstftArgs a) {
   }
   for (int idx = tid; idx < bins * nf; idx += NTHREADS) {
     const int k = idx / nf, f = idx - k * nf;
-    const float lm = a.x[int64_t(k) * a.pitch + fLo + f], lp = a.x[int64_t(bins + k) * a.pitch + fLo + f];
+    const int64_t col = fLo + f - a.frame0;
+    const float lm = a.x[int64_t(k) * a.pitch + col], lp = a.x[int64_t(bins + k) * a.pitch + col];
     const float mag = expf(lm), ph = sinf(lp);
     float sn, cs;
     sincosf(ph, &sn, &cs);
@@ -81,7 +84,7 @@ __global__ void __launch_bounds__(NTHREADS) istftKernel(const IstftArgs a) {
       y += fr[m * nfMax + static_cast<int>(t - fLo)];
       env += win[m] * win[m];
     }
-    a.out[i] = y / env;
+    a.out[i - a.i0] = y / env;
   }
 }
 
@@ -91,18 +94,32 @@ __global__ void __launch_bounds__(NTHREADS) istftKernel(const IstftArgs a) {
 using namespace lkc;
 
 extern "C" LKC_API int lkc_istft_logits_f32_cuda(const LkcArgs* a, void* stream) {
-  LKC_REQUIRE(a && a->numPtrs == 2 && (a->numInts == 5 || a->numInts == 6),
+  LKC_REQUIRE(a && a->numPtrs == 2 && (a->numInts == 5 || a->numInts == 6 || a->numInts == 9),
               "istft_logits_f32_cuda: expected x | out, hop, n_fft");
-  const int64_t rows = a->ints[0], l = a->ints[1], len = a->ints[2], hop = a->ints[3], nfft = a->ints[4];
+  const int64_t rows = a->ints[0], len = a->ints[2], hop = a->ints[3], nfft = a->ints[4];
+  // shard extension (ints [x_pitch, frames, frame0, i0]): x holds some of the `frames` frames of the signal, from frame
+  // frame0 on, and out receives samples i0 .. i0 + len; the caller provides every frame those samples overlap
+  const bool shard = a->numInts == 9;
+  const int64_t lx = a->ints[1], l = shard ? a->ints[6] : lx;
+  const int64_t frame0 = shard ? a->ints[7] : 0, i0 = shard ? a->ints[8] : 0;
   LKC_REQUIRE(nfft >= 2 && nfft % 2 == 0 && hop >= 1, "istft_logits_f32_cuda: n_fft must be even, hop >= 1");
   LKC_REQUIRE(nfft / 2 + 1 <= 64, "istft_logits_f32_cuda: n_fft too large (at most 126)");
   LKC_REQUIRE(rows == nfft + 2, "istft_logits_f32_cuda: x must be f32[n_fft+2, L]");
-  LKC_REQUIRE(l >= 2 && len == hop * (l - 1), "istft_logits_f32_cuda: out must be f32[hop*(L-1)], L >= 2");
+  if (!shard) LKC_REQUIRE(l >= 2 && len == hop * (l - 1), "istft_logits_f32_cuda: out must be f32[hop*(L-1)], L >= 2");
+  if (shard) {
+    LKC_REQUIRE(l >= 2 && len >= 1 && i0 >= 0 && i0 + len <= hop * (l - 1) && frame0 >= 0 && frame0 + lx <= l,
+                "istft_logits_f32_cuda: shard out of range");
+    const int64_t pFirst = nfft / 2 + i0, pLast = nfft / 2 + i0 + len - 1;
+    const int64_t fFirst = pFirst >= nfft ? (pFirst - nfft) / hop + 1 : 0;
+    const int64_t fLast = pLast / hop < l - 1 ? pLast / hop : l - 1;
+    LKC_REQUIRE(fFirst >= frame0 && fLast < frame0 + lx, "istft_logits_f32_cuda: x does not hold every frame the samples overlap");
+  }
   LKC_REQUIRE(hop <= 4096, "istft_logits_f32_cuda: hop out of range");
   IstftArgs p;
   p.x = F(a, 0), p.out = O(a, 1), p.l = l, p.len = len;
-  p.pitch = a->numInts == 6 ? a->ints[5] : l;  // optional trailing int: row pitch of x
-  LKC_REQUIRE(p.pitch >= l, "istft_logits_f32_cuda: the row pitch is smaller than the row");
+  p.pitch = a->numInts >= 6 ? a->ints[5] : lx;  // optional trailing int: row pitch of x
+  p.frame0 = frame0, p.i0 = i0;
+  LKC_REQUIRE(p.pitch >= lx, "istft_logits_f32_cuda: the row pitch is smaller than the row");
   p.nfft = int(nfft), p.hop = int(hop), p.bins = int(nfft / 2 + 1);
   p.nfMax = int(FB + (nfft + hop - 1) / hop + 2);
   const size_t smem = sizeof(float) * (size_t(2) * p.bins * p.nfft + p.nfft + size_t(2) * p.bins * p.nfMax +

@@ -54,6 +54,11 @@ struct ConvFusedParams {
   int64_t ci = 0, l = 0, co = 0, k = 0, dilation = 1, padding = 0, lo = 0;
   // Row pitches in floats of the [C, L] tensors x (x2, x3 share it), residual and out; 0 = contiguous rows.
   int64_t xPitch = 0, resPitch = 0, outPitch = 0;
+  // Window extension (time-sharded tensors): output column t reads x columns xOrigin + t * stride - padding + kk *
+  // dilation; x columns outside [validLo, validHi) count as zero padding (applied after the activation). A regular
+  // call has xOrigin = 0 and the valid range [0, l) (validHi < 0 = not set). statsStride = row stride of `stats` in
+  // chunks (0 = ceil(lo / 128)): the chunk statistics can be written into a slice of a longer row.
+  int64_t xOrigin = 0, validLo = 0, validHi = -1, statsStride = 0;
   Act act = Act::None;
   float slope = 0.f, outScale = 1.f, inScale = 1.f;
   const void* state = nullptr;
@@ -78,6 +83,9 @@ struct ConvtParams {
   int64_t ci, l, co, stride, padLeft;
   float slope;
   int64_t xPitch = 0, resPitch = 0, outPitch = 0;  // row pitches in floats; 0 = contiguous rows
+  // Window extension: x holds haloLeft / haloRight real columns before / after the l columns that produce output
+  // (time-sharded tensors; the zero padding of the transposed conv then applies only where a halo is absent).
+  int64_t haloLeft = 0, haloRight = 0;
 };
 bool convtTcEligible(int64_t ci, int64_t co, int64_t k, int64_t stride, int64_t padding);
 int64_t convtTcPackFloats(int64_t ci, int64_t co, int64_t stride, bool f16);

@@ -106,16 +106,21 @@ _PITCHED = {
 }
 
 
-def _run(name, operands, outs, attrs_int=(), attrs_float=(), state=None):
+def _run(name, operands, outs, attrs_int=(), attrs_float=(), state=None, window=None):
+    """window: the ints of the window extension of include/lkc.h (time-sharded tensors, see timeshard.py); the row
+    pitches are then always passed and the caller vouches for the layout of every operand."""
     ts = list(operands) + list(outs)
     check(all(t.is_cuda and t.device == ts[0].device for t in ts),
           f"{name}: operands must live on one cuda device (use to_cuda); there is no CPU path")
     ints = [d for t in ts for d in t.shape] + list(attrs_int)
     pitched = _PITCHED.get(name, ())
-    for i, t in enumerate(ts):
-        check(t.is_contiguous() or i in pitched, f"{name}: operand {i} must be contiguous")
-    if any(not ts[i].is_contiguous() for i in pitched):
+    if window is None:
+        for i, t in enumerate(ts):
+            check(t.is_contiguous() or i in pitched, f"{name}: operand {i} must be contiguous")
+    if window is not None or any(not ts[i].is_contiguous() for i in pitched):
         ints += [int(ts[i].stride(0)) for i in pitched]
+    if window is not None:
+        ints += [int(v) for v in window]
     with torch.cuda.device(ts[0].device):
         prof = _profile
         if prof is None:
