@@ -303,6 +303,54 @@ def measure_batch64(gen, dev, rank: int, world: int, steps: int, warmup: int) ->
             "rank_loads_T": sharding.loads(lengths, plan)}
 
 
+def measure_time_sharded(gen, dev, rank: int, world: int, t: int, steps: int, single_ms: float) -> dict | None:
+    """BASELINE config 2 on N GPUs: ONE utterance of t frames cut along time over the ranks (lokinfer_b200/timeshard.py:
+    halo columns by plain peer stores + release flags, chunk statistics gathered into every rank's row, bounded
+    waits), one captured graph replay per step on every rank, time = max over ranks. Strong scaling of a single
+    utterance: about 53 exchanges per forward, each a push kernel, a peer round trip and a wait kernel, so the step is
+    bound by exchange latency; the record says how far. Returns the record on rank 0."""
+    import torch.distributed as dist
+
+    from lokinfer_b200 import ops, timeshard as ts
+
+    inp = synth.generator_inputs(t, 1)  # the same utterance on every rank
+    x, har, s = [ops.to_cuda(inp[k], dev) for k in ("x", "har", "s")]
+    single = gen.forward(x, har, s)
+    fabric = ts.IpcFabric(ts.TimeShardedGenerator.arena_bytes(t, world), dev)
+    tsg = ts.TimeShardedGenerator(gen, t, rank, world, fabric)
+    lo, hi = tsg.part.bs[rank], tsg.part.bs[rank + 1]
+    dist.barrier()
+    graph = tsg.capture(x, har, s)
+    for _ in range(3):
+        dist.barrier()
+        graph.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    vals = torch.tensor([a.elapsed_time(b), (tsg.audio - single[lo:hi]).abs().max().item(), float(tsg.status())],
+                        dtype=torch.float64, device=dev)
+    dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    if rank != 0:
+        return None
+    ms = float(vals[0].item()) / steps
+    audio_s = synth.shapes(t)["S"] / SAMPLE_RATE
+    return {"workload": f"kokoro_generator_T{t} time-sharded over {world} GPUs", "ms_per_step": ms,
+            "value": audio_s / (ms * 1e-3), "unit": UNIT, "scaling": "strong",
+            "single_gpu_ms_per_step": single_ms, "speedup_vs_single_gpu": single_ms / ms,
+            "frames_per_rank": [y - x_ for x_, y in zip(tsg.part.bx, tsg.part.bx[1:])],
+            "exchanges_per_forward": 53, "us_per_exchange_over_ideal": (ms - single_ms / world) * 1e3 / 53,
+            "max_abs_diff_vs_single_gpu": float(vals[1].item()), "wait_status": int(vals[2].item()),
+            "limiter": "exchange latency: every conv output is followed by a push kernel, the peer stores with "
+                       "their release flags and a wait kernel on the consumer side before the next conv may start; "
+                       "NCCL is not on this path"}
+
+
 def init_nccl(dev):
     """Process group over NCCL (rank / world size / master address from the torchrun environment). NCCL prints its
     version banner on stdout when the communicator is created: stdout is pointed at stderr until the first
@@ -402,6 +450,9 @@ def run_ours(args, rank: int, local_rank: int, world: int):
 
     # config 3 on every rank (strong scaling), before the single-rank extras
     batch64 = None if args.no_extras else measure_batch64(gen, dev, rank, world, 3, 3)
+    time_sharded = None
+    if world > 1 and not args.no_extras:
+        time_sharded = measure_time_sharded(gen, dev, rank, world, t, args.steps, ms_dev / args.steps)
     roofline, cpu_base, kernels = None, None, None
     if rank == 0:
         # per-launch timing of the fused conv kernels (eager pass, CUDA event pair around every launch)
@@ -464,6 +515,8 @@ def run_ours(args, rank: int, local_rank: int, world: int):
             line["cpu_baseline"] = cpu_base
         if not args.no_extras:
             line["batch64"] = batch64
+            if time_sharded is not None:
+                line["time_sharded"] = time_sharded
             line["cfg1"] = measure_cfg1(gen, dev, args.steps)
             line["cfg0"] = measure_cfg0(dev, peak)
             line["sweep"] = measure_sweep(dev, peak)

@@ -192,6 +192,8 @@ class TimeShardedGenerator:
         self.tickets = a.alloc((self.max_sync,), torch.int32)
         self.flags = a.alloc((self.max_sync, MAX_FLAGS), torch.int32)
         self._bufs, self._cursor, self._sync = [], 0, 0
+        self._stream, self._keep = None, []
+        self.concurrent = True  # independent branches on side streams (as Generator.forward does)
         self._lib = _lib.lib()
         self._lib.lkc_shard_push.argtypes = [ctypes.POINTER(_Push), ctypes.c_void_p]
         self._lib.lkc_shard_wait.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p,
@@ -300,8 +302,15 @@ class TimeShardedGenerator:
         """Generator step: push, then (after every rank has pushed, in the lock-step fabric) wait."""
         self._push(buf, stats)
         yield
+        torch.cuda.set_stream(self._stream)  # another rank of this process may have switched streams meanwhile
         self._wait(buf is not None, stats is not None)
         self._sync += 1
+
+    def _use(self, stream):
+        """Queues what follows on `stream` (branches that do not depend on each other go to different streams, so that
+        the exchange latency of one overlaps the convs of another)."""
+        self._stream = stream
+        torch.cuda.set_stream(stream)
 
     # ------------------------------------------------------------------ sharded ops
 
@@ -362,9 +371,12 @@ class TimeShardedGenerator:
         gen, part, k, n = self.gen, self.part, self.rank, self.world
         gw = gen.w
         first, last = self._ends()
-        self._cursor, self._sync = 0, 0
-        stream = ctypes.c_void_p(ops._stream())
-        with torch.cuda.device(self.device):
+        self._cursor, self._sync, self._keep = 0, 0, []
+        cur = torch.cuda.current_stream(self.device)
+        side = gen._side_streams() if self.concurrent else [cur] * 4
+        try:
+            self._use(cur)
+            stream = ctypes.c_void_p(cur.cuda_stream)
             # a new epoch; nobody may write into this rank's margins before it has finished reading the last forward
             if self._lib.lkc_shard_epoch_bump(ctypes.c_void_p(self.ctl[0:1].data_ptr()), stream) != 0:
                 raise _lib.LkcError(_lib.last_error())
@@ -374,7 +386,9 @@ class TimeShardedGenerator:
             self._sync = 0
             gb = gen.style(s)
             noise = [None, None]
-            for i, k_noise in enumerate((7, 11)):
+            for i, k_noise in enumerate((7, 11)):  # the two noise branches only need `har`: side streams 0 and 1
+                side[i].wait_stream(cur)
+                self._use(side[i])
                 lo, hi = part.rng(i, k)
                 xs = self._buf(256 if i == 0 else 128, i)
                 if i == 0:
@@ -386,11 +400,14 @@ class TimeShardedGenerator:
                     hs = har[:, lo:hi].contiguous()
                     ops._run("conv1d_f32_cuda", [hs, gw["noise_convs.1.weight"], gw["noise_convs.1.bias"]], [xs.own],
                              attrs_int=[1, 0, 1], window=[0, 0, hi - lo])
+                self._keep.append(hs)
                 st = self._channel_stats(xs, i)
                 yield from self._exchange(xs, st)
                 noise[i], _ = yield from self._resblock(xs, st, gb, f"noise_res.{i}", k_noise, i)
             rb = None
             for i, (k_up, u) in enumerate(((20, 10), (12, 6))):
+                self._use(cur)
+                cur.wait_stream(side[i])
                 xi = self._buf(256 if i == 0 else 128, i)
                 if i == 0:
                     hl, hr = int(not first), int(not last)
@@ -422,10 +439,16 @@ class TimeShardedGenerator:
                              window=[hl, hr])
                 st = self._channel_stats(xi, i)
                 yield from self._exchange(xi, st)
-                new_rb = []
-                for j in range(3):
-                    r, _ = yield from self._resblock(xi, st, gb, f"resblocks.{3 * i + j}", RES_KERNELS[j], i)
-                    new_rb.append(r)
+                side[2].wait_stream(cur)
+                side[3].wait_stream(cur)
+                new_rb = [None, None, None]
+                # the k = 11 block is the longest: it stays on the main stream
+                for j, stream_j in ((2, cur), (1, side[2]), (0, side[3])):
+                    self._use(stream_j)
+                    new_rb[j], _ = yield from self._resblock(xi, st, gb, f"resblocks.{3 * i + j}", RES_KERNELS[j], i)
+                self._use(cur)
+                cur.wait_stream(side[2])
+                cur.wait_stream(side[3])
                 rb = new_rb
             xm = self._add3(rb[0], rb[1], rb[2])
             post, _ = self._conv("conv1d_leaky_f32_cuda", xm, "conv_post", gen.ident128, 7, 1, 1, slope=0.01)
@@ -450,6 +473,8 @@ class TimeShardedGenerator:
             d.epoch, d.ticket = self.ctl[0:1].data_ptr(), self.tickets[done_sp: done_sp + 1].data_ptr()
             if nf and self._lib.lkc_shard_push(ctypes.byref(d), stream) != 0:
                 raise _lib.LkcError(_lib.last_error())
+        finally:
+            torch.cuda.set_stream(cur)
 
     def forward(self, x, har, s):
         """One process per GPU: runs the steps back to back (push, then wait). Returns this rank's samples."""

@@ -1,6 +1,7 @@
 """Time sharding with one process per GPU (CUDA IPC peer memory, plain peer stores, release / acquire flags): needs at
 least two GPUs; the single-GPU lock-step form of the same logic is in test_gpu_timeshard.py."""
 import os
+import re
 import subprocess
 import sys
 from pathlib import Path
@@ -20,6 +21,5 @@ def test_time_sharded_processes(cuda, world, t):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), str(worker), str(t)],
                        capture_output=True, text=True, timeout=600, env=env)
-    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("rank ")]
-    assert r.returncode == 0 and len(lines) == world and all(ln.endswith("OK") for ln in lines), \
-        r.stdout[-2000:] + r.stderr[-2000:]
+    verdicts = re.findall(r"rank \d+/\d+ T=\d+ samples .*? status \d+ (OK|FAIL)", r.stdout)  # ranks may share a line
+    assert r.returncode == 0 and verdicts == ["OK"] * world, r.stdout[-2000:] + r.stderr[-2000:]
