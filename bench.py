@@ -602,6 +602,63 @@ def run_sweep(args):
                           "tc_status": ops.conv_tc_status()}), flush=True)
 
 
+def run_sweep_hbm(args):
+    """The HBM-bound kernels of the path at the shapes of the 26 s case, one JSON line each: channel_stats over
+    [128, 124801] and [256, 20800] (reads 4 C L bytes), adain_affine (reads the chunk statistics), add3_scale
+    (3 reads + 1 write), istft_logits over [22, 124801] (reads 4 * 22 * L bytes, writes 4 * 5 (L - 1)). Achieved GB/s =
+    algorithmic bytes / event time, against the measured HBM copy bandwidth. Rows are padded to 16 bytes, as the
+    generator keeps them."""
+    from lokinfer_b200 import ops
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    dev = torch.device("cuda:0")
+    pk = peaks()
+    g = torch.Generator(device=dev)
+    g.manual_seed(9)
+    flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device=dev)  # 256 MB: larger than the L2
+
+    def timed(fn):
+        ms = []
+        for i in range(args.warmup + args.steps):
+            flush.zero_()  # evicts the operands from the L2 between launches
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                ms.append(a.elapsed_time(b))
+        return float(np.median(ms))
+
+    with ops.padded_rows():
+        for c, l in ((128, 124801), (256, 20800)):
+            x = ops.to_cuda(torch.randn(c, l, device=dev, generator=g), dev, rows=True)
+            ms = timed(lambda: ops.channel_stats_f32_cuda(x))
+            st = ops.channel_stats_f32_cuda(x)
+            gbs = 4.0 * c * l / (ms * 1e-3) / 1e9
+            print(json.dumps({"sweep": "channel_stats_f32_cuda", "C": c, "L": l, "ms": ms, "gbs": gbs,
+                              "frac_hbm": gbs / pk["hbm_gbs"], "peak_gbs": pk["hbm_gbs"], "l2": "flushed"}), flush=True)
+            gb = torch.randn(2 * c, device=dev, generator=g)
+            ms = timed(lambda: ops.adain_affine_f32_cuda(st, gb, length=l))
+            gbs = 4.0 * st.numel() / (ms * 1e-3) / 1e9
+            print(json.dumps({"sweep": "adain_affine_f32_cuda", "C": c, "L": l, "ms": ms, "gbs": gbs,
+                              "frac_hbm": gbs / pk["hbm_gbs"], "note": "latency-bound: C blocks, one row of chunk "
+                              "statistics each"}), flush=True)
+            y, z = (ops.to_cuda(torch.randn(c, l, device=dev, generator=g), dev, rows=True) for _ in range(2))
+            ms = timed(lambda: ops.add3_scale_f32_cuda(x, y, z, 1.0 / 3.0))
+            gbs = 16.0 * c * x.stride(0) / (ms * 1e-3) / 1e9
+            print(json.dumps({"sweep": "add3_scale_f32_cuda", "C": c, "L": l, "ms": ms, "gbs": gbs,
+                              "frac_hbm": gbs / pk["hbm_gbs"]}), flush=True)
+        l = 124801
+        post = ops.to_cuda(torch.randn(22, l, device=dev, generator=g) * 0.5, dev, rows=True)
+        ms = timed(lambda: ops.istft_logits_f32_cuda(post))
+        gbs = (4.0 * 22 * l + 4.0 * 5 * (l - 1)) / (ms * 1e-3) / 1e9
+        print(json.dumps({"sweep": "istft_logits_f32_cuda", "L": l, "ms": ms, "gbs": gbs,
+                          "frac_hbm": gbs / pk["hbm_gbs"],
+                          "note": "13.5 MB per launch: too small to fill the HBM pipes (launch + one wave of blocks)"}),
+              flush=True)
+
+
 def run_sweep_convt(args):
     """ConvTranspose sweep: the generator's two upsamplers (512 -> 256, k 20, s 10, p 5) and (256 -> 128, k 12, s 6,
     p 3) at Lin = 320 and 2080, one conv_transpose1d_poly launch (leaky prologue, residual, pad_left as in the
@@ -655,7 +712,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the other BASELINE configs (cfg0, cfg1, sweep, batch64) carried as extra keys")
-    ap.add_argument("--sweep", default=None, choices=["conv", "convt"],
+    ap.add_argument("--sweep", default=None, choices=["conv", "convt", "hbm"],
                     help="run the conv / ConvTranspose kernel sweep instead of the generator")
     ap.add_argument("--workload", default="single", choices=["single", "batch64"],
                     help="single: one utterance of --t frames per GPU (default, weak scaling); batch64: 64 utterances of "
@@ -674,6 +731,10 @@ def main():
     if args.sweep == "convt":
         if rank == 0:
             run_sweep_convt(args)
+        return
+    if args.sweep == "hbm":
+        if rank == 0:
+            run_sweep_hbm(args)
         return
     if args.sweep:
         if rank == 0:
