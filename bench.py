@@ -443,6 +443,11 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     clocks = sampler.stop() if sampler else None
     ms_e2e = timed(lambda: gen.synthesize(host[0], host[1], host[2], audio_host), args.steps, max(1, args.warmup // 2))
 
+    # input option B: the `har` input computed on the device from the F0 curve (harmonic source with in-kernel noise +
+    # STFT, the step before the generator in the reference graph); h2d carries x, f0 and s only
+    f0_host = torch.from_numpy(synth.f0_curve(t, 1 + rank)).pin_memory()
+    ms_e2e_f0 = timed(lambda: gen.synthesize_f0(host[0], f0_host, 1234 + rank, host[2], audio_host), args.steps,
+                      max(1, args.warmup // 2))
     value = world * audio_s * args.steps / (ms_dev * 1e-3)
     e2e = world * audio_s * args.steps / (ms_e2e * 1e-3)
     h2d = sum(h.numel() * 4 for h in host)
@@ -508,6 +513,11 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                        "conv_gflop_per_utterance": conv_flops_per_t() * t / 1e9},
             "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / args.steps},
+            "e2e_from_f0": {"value": world * audio_s * args.steps / (ms_e2e_f0 * 1e-3), "unit": UNIT,
+                            "h2d_bytes_per_step": host[0].numel() * 4 + f0_host.numel() * 4 + host[2].numel() * 4,
+                            "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_f0 / args.steps,
+                            "note": "har = STFT(harmonic_source_rng(F0, seed)) computed on the device inside the "
+                                    "timed region (Generator.synthesize_f0)"},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": roofline, "clocks": clocks, "kernels": kernels,
         }

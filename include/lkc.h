@@ -204,9 +204,15 @@ LKC_API int lkc_istft_logits_f32_cuda(const LkcArgs* a, void* stream);
  * converted to float32, as in the reference). The float32 operation order of the reference kernel is part of the
  * contract (the phase reaches ~1e6 rad). Uses a phase table of 9 n floats as scratch between its two kernels: the
  * library keeps one grow-only buffer per device, so the first call on a device (and any call with a larger n) calls
- * cudaMalloc and must not be inside a stream capture; calls on one device must not overlap in time.
- * The in-kernel random variant (harmonic_source_rng_f32_cpu) is not provided. */
+ * cudaMalloc and must not be inside a stream capture; calls on one device must not overlap in time. */
 LKC_API int lkc_harmonic_source_f32_cuda(const LkcArgs* a, void* stream);
+/* harmonic_source_rng_f32_cpu (kokoro_signal.cpp:42-96, 192, adapter :375-380; rule ops/kokoro.py:429-435): the same
+ * op with the noise drawn in the kernel: Philox4x32-10 keyed by the 64-bit seed, counters (sample_lo, sample_hi, blk,
+ * 0x6C6B6E7A) for blk = 0..2, Box-Muller on the word pairs; deterministic per seed and independent of the launch
+ * geometry (not torch's bit stream, as in the reference).
+ * ptrs f0[n] w[9] b[1] seed | out[300n], where ptrs[3] points at an 8-byte HOST slot holding the i64 seed (the
+ * reference's packing of scalar operands); ints f0(1) w(1) b(1) out(1). Same scratch rule as above. */
+LKC_API int lkc_harmonic_source_rng_f32_cuda(const LkcArgs* a, void* stream);
 /* The same op (same packing, same kernels, bit-identical result) for callers that must not allocate; it has no
  * counterpart in the reference. The phase table lives in a fixed device array of the library, so no call path
  * allocates or frees device memory. Limit: n <= 4096 frames (51 s of audio); larger inputs are rejected. The first

@@ -300,6 +300,7 @@ const Entry kEntries[] = {
     {"convt_tc_pack_f32_cuda", lkc_convt_tc_pack_f32_cuda},
     {"gemm_bias_f32_cuda", lkc_gemm_bias_f32_cuda},
     {"harmonic_source_f32_cuda", lkc_harmonic_source_f32_cuda},
+    {"harmonic_source_rng_f32_cuda", lkc_harmonic_source_rng_f32_cuda},
     {"istft_logits_f32_cuda", lkc_istft_logits_f32_cuda},
     {"leaky_relu_f32_cuda", lkc_leaky_relu_f32_cuda},
     {"pad_reflect1d_f32_cuda", lkc_pad_reflect1d_f32_cuda},

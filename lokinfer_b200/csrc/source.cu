@@ -21,6 +21,8 @@
 // built in double), re / im accumulated over m = 0..n_fft-1 in order with separate multiply and add, imaginary part
 // exactly 0 at DC and Nyquist, rows [0, bins) = sqrt(re^2 + im^2), rows [bins, 2 bins) = atan2(im, re).
 // Both are small HBM / latency-bound kernels (one thread per output sample or frame, coalesced along time).
+#include <cstring>
+
 #include "lkc_common.h"
 
 namespace lkc {
@@ -58,8 +60,47 @@ __global__ void __launch_bounds__(288) harmonicPhaseKernel(const float* __restri
   }
 }
 
+// Counter-based Philox4x32-10 (Salmon et al. 2011), the generator of the reference's in-kernel noise
+// (kernels/cpu/kokoro_signal.cpp:42-96): sample i uses counters (i_lo, i_hi, blk, 0x6C6B6E7A) for blk = 0..2 under
+// the key (seed_lo, seed_hi); Box-Muller on the word pairs (c0, c1) and (c2, c3) of each block gives its normals
+// u1 = (float(c_even) + 0.5) * 2^-32, u2 = float(c_odd) * 2^-32, r = sqrt(-2 ln u1), (r cos(2 pi u2), r sin(2 pi u2));
+// the 9 harmonics take the first 9 of the 12. Stateless: the noise depends only on (seed, sample index).
+__device__ __forceinline__ void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t lo0 = c[0] * 0xD2511F53u, hi0 = __umulhi(c[0], 0xD2511F53u);
+    const uint32_t lo1 = c[2] * 0xCD9E8D57u, hi1 = __umulhi(c[2], 0xCD9E8D57u);
+    const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+    c[0] = n0, c[1] = lo1, c[2] = n2, c[3] = lo0;
+    k0 += 0x9E3779B9u, k1 += 0xBB67AE85u;
+  }
+}
+
+__device__ __forceinline__ void philoxNormals(uint64_t seed, int64_t i, float* nz /* kHarmonics */) {
+  const uint32_t k0 = uint32_t(seed), k1 = uint32_t(seed >> 32);
+#pragma unroll
+  for (int blk = 0; blk * 4 < 10; ++blk) {  // kHarmonics + 1 = 10: three blocks
+    uint32_t c[4] = {uint32_t(uint64_t(i)), uint32_t(uint64_t(i) >> 32), uint32_t(blk), 0x6C6B6E7Au};
+    philox4x32_10(c, k0, k1);
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int id = blk * 4 + 2 * q;
+      if (id >= 9) break;
+      const float u1 = __fmul_rn(__fadd_rn(__uint2float_rn(c[2 * q]), 0.5f), 2.3283064e-10f);
+      const float u2 = __fmul_rn(__uint2float_rn(c[2 * q + 1]), 2.3283064e-10f);
+      const float r = sqrtf(__fmul_rn(-2.f, logf(u1)));
+      const float t = __fmul_rn(6.2831853f, u2);
+      nz[id] = __fmul_rn(r, cosf(t));
+      if (id + 1 < 9) nz[id + 1] = __fmul_rn(r, sinf(t));
+    }
+  }
+}
+
+// RNG = false: the noise is the operand `noise` f32[300 n, 9]; RNG = true: it is drawn in the kernel from `seed`.
+template <bool RNG>
 __global__ void __launch_bounds__(256) harmonicSourceKernel(const float* __restrict__ f0, const float* __restrict__ noise,
-                                                            const float* __restrict__ w, const float* __restrict__ b,
+                                                            uint64_t seed, const float* __restrict__ w,
+                                                            const float* __restrict__ b,
                                                             const float* __restrict__ p300, float* __restrict__ out,
                                                             int64_t n) {
   const int64_t s = n * kUp;
@@ -81,7 +122,10 @@ __global__ void __launch_bounds__(256) harmonicSourceKernel(const float* __restr
     const float uv = voiced ? 1.f : 0.f, amp = voiced ? ampV : ampU;
     const float* r0 = p300 + i0 * kHarmonics;
     const float* r1 = p300 + i1 * kHarmonics;
-    const float* nz = noise + i * kHarmonics;
+    float nzr[kHarmonics];
+    const float* nz = nzr;
+    if constexpr (RNG) philoxNormals(seed, i, nzr);
+    else nz = noise + i * kHarmonics;
     float y = 0.f;
 #pragma unroll
     for (int h = 0; h < kHarmonics; ++h) {
@@ -155,12 +199,14 @@ float* phaseScratch(int64_t floats) {
 
 }  // namespace
 
-int harmonicSourceLaunch(const float* f0, const float* noise, const float* w, const float* b, float* p300, float* out,
-                         int64_t n, cudaStream_t s) {
+// noise != null: the noise operand; noise == null: drawn in the kernel from seed.
+int harmonicSourceLaunch(const float* f0, const float* noise, uint64_t seed, const float* w, const float* b, float* p300,
+                         float* out, int64_t n, cudaStream_t s) {
   harmonicPhaseKernel<<<1, 288, 0, s>>>(f0, p300, n);
   const int64_t samples = n * kUp;
   const int blocks = int(ceilDiv(samples, 256) > 148 * 16 ? 148 * 16 : ceilDiv(samples, 256));
-  harmonicSourceKernel<<<blocks, 256, 0, s>>>(f0, noise, w, b, p300, out, n);
+  if (noise) harmonicSourceKernel<false><<<blocks, 256, 0, s>>>(f0, noise, 0, w, b, p300, out, n);
+  else harmonicSourceKernel<true><<<blocks, 256, 0, s>>>(f0, nullptr, seed, w, b, p300, out, n);
   return launched("harmonic_source_f32_cuda");
 }
 
@@ -177,7 +223,23 @@ extern "C" LKC_API int lkc_harmonic_source_f32_cuda(const LkcArgs* a, void* stre
   LKC_REQUIRE(a->ints[5] == n * kUp, "harmonic_source_f32_cuda: out must be f32[300n]");
   float* p300 = phaseScratch(n * kHarmonics);
   LKC_REQUIRE(p300 != nullptr, "harmonic_source_f32_cuda: cannot allocate the phase table");
-  return harmonicSourceLaunch(F(a, 0), F(a, 1), F(a, 2), F(a, 3), p300, O(a, 4), n, S(stream));
+  return harmonicSourceLaunch(F(a, 0), F(a, 1), 0, F(a, 2), F(a, 3), p300, O(a, 4), n, S(stream));
+}
+
+// operands f0(n), w(9), b(1), seed (an i64 scalar: ptrs[3] points at an 8-byte HOST slot, as the reference packs
+// scalars); out(300 n). ints: f0, w, b, out shapes (kernels/cpu/kokoro_signal.cpp:375-380).
+extern "C" LKC_API int lkc_harmonic_source_rng_f32_cuda(const LkcArgs* a, void* stream) {
+  LKC_REQUIRE(a && a->numPtrs == 5 && a->numInts == 4 && a->ptrs[3], "harmonic_source_rng_f32_cuda: expected f0 w b seed | out");
+  const int64_t n = a->ints[0];
+  LKC_REQUIRE(n >= 1 && n <= (int64_t(1) << 23) / kUp, "harmonic_source_rng_f32_cuda: f0 must be f32[n], 1 <= n <= 27962");
+  LKC_REQUIRE(a->ints[1] == kHarmonics && a->ints[2] == 1, "harmonic_source_rng_f32_cuda: w must be f32[9], b f32[1]");
+  LKC_REQUIRE(a->ints[3] == n * kUp, "harmonic_source_rng_f32_cuda: out must be f32[300n]");
+  int64_t seed;
+  std::memcpy(&seed, a->ptrs[3], sizeof seed);
+  float* p300 = phaseScratch(n * kHarmonics);
+  LKC_REQUIRE(p300 != nullptr, "harmonic_source_rng_f32_cuda: cannot allocate the phase table");
+  return harmonicSourceLaunch(F(a, 0), nullptr, static_cast<uint64_t>(seed), F(a, 1), F(a, 2), p300, O(a, 4), n,
+                              S(stream));
 }
 
 extern "C" LKC_API int lkc_stft_magphase_f32_cuda(const LkcArgs* a, void* stream) {
@@ -228,5 +290,5 @@ extern "C" LKC_API int lkc_harmonic_source_noalloc_f32_cuda(const LkcArgs* a, vo
     if (e != cudaSuccess) return failCuda("harmonic_source_noalloc_f32_cuda: cudaGetSymbolAddress", e);
     table[dev] = ptr;
   }
-  return harmonicSourceLaunch(F(a, 0), F(a, 1), F(a, 2), F(a, 3), table[dev], O(a, 4), n, S(stream));
+  return harmonicSourceLaunch(F(a, 0), F(a, 1), 0, F(a, 2), F(a, 3), table[dev], O(a, 4), n, S(stream));
 }

@@ -103,11 +103,15 @@ class Generator:
     def har_from_f0(self, f0, noise):
         """The generator's `har` input from the F0 curve, as the reference graph computes it before the generator
         (models/kokoro/model.py:720-726): harmonic source (9 harmonics, x300, Linear 9 -> 1, tanh) then STFT(n_fft 20,
-        hop 5) -> cat(magnitude, phase). f0 f32[T] (one value per frame of x), noise f32[300 T, 9] (the normal draw the
-        reference takes from its generator; an operand here) -> f32[22, 60 T + 1]."""
+        hop 5) -> cat(magnitude, phase). f0 f32[T] (one value per frame of x); noise = f32[300 T, 9] (the normal draw
+        as an operand) or an int seed (drawn in the kernel, models/kokoro/model.py:721-722) -> f32[22, 60 T + 1]."""
         ops.check("m_source.l_linear.weight" in self.w, "the state dict has no m_source.l_linear weights")
         w9 = self.w["m_source.l_linear.weight"].reshape(9)
-        src = ops.harmonic_source_f32_cuda(f0, noise, w9, self.w["m_source.l_linear.bias"].reshape(1))
+        bias = self.w["m_source.l_linear.bias"].reshape(1)
+        if isinstance(noise, int):  # a seed: the noise is drawn in the kernel (the variant the reference graph ships)
+            src = ops.harmonic_source_rng_f32_cuda(f0, w9, bias, noise)
+        else:
+            src = ops.harmonic_source_f32_cuda(f0, noise, w9, bias)
         return ops.stft_magphase_f32_cuda(src, n_fft=20, hop=5)
 
     def forward(self, x, har, s, fused=True, outputs=("audio",), concurrent=True, pad_rows=True):
@@ -247,6 +251,27 @@ class Generator:
         bufs["graph"] = g
         self._graphs[t] = bufs
         return bufs
+
+    def synthesize_f0(self, x_host, f0_host, seed, s_host, audio_host=None):
+        """End-to-end call with HOST buffers that starts one step earlier than synthesize(): the `har` input is
+        computed on the device from the F0 curve f32[T] (harmonic source with in-kernel noise from `seed`, then the
+        STFT), as the reference graph does before its generator (models/kokoro/model.py:720-726)."""
+        t = int(x_host.shape[1])
+        b = self.capture(t)
+        f0 = torch.empty(t, dtype=torch.float32, device=self.device)
+        f0.copy_(f0_host, non_blocking=True)
+        b["x"].copy_(x_host, non_blocking=True)
+        b["s"].copy_(s_host, non_blocking=True)
+        b["har"].copy_(self.har_from_f0(f0, int(seed)))
+        b["graph"].replay()
+        if audio_host is None:
+            audio_host = torch.empty(b["audio"].shape, dtype=torch.float32, pin_memory=True)
+        audio_host.copy_(b["audio"], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        status = ops.conv_tc_status()
+        if status != 0:
+            raise RuntimeError(f"tensor-core conv kernels reported status {status:#x}")
+        return audio_host
 
     def synthesize(self, x_host, har_host, s_host, audio_host=None):
         """End-to-end call with HOST buffers (pinned torch tensors for async copies): host -> device copies, one

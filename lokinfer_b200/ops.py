@@ -433,6 +433,32 @@ def harmonic_source_f32_cuda(f0, noise, w, b):
     return out
 
 
+def harmonic_source_rng_f32_cuda(f0, w, b, seed):
+    """Same as harmonic_source_f32_cuda, with the noise generated in-kernel from `seed` (an i64 scalar), like
+    torch's randn_like after manual_seed (Philox4x32-10 + Box-Muller; deterministic per seed, not torch's bit stream)
+    (python/lokinfer/ops/kokoro.py:429-435). The seed travels as the reference packs scalar operands: a pointer to an
+    8-byte host slot."""
+    import ctypes
+    _f32(f0, w, b, rank=1)
+    check(isinstance(seed, int) and not isinstance(seed, bool) and -(1 << 63) <= seed < (1 << 64),
+          "seed must be an i64 scalar")
+    check(w.shape[0] == 9 and b.shape[0] == 1, "w must be f32[9], b f32[1]")
+    check(1 <= f0.shape[0] <= 27962, "f0 must hold 1..27962 frames")
+    out = _new(f0, (f0.shape[0] * 300,))
+    if not f0.is_cuda:
+        return out
+    check(all(t.is_cuda and t.device == f0.device and t.is_contiguous() for t in (f0, w, b)),
+          "harmonic_source_rng_f32_cuda: operands must be contiguous tensors of one cuda device; there is no CPU path")
+    slot = ctypes.c_int64(seed if seed < (1 << 63) else seed - (1 << 64))
+    ptrs = [f0.data_ptr(), w.data_ptr(), b.data_ptr(), ctypes.addressof(slot), out.data_ptr()]
+    ints = [f0.shape[0], 9, 1, out.shape[0]]
+    with torch.cuda.device(f0.device):
+        _lib.run("harmonic_source_rng_f32_cuda", ptrs, ints, (), None, _stream())
+    if _profile is not None:
+        _profile.count += 1
+    return out
+
+
 def stft_magphase_f32_cuda(x, n_fft=20, hop=5):
     """torch.stft(center, reflect, periodic hann(n_fft), onesided) -> cat(abs, angle):
     f32[S] -> f32[n_fft+2, S//hop+1] (python/lokinfer/ops/kokoro.py:438-449)."""

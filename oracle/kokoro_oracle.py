@@ -304,6 +304,50 @@ def harmonic_source(f0, noise, w, b):
     return torch.from_numpy(np.tanh((y + b[0]).astype(np.float64)).astype(np.float32))
 
 
+def philox4x32_10(counters, key):
+    """Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11), vectorised:
+    counters uint32[..., 4], key (k0, k1) -> uint32[..., 4]. The round function and constants are the published ones;
+    the reference uses the same (kernels/cpu/kokoro_signal.cpp:42-64)."""
+    c = [counters[..., i].astype(np.uint64) for i in range(4)]
+    k0, k1 = np.uint64(key[0]), np.uint64(key[1])
+    m0, m1, mask = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57), np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0, p1 = c[0] * m0, c[2] * m1
+        hi0, lo0, hi1, lo1 = p0 >> np.uint64(32), p0 & mask, p1 >> np.uint64(32), p1 & mask
+        c = [hi1 ^ c[1] ^ k0, lo1, hi0 ^ c[3] ^ k1, lo0]
+        k0, k1 = (k0 + np.uint64(0x9E3779B9)) & mask, (k1 + np.uint64(0xBB67AE85)) & mask
+    return np.stack(c, axis=-1).astype(np.uint32)
+
+
+def source_noise_philox(seed, samples):
+    """The normal draw of harmonic_source_rng_f32_cpu (kernels/cpu/kokoro_signal.cpp:66-96): sample i, block blk in
+    0..2: counters (i_lo, i_hi, blk, 0x6C6B6E7A), key = the 64-bit seed; Box-Muller in float32 on the word pairs
+    (c0, c1), (c2, c3) -> normals 4 blk + (0, 1) and 4 blk + (2, 3); the first 9 are used. -> float32[samples, 9]."""
+    i = np.arange(samples, dtype=np.uint64)
+    seed = int(seed) & 0xFFFFFFFFFFFFFFFF
+    key = (seed & 0xFFFFFFFF, seed >> 32)
+    out = np.zeros((samples, 12), dtype=np.float32)
+    scale = np.float32(2.3283064e-10)
+    for blk in range(3):
+        ctr = np.stack([i & np.uint64(0xFFFFFFFF), i >> np.uint64(32), np.full(samples, blk, np.uint64),
+                        np.full(samples, 0x6C6B6E7A, np.uint64)], axis=-1).astype(np.uint32)
+        c = philox4x32_10(ctr, key)
+        for q in range(2):
+            u1 = (c[:, 2 * q].astype(np.float32) + np.float32(0.5)) * scale
+            u2 = c[:, 2 * q + 1].astype(np.float32) * scale
+            r = np.sqrt(np.float32(-2.0) * np.log(u1)).astype(np.float32)
+            t = (np.float32(6.2831853) * u2).astype(np.float32)
+            out[:, 4 * blk + 2 * q] = r * np.cos(t)
+            out[:, 4 * blk + 2 * q + 1] = r * np.sin(t)
+    return out[:, :SOURCE_HARMONICS].copy()
+
+
+def harmonic_source_rng(f0, w, b, seed):
+    """harmonic_source with the noise drawn from `seed` (python/lokinfer/ops/kokoro.py:429-435)."""
+    f0 = np.asarray(f0, dtype=np.float32)
+    return harmonic_source(f0, source_noise_philox(seed, f0.shape[0] * SOURCE_UP), w, b)
+
+
 def harmonic_source_torch(f0, noise, w, b):
     """The torch-op form the reference kernel says it mirrors (kokoro_signal.cpp:98-103): remainder, cumsum (double),
     F.interpolate(linear, align_corners=False), sin, Linear, tanh. Agrees with harmonic_source except where this

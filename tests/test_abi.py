@@ -35,7 +35,7 @@ def test_registry_matches_ops_surface():
         assert hasattr(_lib.lib(), "lkc_" + n)
     assert _lib.find_kernel("conv1d_snake_f32_cpu") is None
     src = inspect.getsource(ops)
-    used = set(re.findall(r'_run\(\s*"(\w+)"', src))
+    used = set(re.findall(r'(?:_run|_lib\.run)\(\s*"(\w+)"', src))
     assert used == set(names), (used ^ set(names))
 
 

@@ -443,6 +443,28 @@ def test_harmonic_source(cuda, frames):
     assert np.abs(outs - O.harmonic_source(f0s, noises, ws, bs).numpy()).max() <= 2e-6
 
 
+@pytest.mark.parametrize("frames,seed", [(1, 0), (30, 7), (238, 1234), (2080, -5), (1040, (1 << 63) - 1)])
+def test_harmonic_source_rng(cuda, frames, seed):
+    """The in-kernel noise variant (harmonic_source_rng): same Philox4x32-10 counters and Box-Muller pairing as the
+    oracle's restatement of kernels/cpu/kokoro_signal.cpp:66-96, so the output matches harmonic_source fed with the
+    oracle's noise within the op's tolerance (2e-6: the noise enters at amplitude 0.003 / 0.033, and logf / sinf /
+    cosf differ from numpy's in the last ulp); deterministic per seed."""
+    from lokinfer_b200 import ops
+    f0, _, w, b = synth.source_case(frames, frames + 3)
+    df0, dw, db = dev(cuda, f0, w, b)
+    out = ops.harmonic_source_rng_f32_cuda(df0, dw, db, seed).cpu().numpy()
+    ref = O.harmonic_source_rng(f0, w, b, seed).numpy()
+    assert out.shape == ref.shape == (300 * frames,)
+    assert np.abs(out - ref).max() <= 2e-6
+    np.testing.assert_array_equal(out, ops.harmonic_source_rng_f32_cuda(df0, dw, db, seed).cpu().numpy())
+    other = ops.harmonic_source_rng_f32_cuda(df0, dw, db, seed ^ 1).cpu().numpy()
+    assert not np.array_equal(out, other)
+    # and against the explicit-noise op with the same draw
+    noise = O.source_noise_philox(seed, 300 * frames)
+    exp = ops.harmonic_source_f32_cuda(df0, dev(cuda, noise)[0], dw, db).cpu().numpy()
+    assert np.abs(out - exp).max() <= 2e-6
+
+
 @pytest.mark.parametrize("s", [11, 25, 600, 6001, 600 * 300, 624000])
 def test_stft_magphase(cuda, s):
     """tests/kernels/test_kokoro_kernels.py:529-542: magnitude within 1e-5 * max, wrapped phase within 1e-4 where

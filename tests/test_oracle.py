@@ -256,3 +256,27 @@ def test_generator_fused_equals_basic():
         assert a.shape == (300 * 6,)
         assert (a - b).abs().max().item() <= tol
     assert rel_l2(a.numpy(), b.numpy()) < 1e-4
+
+
+def test_philox_known_answers_and_source_noise():
+    """Philox4x32-10 against the known-answer vectors published with the generator (Random123 kat_vectors), and the
+    reference's counter layout / Box-Muller pairing (kernels/cpu/kokoro_signal.cpp:66-96): standard normals,
+    deterministic per (seed, sample), independent of how many samples are drawn."""
+    kat = [((0, 0, 0, 0), (0, 0), (0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8)),
+           ((0xffffffff,) * 4, (0xffffffff, 0xffffffff), (0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd)),
+           ((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0),
+            (0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1))]
+    for ctr, key, want in kat:
+        got = O.philox4x32_10(np.array([ctr], dtype=np.uint32), key)[0]
+        assert [int(v) for v in got] == list(want)
+    nz = O.source_noise_philox(1234, 100000)
+    assert nz.shape == (100000, 9) and nz.dtype == np.float32 and np.isfinite(nz).all()
+    assert abs(float(nz.mean())) < 5e-3 and abs(float(nz.std()) - 1.0) < 5e-3
+    np.testing.assert_array_equal(O.source_noise_philox(1234, 1000), nz[:1000])
+    assert not np.array_equal(O.source_noise_philox(1235, 1000), nz[:1000])
+    # first normal of sample 0, spelled out from its counter block
+    c = O.philox4x32_10(np.array([[0, 0, 0, 0x6C6B6E7A]], dtype=np.uint32), (1234, 0))[0]
+    u1 = (np.float32(c[0]) + np.float32(0.5)) * np.float32(2.3283064e-10)
+    u2 = np.float32(c[1]) * np.float32(2.3283064e-10)
+    z0 = np.sqrt(np.float32(-2) * np.log(u1)) * np.cos(np.float32(6.2831853) * u2)
+    assert abs(float(nz[0, 0]) - float(z0)) < 1e-6
