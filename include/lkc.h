@@ -225,6 +225,19 @@ LKC_API int lkc_harmonic_source_noalloc_f32_cuda(const LkcArgs* a, void* stream)
  * ptrs x[S] | out[n_fft+2, S/hop+1]; ints x(1) out(2) hop n_fft. n_fft even, <= 64; S > n_fft/2. */
 LKC_API int lkc_stft_magphase_f32_cuda(const LkcArgs* a, void* stream);
 
+/* ---- decoder AdainResBlk1d stack (the producer of the generator's input, models/kokoro/model.py:158-221, 704-717):
+ * its convs are the fused family above; these are the three ops it needs besides them. */
+/* conv_transpose1d_dw_f32_cpu (kernels/cpu/kokoro_conv.cpp:97-127, adapter :304-307): depthwise
+ * F.conv_transpose1d(groups = C). ptrs x[C,L] w[C,1,K] b[C] | out[C,(L-1)s-2p+K+op]; ints x(2) w(3) b(1) out(2)
+ * output_padding padding stride. */
+LKC_API int lkc_conv_transpose1d_dw_f32_cuda(const LkcArgs* a, void* stream);
+/* upsample_nearest1d_f32_cpu (kokoro_conv.cpp:231-247, adapter :310-312): F.interpolate(mode = 'nearest'), integer
+ * scale. ptrs x[C,L] | out[C,L*scale]; ints x(2) out(2) scale. */
+LKC_API int lkc_upsample_nearest1d_f32_cuda(const LkcArgs* a, void* stream);
+/* concat_rows_f32_cpu (kernels/cpu/kokoro_misc.cpp:220-226, adapter :330-339): torch.cat(xs, dim = 0) of 2..8
+ * f32[R_i, C]. ptrs x_0 .. x_{n-1} | out[sum R, C]; ints x_i(2) each, out(2). */
+LKC_API int lkc_concat_rows_f32_cuda(const LkcArgs* a, void* stream);
+
 /* ---- time sharding of one utterance across GPUs ------------------------------------------------------------
  * No counterpart in the reference (it has no multi-GPU path). One rank owns a contiguous time range of every
  * activation tensor, with a margin of halo columns on both sides, in memory that its peers have mapped (CUDA IPC).

@@ -284,6 +284,7 @@ const Entry kEntries[] = {
     {"add3_scale_f32_cuda", lkc_add3_scale_f32_cuda},
     {"add_f32_cuda", lkc_add_f32_cuda},
     {"channel_stats_f32_cuda", lkc_channel_stats_f32_cuda},
+    {"concat_rows_f32_cuda", lkc_concat_rows_f32_cuda},
     {"conv1d_affine_f32_cuda", lkc_conv1d_affine_f32_cuda},
     {"conv1d_f32_cuda", lkc_conv1d_f32_cuda},
     {"conv1d_leaky_f32_cuda", lkc_conv1d_leaky_f32_cuda},
@@ -293,6 +294,7 @@ const Entry kEntries[] = {
     {"conv1d_snake_f32_cuda", lkc_conv1d_snake_f32_cuda},
     {"conv1d_snake_res_f32_cuda", lkc_conv1d_snake_res_f32_cuda},
     {"conv1d_tc_pack_f32_cuda", lkc_conv1d_tc_pack_f32_cuda},
+    {"conv_transpose1d_dw_f32_cuda", lkc_conv_transpose1d_dw_f32_cuda},
     {"conv_transpose1d_f32_cuda", lkc_conv_transpose1d_f32_cuda},
     {"conv_transpose1d_poly_f32_cuda", lkc_conv_transpose1d_poly_f32_cuda},
     {"conv_transpose1d_poly_mean3_f32_cuda", lkc_conv_transpose1d_poly_mean3_f32_cuda},
@@ -307,6 +309,7 @@ const Entry kEntries[] = {
     {"scale_f32_cuda", lkc_scale_f32_cuda},
     {"snake_f32_cuda", lkc_snake_f32_cuda},
     {"stft_magphase_f32_cuda", lkc_stft_magphase_f32_cuda},
+    {"upsample_nearest1d_f32_cuda", lkc_upsample_nearest1d_f32_cuda},
 };
 constexpr int kNumEntries = static_cast<int>(sizeof(kEntries) / sizeof(kEntries[0]));
 }  // namespace

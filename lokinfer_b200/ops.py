@@ -373,6 +373,45 @@ def conv_transpose1d_poly_f32_cuda(x, wp, b, res, stride, padding, taps, slope, 
     return out
 
 
+def conv_transpose1d_dw_f32_cuda(x, w, b, stride=1, padding=0, output_padding=0):
+    """Depthwise F.conv_transpose1d(groups=C): x f32[C, L], w f32[C, 1, K], b f32[C]
+    (python/lokinfer/ops/kokoro.py:349-371)."""
+    stride, padding = _int(stride, "stride"), _int(padding, "padding")
+    output_padding = _int(output_padding, "output_padding")
+    _f32(x, rank=2)
+    _f32(w, rank=3)
+    _f32(b, rank=1)
+    check(w.shape[0] == x.shape[0] and w.shape[1] == 1, "w must be [C, 1, K]")
+    check(b.shape[0] == x.shape[0], "bias must be f32[C]")
+    check(stride >= 1 and padding >= 0 and 0 <= output_padding < stride, "invalid stride/padding/output_padding")
+    lo = _convt_out(x.shape[1], w.shape[2], stride, padding, output_padding)
+    check(lo >= 1, "empty conv_transpose output")
+    out = _new(x, (x.shape[0], lo))
+    _run("conv_transpose1d_dw_f32_cuda", [x, w, b], [out], attrs_int=[output_padding, padding, stride])
+    return out
+
+
+def upsample_nearest1d_f32_cuda(x, scale):
+    """F.interpolate(mode='nearest', scale_factor=scale) (integer scale): f32[C, L] -> f32[C, L*scale]
+    (python/lokinfer/ops/kokoro.py:392-402)."""
+    scale = _int(scale, "scale")
+    _f32(x, rank=2)
+    check(scale >= 1, "scale must be >= 1")
+    out = _new(x, (x.shape[0], x.shape[1] * scale))
+    _run("upsample_nearest1d_f32_cuda", [x], [out], attrs_int=[scale])
+    return out
+
+
+def concat_rows_f32_cuda(*xs):
+    """torch.cat(xs, dim=0) for 2..8 f32[R_i, C] (python/lokinfer/ops/kokoro.py:152-161)."""
+    check(2 <= len(xs) <= 8, "concat takes 2..8 operands")
+    _f32(*xs, rank=2)
+    check(all(x.shape[1] == xs[0].shape[1] for x in xs), "column counts differ")
+    out = _new(xs[0], (sum(int(x.shape[0]) for x in xs), xs[0].shape[1]))
+    _run("concat_rows_f32_cuda", list(xs), [out])
+    return out
+
+
 def adain1d_f32_cuda(x, gb, eps=1e-5):
     """(1 + gb[:C, None]) * instance_norm(x) + gb[C:, None] (biased var) over x f32[C, L]."""
     _f32(x, rank=2)

@@ -135,3 +135,46 @@ def source_case(n: int, seed: int):
     w = (r.standard_normal(9) * 0.5).astype(np.float32)
     b = (r.standard_normal(1) * 0.1).astype(np.float32)
     return f0, noise, w, b
+
+
+DECODER_BLOCKS = (("decoder.encode", 514, 1024, False), ("decoder.decode.0", 1090, 1024, False),
+                  ("decoder.decode.1", 1090, 1024, False), ("decoder.decode.2", 1090, 1024, False),
+                  ("decoder.decode.3", 1090, 512, True))
+
+
+def decoder_weights(seed: int = 0) -> dict[str, np.ndarray]:
+    """Random-init weights of the decoder in front of the generator (names and shapes of models/kokoro/model.py:
+    158-221, 704-717): five AdainResBlk1d (norm1.fc / norm2.fc Linear(128 -> 2C), conv1 / conv2 k 3, conv1x1 where the
+    channel count changes, the depthwise pool of the upsampling block), asr_res (512 -> 64, k 1), F0_conv / N_conv
+    (1 -> 1, k 3, stride 2). Conv weights ~ N(0, 1 / (Ci K)), biases ~ N(0, 0.01), fc weights ~ N(0, 1 / 128)."""
+    r = np.random.default_rng(1000 + seed)
+    sd = {}
+
+    def conv(name, co, ci, k, bias=True):
+        sd[name + ".weight"] = (r.standard_normal((co, ci, k)) / np.sqrt(ci * k)).astype(np.float32)
+        if bias:
+            sd[name + ".bias"] = (r.standard_normal(co) * 0.1).astype(np.float32)
+
+    for name, cin, cout, up in DECODER_BLOCKS:
+        for fc, c in ((".norm1.fc", cin), (".norm2.fc", cout)):
+            sd[name + fc + ".weight"] = (r.standard_normal((2 * c, 128)) / np.sqrt(128)).astype(np.float32)
+            sd[name + fc + ".bias"] = (r.standard_normal(2 * c) * 0.1).astype(np.float32)
+        conv(name + ".conv1", cout, cin, 3)
+        conv(name + ".conv2", cout, cout, 3)
+        if cin != cout:
+            conv(name + ".conv1x1", cout, cin, 1, bias=False)
+        if up:
+            sd[name + ".pool.weight"] = (r.standard_normal((cin, 1, 3)) / np.sqrt(3)).astype(np.float32)
+            sd[name + ".pool.bias"] = (r.standard_normal(cin) * 0.1).astype(np.float32)
+    conv("decoder.asr_res.0", 64, 512, 1)
+    conv("decoder.F0_conv", 1, 1, 3)
+    conv("decoder.N_conv", 1, 1, 3)
+    return sd
+
+
+def decoder_inputs(frames: int, seed: int = 1) -> dict[str, np.ndarray]:
+    """asr f32[512, F] ~ N(0, 1), the F0 curve f32[2F] (Hz, voiced / unvoiced stretches), the energy curve f32[2F]
+    ~ U(0, 4), style f32[128] ~ N(0, 1)."""
+    r = np.random.default_rng(2000 + seed)
+    return {"asr": r.standard_normal((512, frames)).astype(np.float32), "f0": f0_curve(2 * frames, seed),
+            "n": r.uniform(0.0, 4.0, 2 * frames).astype(np.float32), "s": r.standard_normal(128).astype(np.float32)}

@@ -438,6 +438,83 @@ def adain_resblock1_fused(x, gbs, sd, prefix, k, x_stats=None):
     return x, st
 
 
+SQRT1_2 = 0.7071067811865476
+
+
+def conv_transpose1d_dw(x, w, b, stride=1, padding=0, output_padding=0):
+    """Depthwise F.conv_transpose1d (python/lokinfer/ops/kokoro.py:367-371)."""
+    return F.conv_transpose1d(x[None], w, b, stride=stride, padding=padding, output_padding=output_padding,
+                              groups=x.shape[0])[0]
+
+
+def upsample_nearest1d(x, scale):
+    """F.interpolate(mode='nearest') with an integer scale (python/lokinfer/ops/kokoro.py:399-402)."""
+    return x.repeat_interleave(scale, dim=1)
+
+
+def adain_resblk(x, gb1, gb2, sd, prefix, cin, cout, upsample):
+    """AdainResBlk1d through the basic ops (models/kokoro/model.py:158-174)."""
+    r = leaky_relu(adain1d(x, gb1), 0.2)
+    if upsample:
+        r = conv_transpose1d_dw(r, sd[prefix + ".pool.weight"], sd[prefix + ".pool.bias"], stride=2, padding=1,
+                                output_padding=1)
+    r = conv1d(r, sd[prefix + ".conv1.weight"], sd[prefix + ".conv1.bias"], padding=1)
+    r = leaky_relu(adain1d(r, gb2), 0.2)
+    r = conv1d(r, sd[prefix + ".conv2.weight"], sd[prefix + ".conv2.bias"], padding=1)
+    sc = upsample_nearest1d(x, 2) if upsample else x
+    if cin != cout:
+        sc = conv1d(sc, sd[prefix + ".conv1x1.weight"])
+    return (r + sc) * SQRT1_2
+
+
+def adain_resblk_fused(x, gb1, gb2, sd, prefix, cin, cout, upsample):
+    """The same block through the fused conv contracts (models/kokoro/model.py:205-221): stats -> adain_affine ->
+    conv1d_leaky -> adain_affine -> conv1d_leaky(+shortcut, x 1/sqrt 2); the upsample block keeps the basic AdaIN /
+    leaky / depthwise-convT front and an identity affine on conv1."""
+    dt = x.dtype
+    af = adain_affine(channel_stats(x), gb1, x.shape[1])
+    if upsample:
+        r = leaky_relu(adain1d(x, gb1), 0.2)
+        r = conv_transpose1d_dw(r, sd[prefix + ".pool.weight"], sd[prefix + ".pool.bias"], stride=2, padding=1,
+                                output_padding=1)
+        ident = torch.stack([torch.zeros(cin), torch.ones(cin), torch.zeros(cin)]).to(dt)
+        h, st = conv1d_fused(r, sd[prefix + ".conv1.weight"], sd[prefix + ".conv1.bias"], ident, "none", padding=1)
+    else:
+        h, st = conv1d_fused(x, sd[prefix + ".conv1.weight"], sd[prefix + ".conv1.bias"], af, "leaky", slope=0.2,
+                             padding=1)
+    af = adain_affine(st, gb2, h.shape[1])
+    sc = upsample_nearest1d(x, 2) if upsample else x
+    if cin != cout:
+        sc = conv1d(sc, sd[prefix + ".conv1x1.weight"])
+    out, _ = conv1d_fused(h, sd[prefix + ".conv2.weight"], sd[prefix + ".conv2.bias"], af, "leaky", slope=0.2,
+                          residual=sc, out_scale=SQRT1_2, padding=1)
+    return out
+
+
+DECODER_BLOCKS = (("decoder.encode", 514, 1024, False), ("decoder.decode.0", 1090, 1024, False),
+                  ("decoder.decode.1", 1090, 1024, False), ("decoder.decode.2", 1090, 1024, False),
+                  ("decoder.decode.3", 1090, 512, True))
+
+
+def decoder(sd, asr, f0, n_curve, s, fused=True):
+    """The decoder in front of the generator (models/kokoro/model.py:704-717): asr [512, F] aligned text features,
+    f0 / n_curve [2F] pitch and energy curves, s [128] style -> x [512, 2F]."""
+    dt = asr.dtype
+    sd = {k: (v if torch.is_tensor(v) else T(v)).to(dt) for k, v in sd.items()}
+    gbs = style_bank(sd, s)
+    f0d = conv1d(f0.reshape(1, -1), sd["decoder.F0_conv.weight"], sd["decoder.F0_conv.bias"], stride=2, padding=1)
+    nd = conv1d(n_curve.reshape(1, -1), sd["decoder.N_conv.weight"], sd["decoder.N_conv.bias"], stride=2, padding=1)
+    blk = adain_resblk_fused if fused else adain_resblk
+    x = torch.cat([asr, f0d, nd], 0)
+    name, cin, cout, up = DECODER_BLOCKS[0]
+    x = blk(x, gbs[name + ".norm1.fc"], gbs[name + ".norm2.fc"], sd, name, cin, cout, up)
+    asr_res = conv1d(asr, sd["decoder.asr_res.0.weight"], sd["decoder.asr_res.0.bias"])
+    for name, cin, cout, up in DECODER_BLOCKS[1:]:
+        x = torch.cat([x, asr_res, f0d, nd], 0)
+        x = blk(x, gbs[name + ".norm1.fc"], gbs[name + ".norm2.fc"], sd, name, cin, cout, up)
+    return x
+
+
 def generator(sd, x, har, s, fused=True, stages=False):
     """The generator part of the reference graph (models/kokoro/model.py:735-781): x [512, T] decoder features,
     har [22, 60 T + 1] harmonic-source STFT, s [128] style -> audio [300 T]. fused=False is the basic-kernel

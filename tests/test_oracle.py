@@ -280,3 +280,15 @@ def test_philox_known_answers_and_source_noise():
     u2 = np.float32(c[1]) * np.float32(2.3283064e-10)
     z0 = np.sqrt(np.float32(-2) * np.log(u1)) * np.cos(np.float32(6.2831853) * u2)
     assert abs(float(nz[0, 0]) - float(z0)) < 1e-6
+
+
+def test_decoder_fused_equals_basic():
+    """The decoder stack through the fused conv contracts (models/kokoro/model.py:205-221) equals the basic-op stack
+    (:158-174): the restated graph wiring is consistent (float64 so that only the wiring is tested)."""
+    from lokinfer_b200 import synth
+    sd = synth.decoder_weights(0)
+    inp = synth.decoder_inputs(12, 1)
+    a = [O.T(inp[k], torch.float64) for k in ("asr", "f0", "n", "s")]
+    fused, basic = O.decoder(sd, *a, fused=True), O.decoder(sd, *a, fused=False)
+    assert tuple(fused.shape) == (512, 24)
+    assert (fused - basic).abs().max().item() <= 1e-9 * basic.abs().max().item()
