@@ -509,7 +509,8 @@ def run_ours(args, rank: int, local_rank: int, world: int):
             "config": {"workload": f"kokoro_generator_T{t}", "audio_seconds_per_utterance": audio_s,
                        "utterances_per_step": world, "L0": sh["L0"], "L1": sh["L1"], "samples": sh["S"],
                        "sharding": "one utterance per GPU, no communication" if world > 1 else "single GPU",
-                       "l2": "working set per step (~2 GB of activations) is larger than the 126 MB L2",
+                       "l2": "working set per step is larger than the 126 MB L2",
+                       "arena_bytes": bufs.get("arena_bytes"), "unplanned_bytes": bufs.get("unplanned_bytes"),
                        "conv_gflop_per_utterance": conv_flops_per_t() * t / 1e9},
             "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / args.steps},

@@ -147,7 +147,7 @@ class Generator:
         noise = [None, None]
         if par:
             for i in (0, 1):
-                side[i].wait_stream(cur)
+                ops.join(side[i], cur)
         for i, (_, _, k_noise) in enumerate(((20, 10, 7), (12, 6, 11))):
             if not fused:
                 break
@@ -162,7 +162,7 @@ class Generator:
         for i, (k_up, u, k_noise) in enumerate(((20, 10, 7), (12, 6, 11))):
             if fused:
                 if par:
-                    cur.wait_stream(side[i])
+                    ops.join(cur, side[i])
                 if i == 0:
                     xin = x
                 else:
@@ -177,15 +177,15 @@ class Generator:
                 keep += [x, xst, *(rb or [])]
                 new_rb = [None, None, None]
                 if par:
-                    side[2].wait_stream(cur)
-                    side[3].wait_stream(cur)
+                    ops.join(side[2], cur)
+                    ops.join(side[3], cur)
                 # the k = 11 block is the longest: it stays on the current stream
                 for j, stream in ((2, None), (1, side[2] if par else None), (0, side[3] if par else None)):
                     with on(stream):
                         new_rb[j] = self.adain_resblock1_fused(x, gb, f"resblocks.{3 * i + j}", RES_KERNELS[j], xst)[0]
                 if par:
-                    cur.wait_stream(side[2])
-                    cur.wait_stream(side[3])
+                    ops.join(cur, side[2])
+                    ops.join(cur, side[3])
                 rb = new_rb
             else:
                 if i == 0:
@@ -228,11 +228,17 @@ class Generator:
 
     # ------------------------------------------------------------------ CUDA graph replay
 
-    def capture(self, t: int):
+    def capture(self, t: int, planned: bool = True):
         """Records forward(fused=True) for input length t into a CUDA graph (once per t). Returns a dict with the
-        static buffers `x`, `har`, `s`, `audio` and the `graph`; fill the inputs, then graph.replay()."""
+        static buffers `x`, `har`, `s`, `audio` and the `graph`; fill the inputs, then graph.replay().
+
+        planned=True (default): the forward's intermediates live in a planned arena (arena.py): one traced forward
+        gives every tensor's life, the plan overlays tensors that are never alive together (judged by the fork / join
+        structure of the streams, not by program order), and the captured forward takes views of ONE device buffer
+        sized by the plan (`arena_bytes`; `unplanned_bytes` is what keeping every intermediate would take)."""
         if t in self._graphs:
             return self._graphs[t]
+        from .arena import PlannedArena, Tracer
         sh = shapes(t)
         dev = self.device
         pitch = -(-t // ops.ROW_ALIGN) * ops.ROW_ALIGN  # rows of x start on 16-byte boundaries for any t
@@ -240,15 +246,33 @@ class Generator:
                 "s": torch.zeros(128, device=dev)}
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
+        arena = None
         with torch.cuda.stream(side):
             for _ in range(2):  # warm-up outside capture: lazy module loading, function attributes
-                self.forward(bufs["x"], bufs["har"], bufs["s"])
+                ref = self.forward(bufs["x"], bufs["har"], bufs["s"])
+            if planned:
+                with ops.tracing(Tracer()) as tr:
+                    tr.pin(self.forward(bufs["x"], bufs["har"], bufs["s"]))
+                arena = PlannedArena(tr, dev)
+                del tr
+                arena.begin()
+                with ops.use_allocator(arena.allocator):
+                    again = self.forward(bufs["x"], bufs["har"], bufs["s"])
+                torch.cuda.synchronize(dev)
+                ops.check(torch.equal(again, ref), "the planned arena changed the result of the forward")
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            bufs["audio"] = self.forward(bufs["x"], bufs["har"], bufs["s"])
+            if arena is not None:
+                arena.begin()
+                with ops.use_allocator(arena.allocator):
+                    bufs["audio"] = self.forward(bufs["x"], bufs["har"], bufs["s"])
+            else:
+                bufs["audio"] = self.forward(bufs["x"], bufs["har"], bufs["s"])
         bufs["graph"] = g
+        if arena is not None:
+            bufs["arena"], bufs["arena_bytes"], bufs["unplanned_bytes"] = arena, arena.nbytes, arena.unplanned_bytes
         self._graphs[t] = bufs
         return bufs
 

@@ -121,6 +121,8 @@ def _run(name, operands, outs, attrs_int=(), attrs_float=(), state=None, window=
         ints += [int(ts[i].stride(0)) for i in pitched]
     if window is not None:
         ints += [int(v) for v in window]
+    if _tracer is not None:
+        _tracer.on_run(ts, _stream())
     with torch.cuda.device(ts[0].device):
         prof = _profile
         if prof is None:
@@ -149,6 +151,32 @@ def _torch_alloc(shape, device):
 
 allocator = _torch_alloc  # (shape, device) -> contiguous f32 tensor; replaced by a planned arena (see arena.py)
 _pad_rows = False
+_tracer = None  # arena.Tracer while a forward is being traced for the memory plan
+
+
+def _alloc(shape, device):
+    t = allocator(tuple(int(d) for d in shape), device)
+    if _tracer is not None:
+        _tracer.on_alloc(t, _stream())
+    return t
+
+
+@contextlib.contextmanager
+def tracing(tracer):
+    """Records every result allocation, kernel call and stream join inside the block into `tracer`."""
+    global _tracer
+    prev, _tracer = _tracer, tracer
+    try:
+        yield tracer
+    finally:
+        _tracer = prev
+
+
+def join(waiter, waited):
+    """waiter.wait_stream(waited), visible to the tracer (the memory plan needs the fork / join structure)."""
+    waiter.wait_stream(waited)
+    if _tracer is not None:
+        _tracer.on_join(waiter.cuda_stream, waited.cuda_stream)
 
 
 @contextlib.contextmanager
@@ -177,8 +205,8 @@ def empty_rows(c, l, device):
     """f32[c, l] with padded rows when padded_rows() is active (else contiguous)."""
     if _pad_rows:
         pitch = ceildiv(int(l), ROW_ALIGN) * ROW_ALIGN
-        return allocator((int(c), pitch), device)[:, :int(l)]
-    return allocator((int(c), int(l)), device)
+        return _alloc((int(c), pitch), device)[:, :int(l)]
+    return _alloc((int(c), int(l)), device)
 
 
 def _new(like, shape, rows=False):
@@ -189,7 +217,7 @@ def _new(like, shape, rows=False):
         return torch.empty(tuple(shape), dtype=torch.float32, device="meta")
     if rows:
         return empty_rows(shape[0], shape[1], like.device)
-    return allocator(tuple(int(d) for d in shape), like.device)
+    return _alloc(shape, like.device)
 
 
 def _full_rows(x):
@@ -250,7 +278,7 @@ def add3_scale_f32_cuda(a, b, c, scale):
     if a.is_cuda and not (a.is_contiguous() and b.is_contiguous() and c.is_contiguous()):
         check(a.stride() == b.stride() == c.stride(), "padded operands must share one row pitch")
         fa, fb, fc = _full_rows(a), _full_rows(b), _full_rows(c)
-        out = allocator(tuple(fa.shape), a.device)
+        out = _alloc(tuple(fa.shape), a.device)
         _run("add3_scale_f32_cuda", [fa, fb, fc], [out], attrs_float=[_float(scale, "scale")])
         return out[:, :a.shape[1]]
     out = _new(a, a.shape)

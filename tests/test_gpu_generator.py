@@ -152,6 +152,28 @@ def test_graph_replay_matches_eager(cuda, gen):
     np.testing.assert_array_equal(a1, a2)
 
 
+def test_planned_arena(cuda):
+    """The captured forward lives in a planned arena: identical samples to the eager forward (every intermediate its
+    own allocation) and to a capture without the plan, in well under the memory of keeping every intermediate."""
+    from lokinfer_b200 import Generator, ops
+    t = 416
+    inp = synth.generator_inputs(t, 9)
+    g1, g2 = Generator(synth.generator_weights(0), cuda), Generator(synth.generator_weights(0), cuda)
+    d = [ops.to_cuda(inp[k], cuda) for k in ("x", "har", "s")]
+    eager = g1.forward(*d)
+    b1, b2 = g1.capture(t), g2.capture(t, planned=False)
+    assert "arena" in b1 and "arena" not in b2
+    assert b1["arena_bytes"] <= 0.55 * b1["unplanned_bytes"]
+    for b in (b1, b2):
+        for k, v in zip(("x", "har", "s"), d):
+            b[k].copy_(v)
+        for _ in range(3):
+            b["graph"].replay()
+    torch.cuda.synchronize()
+    assert torch.equal(b1["audio"], eager) and torch.equal(b2["audio"], eager)
+    assert ops.conv_tc_status() == 0
+
+
 def test_full_size_properties(cuda, gen):
     """The 26 s case (T = 2080: L0 = 20800, L1 = 124801, 624000 samples), too large for the CPU oracle in a test:
     exact shapes, run-to-run determinism, agreement of the fused graph with the basic-kernel graph (two independent
