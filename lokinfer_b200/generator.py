@@ -226,6 +226,22 @@ class Generator:
             self._streams = [torch.cuda.Stream(device=self.device) for _ in range(4)]
         return self._streams
 
+    def _warm_stream(self):
+        """The stream capture() runs its warm-up and traced forwards on: one per generator, and never the same CUDA
+        stream as a side stream. torch hands streams out of a pool of 32 round-robin, so a stream made later can BE an
+        earlier one; a traced forward whose main stream coincided with a side stream would look more serial than the
+        captured one is, and the memory plan made from it would overlay tensors of branches that run concurrently."""
+        if getattr(self, "_warm", None) is None:
+            taken = {s.cuda_stream for s in self._side_streams()}
+            for _ in range(64):
+                s = torch.cuda.Stream(device=self.device)
+                if s.cuda_stream not in taken:
+                    self._warm = s
+                    break
+            else:
+                raise RuntimeError("no CUDA stream distinct from the side streams")
+        return self._warm
+
     # ------------------------------------------------------------------ CUDA graph replay
 
     def capture(self, t: int, planned: bool = True):
@@ -244,7 +260,7 @@ class Generator:
         pitch = -(-t // ops.ROW_ALIGN) * ops.ROW_ALIGN  # rows of x start on 16-byte boundaries for any t
         bufs = {"x": torch.zeros(512, pitch, device=dev)[:, :t], "har": torch.zeros(22, sh["L1"], device=dev),
                 "s": torch.zeros(128, device=dev)}
-        side = torch.cuda.Stream(device=dev)
+        side = self._warm_stream()
         side.wait_stream(torch.cuda.current_stream(dev))
         arena = None
         with torch.cuda.stream(side):

@@ -174,6 +174,29 @@ def test_planned_arena(cuda):
     assert ops.conv_tc_status() == 0
 
 
+def test_many_captures_keep_their_plans_valid(cuda):
+    """One generator captures more lengths than torch's stream pool has streams (32): a stream made for a later
+    capture can be the same CUDA stream as one of the generator's side streams. The memory plan must still be made
+    for the concurrency the captured graph really has: every replay equals the eager forward."""
+    from lokinfer_b200 import Generator, ops
+    g = Generator(synth.generator_weights(0), cuda)
+    lengths = list(range(40, 40 + 36))
+    worst = 0.0
+    for i, t in enumerate(lengths):
+        inp = synth.generator_inputs(t, 500 + i)
+        d = [ops.to_cuda(inp[k], cuda) for k in ("x", "har", "s")]
+        eager = g.forward(*d)
+        b = g.capture(t)
+        for k, v in zip(("x", "har", "s"), d):
+            b[k].copy_(v)
+        for _ in range(2):
+            b["graph"].replay()
+        torch.cuda.synchronize()
+        assert torch.equal(b["audio"], eager), (i, t)
+        worst = max(worst, eager.abs().max().item())
+    assert ops.conv_tc_status() == 0 and worst > 0
+
+
 def test_full_size_properties(cuda, gen):
     """The 26 s case (T = 2080: L0 = 20800, L1 = 124801, 624000 samples), too large for the CPU oracle in a test:
     exact shapes, run-to-run determinism, agreement of the fused graph with the basic-kernel graph (two independent
