@@ -47,6 +47,7 @@ TRAFFIC = {"bytes": 130409984 + 26507776, "algorithmic": 3 * 4 * 128 * 124801,
            "kernel": "convTcKernel, conv1d_snake_res, Ci = Co = 128, L = 124801, K = 11, dilation 5 (one launch)",
            "source": "profiles/conv_tc_c128_k11_L124801.md"}
 
+BATCH_STREAMS = 3  # utterance graphs of one GPU are replayed round-robin on this many streams (config 3)
 METRIC = "kokoro_generator_audio_seconds_per_second"
 UNIT = "audio-s/s"
 SAMPLE_RATE = 24000.0
@@ -272,10 +273,20 @@ def measure_batch64(gen, dev, rank: int, world: int, steps: int, warmup: int) ->
             bufs[k].copy_(torch.from_numpy(inp[k]))
         graphs.append(bufs["graph"])
     torch.cuda.synchronize()
+    # Utterances are independent (own static buffers, own arena): their graphs are replayed round-robin on a few
+    # streams, so that the convs of a short utterance (a 1.5 s utterance has 10-30 tiles per conv for 148 SMs) share
+    # the GPU with those of another one instead of leaving most SMs idle.
+    main = torch.cuda.current_stream(dev)
+    lanes = [torch.cuda.Stream(device=dev) for _ in range(BATCH_STREAMS)]
 
     def step():
-        for g in graphs:
-            g.replay()
+        for ln in lanes:
+            ln.wait_stream(main)
+        for i, g in enumerate(graphs):
+            with torch.cuda.stream(lanes[i % BATCH_STREAMS]):
+                g.replay()
+        for ln in lanes:
+            main.wait_stream(ln)
 
     for _ in range(max(warmup, 3)):
         step()
@@ -300,7 +311,7 @@ def measure_batch64(gen, dev, rank: int, world: int, steps: int, warmup: int) ->
             "unit": UNIT, "ms_per_step": float(ms.item()) / steps, "scaling": "strong", "utterances": 64,
             "T_range": [120, 800], "audio_seconds_per_step": total_audio,
             "sharding": "by utterance, longest first, no communication",
-            "rank_loads_T": sharding.loads(lengths, plan)}
+            "streams_per_gpu": BATCH_STREAMS, "rank_loads_T": sharding.loads(lengths, plan)}
 
 
 def measure_time_sharded(gen, dev, rank: int, world: int, t: int, steps: int, single_ms: float) -> dict | None:
