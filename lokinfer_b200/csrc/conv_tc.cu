@@ -12,7 +12,7 @@
 // The tensor core adds into its f32 accumulator with truncation, so a long accumulation chain drifts towards zero by
 // about 1.5e-8 of the result per MMA (measured: the error grows linearly with the chain length). Two accumulators
 // keep that out of the result: Dhi (TMEM columns 0-255) takes only the hi*hi products of a short run of MMAs (a drain
-// group: as many whole 16-channel chunks as fit in 12 chained MMAs, at least one chunk), is then drained by the
+// group: as many whole 16-channel chunks as fit in 24 chained MMAs, at least one chunk), is then drained by the
 // epilogue warps into f32 registers (round-to-nearest adds on the CUDA cores) and restarted; Dlo (columns 256-511)
 // takes every lo product of the tile, where the same drift is scaled by 2^-11.
 //
@@ -24,19 +24,24 @@
 // take 4-byte cp.async loads and transposed 4-byte stores instead; the arithmetic is the same on both routes.
 // No copy uses cluster multicast, and every tensor map covers memory of this GPU only.
 //
-// One persistent CTA per SM, 20 warps in 5 warpgroups, warp-specialised (registers rebalanced with setmaxnreg):
+// One persistent CTA per SM, 20 warps in 5 warpgroups, warp-specialised (registers rebalanced with setmaxnreg). A warp
+// is issued by scheduler (warp id % 4) of the SM. The MMA issuer's instructions between two MMAs are what keeps the
+// tensor pipe fed, so its scheduler (1) hosts no activation producer, only the other two light control warps and the
+// two epilogue warps that TMEM's lane rule puts there (measured: the issuer's own time outside waits fell by 15-19 %
+// against a layout with two producers on its scheduler):
 //   warps 0-7   accumulate + epilogue: 128 running sums per thread, started from the bias; the residual is added one
 //               32-column batch at a time (fetched into the warp's tile behind a Dhi drain); per drain group += Dhi
 //               (tcgen05.ld); per tile += Dlo, oscale, chunk statistics and the store
-//   warps 8-15  activation producers: affine -> Snake / leaky -> hi / lo split of the current chunk's raw window into
+//   warps 8, 10, 11, 12, 14, 15, 16, 18
+//               activation producers: affine -> Snake / leaky -> hi / lo split of the current chunk's raw window into
 //               shared memory in the K-major no-swizzle UMMA layout [16-byte K chunk][time row][4 f32 or 8 f16
 //               channels]: a tap shift of kk*d time steps is a +16*kk*d byte offset of the descriptor start address,
 //               so one staged window serves all taps (on the unaligned route they also issue the cp.async of the next
 //               chunk's raw window)
-//   warp 16     weight producer: one cp.async.bulk per tap group (up to 4 taps; hi | lo of [128 co x 16 ci] per tap,
+//   warp 9      weight producer: one cp.async.bulk per tap group (up to 4 taps; hi | lo of [128 co x 16 ci] per tap,
 //               pre-packed in the UMMA layout, L2-resident) into a ring of shared-memory slots
-//   warp 17     MMA issuer (one lane): per tap group one wait, the group's MMAs back to back, one release
-//   warp 18     raw-window loader of the aligned route (one lane): two tiled TMA loads per chunk, one chunk ahead
+//   warp 13     MMA issuer (one lane): per tap group one wait, the group's MMAs back to back, one release
+//   warp 17     raw-window loader of the aligned route (one lane): two tiled TMA loads per chunk, one chunk ahead
 //   warp 19     idle (completes the fifth warpgroup)
 // All hand-offs are mbarriers. Every wait is bounded: on a timeout the kernel records a status word, drains its
 // copies in flight and returns (TMEM is freed on every path).
@@ -62,14 +67,15 @@ constexpr int KC = 16;          // input channels per staged chunk (one weight s
 constexpr int MAX_NB = 4;       // most activation (hi / lo) buffers
 constexpr int NRAW = 2;         // raw-input staging buffers, filled one chunk ahead
 constexpr int EPI_WARPS = 8, PRO_WARPS = 8;
-constexpr int W_WARP = EPI_WARPS + PRO_WARPS, MMA_WARP = W_WARP + 1, RAW_WARP = W_WARP + 2;
+constexpr int W_WARP = 9, MMA_WARP = 13, RAW_WARP = 17, IDLE_WARP = 19;  // scheduler 1 = warp id % 4 == 1
 constexpr int NWARPS = EPI_WARPS + PRO_WARPS + 4;
 constexpr int NTHREADS = NWARPS * 32;  // 640
-constexpr int LAUNCH_REGS = 96, EPI_REGS = 160, PRO_REGS = 56, CTL_REGS = 40;
+// warpgroups 2-4 mix producers and control warps, and setmaxnreg takes one value per warpgroup
+constexpr int LAUNCH_REGS = 96, EPI_REGS = 152, PRO_REGS = 56, CTL_REGS = PRO_REGS;
 static_assert(NTHREADS * LAUNCH_REGS <= 65536, "launch register budget");
 // setmaxnreg moves registers inside the CTA's own launch allocation (NTHREADS * LAUNCH_REGS); an increase beyond what
 // the decreases release would block forever.
-static_assert(EPI_WARPS * 32 * EPI_REGS + PRO_WARPS * 32 * PRO_REGS + 4 * 32 * CTL_REGS <= NTHREADS * LAUNCH_REGS,
+static_assert(EPI_WARPS * 32 * EPI_REGS + (NWARPS - EPI_WARPS) * 32 * PRO_REGS <= NTHREADS * LAUNCH_REGS,
               "register pool");
 // Operand formats (template parameter F16 of the kernel):
 //   tf32 split (F16 = false): hi = tf32(v), lo = v - hi, both stored as f32; per tap and 16 channels 6 MMAs of
@@ -96,7 +102,7 @@ static_assert(BOX_BYTES <= STAGE_FLOATS * 4, "a swizzled box fits in a warp's ti
 constexpr int MAX_HALO = 50;     // (K - 1) * dilation of the widest Kokoro conv (K 11, dilation 5)
 constexpr int MAX_W_STAGES = 4, MIN_W_STAGES = 2, PREF_W_STAGES = 2;  // weight ring slots
 constexpr int TAP_GROUP = 4;  // most taps per weight slot: one bulk copy, one wait, MMAs back to back, one release
-constexpr int MAX_CHAIN = 12;  // chained hi MMAs between two drains (more only when one chunk alone has more)
+constexpr int MAX_CHAIN = 24;  // most chained hi MMAs between two drains of Dhi
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr uint32_t SLEEP_EPI_NS = 256, SLEEP_PRO_NS = 128, SLEEP_W_NS = 64, SLEEP_MMA_NS = 32;
 constexpr uint64_t WAIT_LIMIT_NS = 200ull * 1000 * 1000;  // 0.2 s: a healthy wait is tens of microseconds
@@ -570,13 +576,15 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
         tcFenceAfter();
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          float v[32];
-          tmemLoad32(tmemHi + laneBase + g * 128 + b * 32, v);
+        for (int b = 0; b < 8; ++b) {
+          uint32_t v[16];
+          tmemLoad16Async(tmemHi + laneBase + g * 128 + b * 16, v);
+          tmemWaitLoads();
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {  // packed f32x2 adds: half the instructions of the accumulate loop
-            const float2 sum = __fadd2_rn(make_float2(S[b * 32 + j], S[b * 32 + j + 1]), make_float2(v[j], v[j + 1]));
-            S[b * 32 + j] = sum.x, S[b * 32 + j + 1] = sum.y;
+          for (int j = 0; j < 16; j += 2) {  // packed f32x2 adds: half the instructions of the accumulate loop
+            const float2 sum = __fadd2_rn(make_float2(S[b * 16 + j], S[b * 16 + j + 1]),
+                                          make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])));
+            S[b * 16 + j] = sum.x, S[b * 16 + j + 1] = sum.y;
           }
         }
         tcFenceBefore();
@@ -771,10 +779,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     if (tmaOut && lane == 0) bulkWaitAll();
     if (kProf && warp == 0)
       profAdd(5, wHi), profAdd(6, wLo), profAdd(7, cPre), profAdd(8, cFin), profAdd(9, clock64() - tStart);
-  } else if (warp < EPI_WARPS + PRO_WARPS) {
+  } else if ((warp & 3) != 1 && warp != IDLE_WARP) {
     // ------------------------------------------------------------------ activation producers
     regDec<PRO_REGS>();
-    const int pw = warp - EPI_WARPS;
+    const int pw = (warp - EPI_WARPS) - ((warp - EPI_WARPS + 2) >> 2);  // 8, 10, 11, 12, 14, 15, 16, 18 -> 0..7
     const int cg = pw & 3, hf = pw >> 2;  // channel group of 4 inside the 16-channel chunk; row half
     const int rowsHalf = (rows + 1) >> 1;
     const int r0 = hf * rowsHalf, r1 = (r0 + rowsHalf < rows) ? r0 + rowsHalf : rows;
@@ -782,7 +790,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const bool tmaIn = a.tmaIn != 0;
     const int runSkip = (KC - 1) * half;  // a raw window index i >= half sits in the second run: + runSkip floats
     // per-channel parameters, once: sPar = [mean | a | b | inv] with a = scale, b = beta (x alpha for Snake), inv = 1/alpha
-    for (int c = threadIdx.x - EPI_WARPS * 32; c < a.ci; c += PRO_WARPS * 32) {
+    for (int c = pw * 32 + lane; c < a.ci; c += PRO_WARPS * 32) {
       const float al = ACT == 1 ? a.alpha[c] : 1.f;
       sPar[c] = a.affine ? a.affine[c] : 0.f;
       sPar[a.ci + c] = (a.affine ? a.affine[a.ci + c] : 1.f) * al;
@@ -1251,10 +1259,10 @@ static size_t convTcSmemBytes(int64_t ci, int rows, int k, bool f16, int* wStage
   return smemLayout(int(ci), rows, half, nb, bestWs, bestG, actRow, tap).total;
 }
 
-// The hi chain between two drains holds at most MAX_CHAIN MMAs, or one chunk's MMAs when a chunk alone has more
-// (K > 12 with f16 halves, K > 6 with tf32 halves); chunks with more than 2 MAX_CHAIN hi MMAs go to the CUDA-core
-// kernel, so the chain (and the truncation drift it accumulates, about 1.5e-8 per MMA) stays bounded.
-static bool chainOk(int64_t k, bool f16) { return k * (f16 ? 1 : 2) <= 2 * MAX_CHAIN; }
+// The hi chain between two drains holds at most MAX_CHAIN MMAs: whole chunks while they fit, and a chunk that alone
+// has more (K > 24 with f16 halves, K > 12 with tf32 halves) goes to the CUDA-core kernel, so the chain (and the
+// truncation drift it accumulates, about 1.5e-8 of the result per MMA: 3.7e-7 at 24) stays bounded.
+static bool chainOk(int64_t k, bool f16) { return k * (f16 ? 1 : 2) <= MAX_CHAIN; }
 
 bool convTcEligible(const ConvFusedParams& p, bool f16) {
   if (!(p.state != nullptr && p.x2 == nullptr && p.ci % KC == 0 && p.co >= 1 && p.ci >= KC && p.k >= 1 &&
@@ -1419,8 +1427,8 @@ static int finishArgs(TcArgs& a, TcMaps& m, bool f16, bool boxesOk, int* grid, s
   if (int rc = deviceInfo(&d)) return rc;
   a.status = d->status;
   a.prof = (kProf && gProfileOn) ? d->prof : nullptr;
-  // Dhi is drained into the f32 running sums after at most MAX_CHAIN chained MMAs (one chunk's MMAs when a chunk
-  // alone has more); with a residual, at least four drains per tile so that each hides one residual batch.
+  // Dhi is drained into the f32 running sums after as many whole chunks as fit in MAX_CHAIN chained MMAs; with a
+  // residual, at least four drains per tile so that each hides one residual batch.
   const int perChunk = a.k * (f16 ? 1 : 2), nChunks = a.ci / KC;
   int n = MAX_CHAIN / perChunk;
   if (a.residual && n > nChunks / 4) n = nChunks / 4;
