@@ -151,6 +151,25 @@ def _event_ms(fn, reps: int, warmup: int) -> float:
     return a.elapsed_time(b) / reps
 
 
+def _graph_ms(fn, reps: int, warmup: int) -> float:
+    """Average milliseconds of one fn() launch: `reps` calls captured back to back into one CUDA graph (after `warmup`
+    eager calls), the graph replayed once untimed and then three times between two events. Keeps the host's launch
+    path (Python, ctypes, tensor-map encoding: tens of microseconds per call) out of the number, which matters for
+    kernels that run shorter than that."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            keep = [fn() for _ in range(reps)]
+    graph.replay()
+    ms = _event_ms(graph.replay, 3, 0) / reps
+    del keep, graph
+    return ms
+
+
 def measure_cfg1(gen, dev, steps: int) -> dict:
     """BASELINE config 1: the 4 s sentence case (T = 320), one CUDA-graph replay per step, inputs resident."""
     t = 320
@@ -202,8 +221,9 @@ def measure_sweep(dev, peak: float) -> dict:
     """BASELINE config 4: fused conv1d_snake_res at Cin = Cout in {128, 256, 512}, K in {3, 7, 11}, dilation in
     {1, 3, 5}, L in {320, 3200, 19200, 124800} (rows 16-byte aligned: every L is a multiple of 4), and the two
     ConvTranspose upsamplers at Lin in {320, 2080} (x10) / {3200, 20800} (x6). Inputs are seeded normal draws made on
-    the device; 5 launches per point after 2 warm-ups. Rows: [C, L, K, dilation, ms, TFLOP/s, fraction of the
-    split-operand tensor roofline]."""
+    the device; per point 5 launches captured into one CUDA graph after 2 warm-ups, the graph replayed three times
+    between two events (the host's launch path is longer than the kernels of the short rows). Rows: [C, L, K,
+    dilation, ms, TFLOP/s, fraction of the split-operand tensor roofline]."""
     from lokinfer_b200 import ops
 
     g = torch.Generator(device=dev)
@@ -221,7 +241,7 @@ def measure_sweep(dev, peak: float) -> dict:
                 res = torch.randn(c, l, device=dev, generator=g)
                 for d in (1, 3, 5):
                     pad = d * (k - 1) // 2
-                    ms = _event_ms(lambda: ops.conv1d_snake_f32_cuda(x, w, bias, affine, alpha, residual=res,
+                    ms = _graph_ms(lambda: ops.conv1d_snake_f32_cuda(x, w, bias, affine, alpha, residual=res,
                                                                      padding=pad, dilation=d, state=st), 5, 2)
                     tf = 2.0 * c * c * k * l / (ms * 1e-3) / 1e12
                     rows.append([c, l, k, d, round(ms, 5), round(tf, 2), round(tf / peak, 4)])
@@ -236,7 +256,7 @@ def measure_sweep(dev, peak: float) -> dict:
             x = torch.randn(ci, lin, device=dev, generator=g)
             with ops.padded_rows():
                 res = ops.to_cuda(torch.randn(co, lin * s + pl, device=dev, generator=g), dev, rows=True)
-                ms = _event_ms(lambda: ops.conv_transpose1d_poly_f32_cuda(x, wp, bias, res, stride=s, padding=p,
+                ms = _graph_ms(lambda: ops.conv_transpose1d_poly_f32_cuda(x, wp, bias, res, stride=s, padding=p,
                                                                           taps=k // s, slope=0.1, pad_left=pl,
                                                                           state=st), 5, 2)
             tf = 2.0 * ci * co * k * lin / (ms * 1e-3) / 1e12
@@ -472,8 +492,9 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     roofline, cpu_base, kernels = None, None, None
     if rank == 0:
         # per-launch timing of the fused conv kernels (eager pass, CUDA event pair around every launch)
-        # one stream, every launch repeated 4x back to back inside its event pair (after one untimed launch)
-        with ops.Profile(repeat=4) as prof:
+        # one stream; every launch is followed by a small captured graph of 4 repeats of itself, replayed once untimed
+        # and once inside its event pair: no host launch path inside the timed region, as in the captured forward
+        with ops.Profile(repeat=4, graph=True) as prof:
             gen.forward(bufs["x"], bufs["har"], bufs["s"], concurrent=False)
         rows = prof.rows()
         agg = {}
@@ -503,9 +524,13 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                     "product)",
                     "conv_ms_per_step": conv_ms, "conv_flops_per_step": conv_flops,
                     "note": "conv_ms_per_step sums the launches timed one at a time on one stream (each alone on the "
-                            "GPU); ms_per_step is the captured graph, where independent branches run on side streams "
-                            "and the tail of one persistent conv overlaps the start of another, so it can be smaller "
-                            "than conv_ms_per_step"}
+                            "GPU, 4 graph-captured repeats per launch inside its event pair); ms_per_step is the "
+                            "captured forward, where independent branches run on side streams and the tail of one "
+                            "persistent conv overlaps the start of another, so it can be smaller than conv_ms_per_step",
+                    # the same FLOPs over the whole captured step (all kernels of the forward, not only the convs): a
+                    # lower bound of what the convs reach inside the step
+                    "achieved_step_bound": conv_flops / (ms_dev / args.steps * 1e-3) / 1e12,
+                    "frac_step_bound": conv_flops / (ms_dev / args.steps * 1e-3) / 1e12 / peak}
         if world == 1 and not args.no_cpu:
             t_sample = t
             rate, sec, cores = cpu_generator_rate(t_sample, 3, 1, None)

@@ -141,7 +141,8 @@ LKC_API int lkc_conv1d_leaky_mean3_f32_cuda(const LkcArgs* a, void* stream);
  * semantics. lkc_conv1d_tc_status waits for all work queued on the current device (cudaDeviceSynchronize; do not call
  * it inside a stream capture), then reads (and optionally clears) the device status word: low 16 bits = role << 8 |
  * code of the first bounded wait that gave up (0 = none); bit 0x10000 = an activation exceeded the f16 range (65504)
- * under the f16 operand split and was clamped; bit 0x20000 = a weight exceeded that range when an f16 pack was made
+ * under the f16 operand split (it became an infinite operand: the output of that launch is not finite); bit 0x20000
+ * = a weight exceeded that range when an f16 pack was made
  * (pack it again after lkc_set_conv_path(2): the tf32 format has the range of f32). lkc_set_conv_io(1) makes later
  * launches use 4-byte accesses even for aligned rows, lkc_set_conv_io(0) (default) the TMA unit where rows are
  * 16-byte aligned (A/B testing). lkc_set_conv_path chooses the path and the operand format of packs made

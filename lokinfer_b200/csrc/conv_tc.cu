@@ -84,8 +84,8 @@ static_assert(EPI_WARPS * 32 * EPI_REGS + (NWARPS - EPI_WARPS) * 32 * PRO_REGS <
 //     per tap and 16 channels 3 MMAs of kind::f16 (K16): hi*hi into Dhi, lo*hi + hi*lo into Dlo, which is folded in
 //     with the factor 2^-11. Products are exact and accumulate in f32 as before, so the accuracy is that of the
 //     tf32 split at half the tensor time, half the staged bytes and half the weight traffic. Values beyond the f16
-//     range (|v| > 65504) are clamped in the f16 operands and flagged in the status word (activations:
-//     kStatusF16Range, weights at pack time: kStatusF16Weights).
+//     range (|v| > 65504) are flagged in the status word: an activation becomes an infinite f16 operand (the output
+//     of that launch is then not finite; kStatusF16Range), a weight is clamped at pack time (kStatusF16Weights).
 constexpr float kLoScale = 2048.f;  // 2^11
 constexpr int kStatusF16Range = 0x10000, kStatusF16Weights = 0x20000, kStatusWaitMask = 0xffff;
 template <bool F16>
@@ -289,23 +289,6 @@ __device__ __forceinline__ void tmemLoad16Async(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 __device__ __forceinline__ void tmemWaitLoads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void tmemLoad32(uint32_t taddr, float* v) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrix = 8 rows x 16 bytes stored contiguously (rows at
 // 16-byte pitch), `sbo` = byte distance between 8-row groups, `lbo` = byte distance between the two 16-byte K chunks
@@ -870,47 +853,48 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         pb[h] = make_float2(par[2 * a.ci], par[2 * a.ci + 1]);
         pi[h] = make_float2(par[3 * a.ci], par[3 * a.ci + 1]);
       }
-#pragma unroll 2
+      float big = 0.f;  // largest |value| this thread staged in the chunk (f16 range check, once per chunk)
+#pragma unroll
       for (int sl = 0; sl < SLOTS; ++sl) {
-        const int r = r0 + sl * 32 + lane;
-        if (r < r1) {
-          const int64_t pos = pos0 + r;
-          const bool ok = pos >= a.validLo && pos < a.validHi;
-          float2 v01 = make_float2(0.f, 0.f), v23 = v01;
-          if (ok) {
-            const float* sp = src + r + (r + delta >= half ? runSkip : 0);
-            v01 = activate2<ACT>(make_float2(sp[0], sp[half]), nm[0], pa[0], pb[0], pi[0], a.slope);
-            v23 = activate2<ACT>(make_float2(sp[2 * half], sp[3 * half]), nm[1], pa[1], pb[1], pi[1], a.slope);
-          }
-          if constexpr (!F16) {
-            float4 h, l;
-            h.x = tf32Round(v01.x), h.y = tf32Round(v01.y), h.z = tf32Round(v23.x), h.w = tf32Round(v23.y);
-            const float2 l01 = __fadd2_rn(v01, make_float2(-h.x, -h.y)), l23 = __fadd2_rn(v23, make_float2(-h.z, -h.w));
-            l = make_float4(l01.x, l01.y, l23.x, l23.y);
+        // Branch-free body, so that the iterations' dependency chains interleave: rows beyond the thread's range
+        // recompute its last row and skip the stores; positions outside the valid range select zero.
+        const int rq = r0 + sl * 32 + lane;
+        const bool inr = rq < r1;
+        const int r = inr ? rq : r1 - 1;
+        const int64_t pos = pos0 + r;
+        const bool ok = pos >= a.validLo && pos < a.validHi;
+        const float* sp = src + r + (r + delta >= half ? runSkip : 0);
+        float2 v01 = activate2<ACT>(make_float2(sp[0], sp[half]), nm[0], pa[0], pb[0], pi[0], a.slope);
+        float2 v23 = activate2<ACT>(make_float2(sp[2 * half], sp[3 * half]), nm[1], pa[1], pb[1], pi[1], a.slope);
+        v01.x = ok ? v01.x : 0.f, v01.y = ok ? v01.y : 0.f, v23.x = ok ? v23.x : 0.f, v23.y = ok ? v23.y : 0.f;
+        if constexpr (!F16) {
+          float4 h, l;
+          h.x = tf32Round(v01.x), h.y = tf32Round(v01.y), h.z = tf32Round(v23.x), h.w = tf32Round(v23.y);
+          const float2 l01 = __fadd2_rn(v01, make_float2(-h.x, -h.y)), l23 = __fadd2_rn(v23, make_float2(-h.z, -h.w));
+          l = make_float4(l01.x, l01.y, l23.x, l23.y);
+          if (inr) {
             *reinterpret_cast<float4*>(hi + r * 4) = h;
             *reinterpret_cast<float4*>(lo + r * 4) = l;
-          } else {
-            // hi = f16(v) (clamped to the f16 range), lo = f16((v - hi) * 2^11); 4 channels = 8 bytes of the row's
-            // 16-byte K chunk (channel groups 2 j and 2 j + 1 share chunk j)
-            const float big = fmaxf(fmaxf(fabsf(v01.x), fabsf(v01.y)), fmaxf(fabsf(v23.x), fabsf(v23.y)));
-            if (big > 65504.f) {
-              atomicOr(a.status, kStatusF16Range);
-              v01.x = fminf(fmaxf(v01.x, -65504.f), 65504.f), v01.y = fminf(fmaxf(v01.y, -65504.f), 65504.f);
-              v23.x = fminf(fmaxf(v23.x, -65504.f), 65504.f), v23.y = fminf(fmaxf(v23.y, -65504.f), 65504.f);
-            }
-            const __half2 h01 = __float22half2_rn(v01), h23 = __float22half2_rn(v23);
-            const float2 sc = make_float2(kLoScale, kLoScale);
-            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-            const __half2 l01 = __float22half2_rn(__fmul2_rn(__fadd2_rn(v01, make_float2(-f01.x, -f01.y)), sc));
-            const __half2 l23 = __float22half2_rn(__fmul2_rn(__fadd2_rn(v23, make_float2(-f23.x, -f23.y)), sc));
-            uint2 hw, lw;
-            hw.x = *reinterpret_cast<const uint32_t*>(&h01), hw.y = *reinterpret_cast<const uint32_t*>(&h23);
-            lw.x = *reinterpret_cast<const uint32_t*>(&l01), lw.y = *reinterpret_cast<const uint32_t*>(&l23);
+          }
+        } else {
+          // hi = f16(v), lo = f16((v - hi) * 2^11); 4 channels = 8 bytes of the row's 16-byte K chunk (channel groups
+          // 2 j and 2 j + 1 share chunk j). A value beyond the f16 range becomes infinite here and is reported below.
+          big = fmaxf(big, fmaxf(fmaxf(fabsf(v01.x), fabsf(v01.y)), fmaxf(fabsf(v23.x), fabsf(v23.y))));
+          const __half2 h01 = __float22half2_rn(v01), h23 = __float22half2_rn(v23);
+          const float2 sc = make_float2(kLoScale, kLoScale);
+          const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+          const __half2 l01 = __float22half2_rn(__fmul2_rn(__fadd2_rn(v01, make_float2(-f01.x, -f01.y)), sc));
+          const __half2 l23 = __float22half2_rn(__fmul2_rn(__fadd2_rn(v23, make_float2(-f23.x, -f23.y)), sc));
+          uint2 hw, lw;
+          hw.x = *reinterpret_cast<const uint32_t*>(&h01), hw.y = *reinterpret_cast<const uint32_t*>(&h23);
+          lw.x = *reinterpret_cast<const uint32_t*>(&l01), lw.y = *reinterpret_cast<const uint32_t*>(&l23);
+          if (inr) {
             *reinterpret_cast<uint2*>(hi + r * 4) = hw;
             *reinterpret_cast<uint2*>(lo + r * 4) = lw;
           }
         }
       }
+      if (F16 && big > 65504.f) atomicOr(a.status, kStatusF16Range);
       fenceProxyAsync();  // generic-proxy stores -> visible to the tensor core (async proxy)
       __syncwarp();
       if (lane == 0) {
@@ -1005,7 +989,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       // and, rarely, a real wait separate two rounds.
       // Order inside a round: the lo MMAs first, then the hi MMAs, so that the wait for the Dhi drain at the start
       // of a drain group is covered by the round's own lo MMAs. The first round of a tile goes the other way round,
-      // because there Dhi is handed back before Dlo.
+      // because there Dhi is handed back before Dlo. (Issuing hi first in the last round of a drain group as well,
+      // which lengthens the cover of the drain to this round's and the next round's lo MMAs, shortened the waits
+      // but not the tile: the extra code in this loop cost what the waits gave back.)
       const uint64_t dA0 = makeDesc(smemAddr(sW), MT * 16, 128);
       const uint64_t dB0 = makeDesc(smemAddr(sAct), rows * 16, 128);
       constexpr uint32_t kStageU = W_STAGE_BYTES >> 4, kLoAU = (W_STAGE_BYTES / 2) >> 4, kKsAU = (2 * MT * 16) >> 4;
@@ -1040,65 +1026,63 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             const uint32_t accHi = (kk | g) == 0 ? 0u : 1u, accLo = (kk | c) == 0 ? 0u : 1u;
             const bool needHi = (kk | g) == 0, needLo = (kk | c) == 0;  // Dhi drained / Dlo of the last tile folded
             const uint32_t aLo = uint32_t(dA), aHi = uint32_t(dA >> 32), bLo = uint32_t(dB), bHi = uint32_t(dB >> 32);
-            auto hiTap = [&](int j) {
-              const uint32_t acc = j == 0 ? accHi : 1u;
+            // Rolled issue loops: the issuer's code between two MMAs has to be fetched and issued while at most one
+            // MMA is in flight, so the loops are kept to a handful of instructions and exist once per order.
+            auto issueHi = [&](uint32_t acc) {
               if constexpr (F16) {
-                mmaF16W(tmemHi, aLo + uint32_t(j) * kStageU, aHi, bLo + uint32_t(j * dil), bHi, kIdescF16, acc);
+                uint32_t aj = aLo, bj = bLo;
+#pragma unroll 1
+                for (int j = 0; j < gN; ++j, aj += kStageU, bj += uint32_t(dil), acc = 1u)
+                  mmaF16W(tmemHi, aj, aHi, bj, bHi, kIdescF16, acc);
               } else {
-                const uint64_t dAh = dA + uint32_t(j) * kStageU, dBh = dB + uint32_t(j * dil);
-                mmaTf32(tmemHi, dAh, dBh, kIdesc, acc);
-                mmaTf32(tmemHi, dAh + kKsAU, dBh + ksBU, kIdesc, 1u);
+                uint64_t dAh = dA, dBh = dB;
+#pragma unroll 1
+                for (int j = 0; j < gN; ++j, dAh += kStageU, dBh += uint32_t(dil), acc = 1u) {
+                  mmaTf32(tmemHi, dAh, dBh, kIdesc, acc);
+                  mmaTf32(tmemHi, dAh + kKsAU, dBh + ksBU, kIdesc, 1u);
+                }
               }
             };
-            auto loTap = [&](int j) {
-              const uint32_t acc = j == 0 ? accLo : 1u;
+            auto issueLo = [&](uint32_t acc) {
               if constexpr (F16) {
-                const uint32_t aj = aLo + uint32_t(j) * kStageU, bj = bLo + uint32_t(j * dil);
-                mmaF16W(tmemLo, aj + kLoAU, aHi, bj, bHi, kIdescF16, acc);
-                mmaF16W(tmemLo, aj, aHi, bj + loBU, bHi, kIdescF16, 1u);
+                uint32_t aj = aLo, bj = bLo;
+#pragma unroll 1
+                for (int j = 0; j < gN; ++j, aj += kStageU, bj += uint32_t(dil), acc = 1u) {
+                  mmaF16W(tmemLo, aj + kLoAU, aHi, bj, bHi, kIdescF16, acc);
+                  mmaF16W(tmemLo, aj, aHi, bj + loBU, bHi, kIdescF16, 1u);
+                }
               } else {
-                const uint64_t dAh = dA + uint32_t(j) * kStageU, dBh = dB + uint32_t(j * dil);
-                const uint64_t dAl = dAh + kLoAU, dBl = dBh + loBU;
-                mmaTf32(tmemLo, dAl, dBh, kIdesc, acc);
-                mmaTf32(tmemLo, dAh, dBl, kIdesc, 1u);
-                mmaTf32(tmemLo, dAl + kKsAU, dBh + ksBU, kIdesc, 1u);
-                mmaTf32(tmemLo, dAh + kKsAU, dBl + ksBU, kIdesc, 1u);
+                uint64_t dAh = dA, dBh = dB;
+#pragma unroll 1
+                for (int j = 0; j < gN; ++j, dAh += kStageU, dBh += uint32_t(dil), acc = 1u) {
+                  const uint64_t dAl = dAh + kLoAU, dBl = dBh + loBU;
+                  mmaTf32(tmemLo, dAl, dBh, kIdesc, acc);
+                  mmaTf32(tmemLo, dAh, dBl, kIdesc, 1u);
+                  mmaTf32(tmemLo, dAl + kKsAU, dBh + ksBU, kIdesc, 1u);
+                  mmaTf32(tmemLo, dAh + kKsAU, dBl + ksBU, kIdesc, 1u);
+                }
               }
             };
             int nslot = slot + 1;
             uint32_t nph = slotPh;
-            if (needLo) {  // first round of a tile: hi, then lo
+            if (nslot == wStages) nslot = 0, nph ^= 1;
+            if (needLo) {  // first round of a tile: hi, then lo (Dhi is handed back before Dlo)
               if (needHi && !waitT(hiEmpty, groupPar ^ 1, wHe, SLEEP_MMA_NS)) {
                 giveUp(4, 1);
                 dead = true;
                 break;
               }
               tcFenceAfter();
-              hiTap(0);
-              if (nslot == wStages) nslot = 0, nph ^= 1;
-              ready = mbarTryWait(&wFull[nslot], nph);
-#pragma unroll
-              for (int j = 1; j < TAP_GROUP; ++j)
-                if (j < gN) hiTap(j);
+              issueHi(accHi);
               if (!waitT(loEmpty, tilePar ^ 1, wLe, SLEEP_MMA_NS)) {
                 giveUp(4, 4);
                 dead = true;
                 break;
               }
               tcFenceAfter();
-#pragma unroll
-              for (int j = 0; j < TAP_GROUP; ++j)
-                if (j < gN) loTap(j);
+              issueLo(accLo);
             } else {
-              loTap(0);
-              if (nslot == wStages) nslot = 0, nph ^= 1;
-              static_assert(TAP_GROUP == 4, "the switches below spell out group sizes 1..4");
-              switch (gN) {  // exact tap counts: a predicated-off tap still costs the issuing thread its slots
-                case 4: loTap(1), loTap(2), loTap(3); break;
-                case 3: loTap(1), loTap(2); break;
-                case 2: loTap(1); break;
-                default: break;
-              }
+              issueLo(accLo);
               if (needHi) {
                 if (!waitT(hiEmpty, groupPar ^ 1, wHe, SLEEP_MMA_NS)) {
                   giveUp(4, 1);
@@ -1107,17 +1091,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                 }
                 tcFenceAfter();
               }
-              switch (gN) {
-                case 4: hiTap(0), hiTap(1), hiTap(2), hiTap(3); break;
-                case 3: hiTap(0), hiTap(1), hiTap(2); break;
-                case 2: hiTap(0), hiTap(1); break;
-                default: hiTap(0); break;
-              }
-              // first poll of the next slot's barrier, with the whole round queued behind it: a poll of a barrier
-              // that is not complete yet parks the thread for a while, which is free here and was not after the
-              // round's first MMA (with two slots the next one is still being refilled at that point)
-              ready = mbarTryWait(&wFull[nslot], nph);
+              issueHi(accHi);
             }
+            // first poll of the next slot's barrier, with the whole round queued behind it
+            ready = mbarTryWait(&wFull[nslot], nph);
             mmaCommit(&wEmpty[slot]);  // weight slot free once the MMAs have read it
             kk += gN;
             slot = nslot, slotPh = nph;

@@ -317,7 +317,7 @@ class Generator:
         """End-to-end call with HOST buffers (pinned torch tensors for async copies): host -> device copies, one
         graph replay, device -> host copy of the waveform. Returns the host waveform tensor. Raises if the tensor-core
         kernels reported a problem during the call (a bounded wait that gave up, or an activation beyond the f16
-        range of the split operands, which is clamped and would make the waveform wrong)."""
+        range of the split operands, which overflows there and makes the waveform wrong)."""
         t = int(x_host.shape[1])
         b = self.capture(t)
         b["x"].copy_(x_host, non_blocking=True)

@@ -262,7 +262,7 @@ def test_conv1d_tensor_core_tf32_split(cuda, ci, co, l, k, d, variant):
 
 
 def test_conv1d_f16_split_reports_values_beyond_f16_range(cuda):
-    """Activations beyond the f16 range (65504) are clamped by the f16 operand split and reported in the status
+    """Activations beyond the f16 range (65504) overflow the f16 operand split and are reported in the status
     word (bit 0x10000); the tf32 split and the CUDA-core kernel take the same input without a report."""
     from lokinfer_b200 import ops
     ci = co = 128
