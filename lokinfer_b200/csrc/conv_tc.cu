@@ -38,7 +38,7 @@
 //               channels]: a tap shift of kk*d time steps is a +16*kk*d byte offset of the descriptor start address,
 //               so one staged window serves all taps (on the unaligned route they also issue the cp.async of the next
 //               chunk's raw window)
-//   warp 9      weight producer: one cp.async.bulk per tap group (up to 4 taps; hi | lo of [128 co x 16 ci] per tap,
+//   warp 9      weight producer: one cp.async.bulk per tap group (up to 6 taps; hi | lo of [128 co x 16 ci] per tap,
 //               pre-packed in the UMMA layout, L2-resident) into a ring of shared-memory slots
 //   warp 13     MMA issuer (one lane): per tap group one wait, the group's MMAs back to back, one release
 //   warp 17     raw-window loader of the aligned route (one lane): two tiled TMA loads per chunk, one chunk ahead
@@ -101,7 +101,7 @@ constexpr int BOX = 32, BOX_BYTES = BOX * BOX * 4;  // residual / output boxes o
 static_assert(BOX_BYTES <= STAGE_FLOATS * 4, "a swizzled box fits in a warp's tile");
 constexpr int MAX_HALO = 50;     // (K - 1) * dilation of the widest Kokoro conv (K 11, dilation 5)
 constexpr int MAX_W_STAGES = 4, MIN_W_STAGES = 2, PREF_W_STAGES = 2;  // weight ring slots
-constexpr int TAP_GROUP = 4;  // most taps per weight slot: one bulk copy, one wait, MMAs back to back, one release
+constexpr int TAP_GROUP = 6;  // most taps per weight slot: one bulk copy, one wait, MMAs back to back, one release
 constexpr int MAX_CHAIN = 24;  // most chained hi MMAs between two drains of Dhi
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr uint32_t SLEEP_EPI_NS = 256, SLEEP_PRO_NS = 128, SLEEP_W_NS = 64, SLEEP_MMA_NS = 32;
@@ -1218,7 +1218,8 @@ static size_t convTcSmemBytes(int64_t ci, int rows, int k, bool f16, int* wStage
   const SmemLayout base = smemLayout(int(ci), rows, half, nb, 0, 0, actRow, tap);
   if (base.total > uint32_t(kMaxSmem)) return 0;
   const size_t avail = size_t(kMaxSmem) - base.total;
-  // Large groups matter more than a deep ring (measured: two slots of four taps beat four slots of three).
+  // Large groups matter more than a deep ring (measured: two slots of four taps beat four slots of three, and at
+  // K = 11 two slots of six beat three of four).
   int bestG = 0, bestWs = 0;
   for (int g = TAP_GROUP; g >= 1; --g) {
     const int groups = (k + g - 1) / g, gmax = (k + groups - 1) / groups;  // near-equal groups, the largest has gmax taps
