@@ -338,8 +338,8 @@ def measure_time_sharded(gen, dev, rank: int, world: int, t: int, steps: int, si
     """BASELINE config 2 on N GPUs: ONE utterance of t frames cut along time over the ranks (lokinfer_b200/timeshard.py:
     halo columns by plain peer stores + release flags, chunk statistics gathered into every rank's row, bounded
     waits), one captured graph replay per step on every rank, time = max over ranks. Strong scaling of a single
-    utterance: about 53 exchanges per forward, each a push kernel, a peer round trip and a wait kernel, so the step is
-    bound by exchange latency; the record says how far. Returns the record on rank 0."""
+    utterance: about 53 exchanges per forward, each one kernel (push, peer round trip, wait), so the step is bound by
+    exchange latency; the record says how far. Returns the record on rank 0."""
     import torch.distributed as dist
 
     from lokinfer_b200 import ops, timeshard as ts
@@ -377,9 +377,9 @@ def measure_time_sharded(gen, dev, rank: int, world: int, t: int, steps: int, si
             "frames_per_rank": [y - x_ for x_, y in zip(tsg.part.bx, tsg.part.bx[1:])],
             "exchanges_per_forward": 53, "us_per_exchange_over_ideal": (ms - single_ms / world) * 1e3 / 53,
             "max_abs_diff_vs_single_gpu": float(vals[1].item()), "wait_status": int(vals[2].item()),
-            "limiter": "exchange latency: every conv output is followed by a push kernel, the peer stores with "
-                       "their release flags and a wait kernel on the consumer side before the next conv may start; "
-                       "NCCL is not on this path"}
+            "limiter": "exchange latency: every conv output is followed by one exchange kernel (peer stores of the "
+                       "boundary columns and the statistics slice, release flags, then a bounded wait for the "
+                       "neighbours' flags) before the next conv may start; NCCL is not on this path"}
 
 
 def init_nccl(dev):

@@ -268,6 +268,12 @@ LKC_API int lkc_shard_push(const LkcShardPush* desc, void* stream);
 LKC_API int lkc_shard_wait(void* const* flags, int num_flags, const void* epoch, int delta, uint64_t limit_ns,
                            void* status, void* stream);
 LKC_API int lkc_shard_epoch_bump(void* epoch, void* stream);
+/* lkc_shard_push followed by lkc_shard_wait on wait_flags in ONE launch (the block that publishes the flags then waits
+ * for this rank's own): one kernel between a producer and its consumer instead of two. Only for ranks on different
+ * GPUs: ranks that share a GPU queue every push before any wait (separate calls), since a kernel that waits for a
+ * later launch on its own GPU would only run out its limit. */
+LKC_API int lkc_shard_exchange(const LkcShardPush* desc, void* const* wait_flags, int num_wait, int delta,
+                               uint64_t limit_ns, void* status, void* stream);
 /* Set-up of the peer-mapped memory the calls above work on (the only entry points that allocate device memory on
  * purpose; none of them is on the data path): lkc_peer_alloc = cudaMalloc + zero fill of one arena, lkc_peer_handle
  * exports it (64-byte CUDA IPC handle, to be sent to the other ranks by any host channel), lkc_peer_open maps a

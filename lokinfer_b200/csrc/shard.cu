@@ -31,6 +31,11 @@ struct PushArgs {
   int numFlags;
   const int* epoch;
   unsigned* ticket;
+  // exchange form: after its own flags are out, the last block waits for these (numWait = 0: push only)
+  const int* waitFlags[kMaxFlags];
+  int numWait, delta;
+  unsigned long long limitNs;
+  int* status;
 };
 
 __device__ __forceinline__ void storeReleaseSys(int* p, int v) {
@@ -47,9 +52,25 @@ __device__ __forceinline__ uint64_t timerNs() {
   return t;
 }
 
+// Gives up after limitNs: status |= 1 << 24 | flag index (first one wins the index bits).
+__device__ __forceinline__ void waitFlag(const int* flag, int f, int want, unsigned long long limitNs, int* status) {
+  const uint64_t t0 = timerNs();
+  unsigned spins = 0;
+  while (loadAcquireSys(flag) < want) {
+    __nanosleep(64);
+    if ((++spins & 15u) == 0 && timerNs() - t0 > limitNs) {
+      atomicCAS(status, 0, (1 << 24) | f);
+      return;
+    }
+  }
+}
+
 // All copies (lanes along the columns of a block), then a system-scope fence per thread; the last block to finish
-// publishes the epoch in every destination flag.
+// publishes the epoch in every destination flag and, in the exchange form, then waits for this rank's own flags (one
+// thread per flag), so that one launch stands between the producing kernel and its consumer instead of two. The wait
+// comes after the push: no rank waits before its own boundary data is out.
 __global__ void __launch_bounds__(256) shardPushKernel(const PushArgs a) {
+  __shared__ int sLast;
   for (int i = 0; i < a.numCopies; ++i) {
     const int64_t total = int64_t(a.rows[i]) * a.cols[i];
     for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < total; idx += int64_t(gridDim.x) * blockDim.x) {
@@ -61,13 +82,18 @@ __global__ void __launch_bounds__(256) shardPushKernel(const PushArgs a) {
   __syncthreads();
   if (threadIdx.x == 0) {
     const unsigned done = atomicAdd(a.ticket, 1u);
-    if (done == gridDim.x - 1) {
+    sLast = done == gridDim.x - 1;
+    if (sLast) {
       *a.ticket = 0;  // ready for the next launch that uses this ticket
       __threadfence_system();
       const int e = *a.epoch;
       for (int f = 0; f < a.numFlags; ++f) storeReleaseSys(a.flags[f], e);
     }
   }
+  if (a.numWait == 0) return;
+  __syncthreads();
+  if (sLast && int(threadIdx.x) < a.numWait)
+    waitFlag(a.waitFlags[threadIdx.x], int(threadIdx.x), *a.epoch + a.delta, a.limitNs, a.status);
 }
 
 struct WaitArgs {
@@ -79,20 +105,11 @@ struct WaitArgs {
   int* status;
 };
 
-// One thread per flag. Gives up after limitNs: status |= 1 << 24 | flag index (first one wins the index bits).
+// One thread per flag.
 __global__ void shardWaitKernel(const WaitArgs a) {
   const int f = threadIdx.x;
   if (f >= a.numFlags) return;
-  const int want = *a.epoch + a.delta;
-  const uint64_t t0 = timerNs();
-  unsigned spins = 0;
-  while (loadAcquireSys(a.flags[f]) < want) {
-    __nanosleep(64);
-    if ((++spins & 15u) == 0 && timerNs() - t0 > a.limitNs) {
-      atomicCAS(a.status, 0, (1 << 24) | f);
-      return;
-    }
-  }
+  waitFlag(a.flags[f], f, *a.epoch + a.delta, a.limitNs, a.status);
 }
 
 __global__ void epochBumpKernel(int* epoch) { *epoch += 1; }
@@ -102,7 +119,8 @@ __global__ void epochBumpKernel(int* epoch) { *epoch += 1; }
 
 using namespace lkc;
 
-extern "C" LKC_API int lkc_shard_push(const LkcShardPush* d, void* stream) {
+static int pushLaunch(const LkcShardPush* d, void* const* waitFlags, int numWait, int delta, uint64_t limitNs,
+                      void* status, void* stream, const char* what) {
   LKC_REQUIRE(d && d->num_copies >= 0 && d->num_copies <= kMaxCopies && d->num_flags >= 0 && d->num_flags <= kMaxFlags,
               "shard_push: too many copies or flags");
   LKC_REQUIRE(d->epoch && d->ticket, "shard_push: null epoch or ticket");
@@ -125,10 +143,25 @@ extern "C" LKC_API int lkc_shard_push(const LkcShardPush* d, void* stream) {
   }
   a.numFlags = d->num_flags;
   a.epoch = static_cast<const int*>(d->epoch), a.ticket = static_cast<unsigned*>(d->ticket);
+  LKC_REQUIRE(numWait >= 0 && numWait <= kMaxFlags && (numWait == 0 || (waitFlags && status)), "shard_exchange: bad wait");
+  for (int f = 0; f < numWait; ++f) {
+    LKC_REQUIRE(waitFlags[f], "shard_exchange: null flag");
+    a.waitFlags[f] = static_cast<const int*>(waitFlags[f]);
+  }
+  a.numWait = numWait, a.delta = delta, a.limitNs = limitNs, a.status = static_cast<int*>(status);
   int blocks = int(ceilDiv(most, 256));
   blocks = blocks < 1 ? 1 : (blocks > 64 ? 64 : blocks);
   shardPushKernel<<<blocks, 256, 0, S(stream)>>>(a);
-  return launched("shard_push");
+  return launched(what);
+}
+
+extern "C" LKC_API int lkc_shard_push(const LkcShardPush* d, void* stream) {
+  return pushLaunch(d, nullptr, 0, 0, 0, nullptr, stream, "shard_push");
+}
+
+extern "C" LKC_API int lkc_shard_exchange(const LkcShardPush* d, void* const* wait_flags, int num_wait, int delta,
+                                          uint64_t limit_ns, void* status, void* stream) {
+  return pushLaunch(d, wait_flags, num_wait, delta, limit_ns, status, stream, "shard_exchange");
 }
 
 extern "C" LKC_API int lkc_shard_wait(void* const* flags, int num_flags, const void* epoch, int delta,

@@ -13,7 +13,8 @@ computes over its own columns are exactly the chunks of the unsharded tensor. Ev
 buffer [C, MARGIN + longest shard + MARGIN]; the margins hold the neighbours' boundary columns (the receptive-field
 halo, at most 25 columns for k = 11, dilation 5).
 
-After each producing kernel comes one exchange (lkc_shard_push / lkc_shard_wait, csrc/shard.cu): the boundary columns
+After each producing kernel comes one exchange (lkc_shard_push + lkc_shard_wait, or both in one launch with
+lkc_shard_exchange when every rank has its own GPU; csrc/shard.cu): the boundary columns
 go into the neighbours' margins and the rank's slice of the chunk statistics into every rank's copy of the whole
 statistics row, by plain stores to peer memory, then a release flag per destination; the consumer waits (bounded) on
 its own flags. About 53 exchanges per forward: the sharded forward is bound by their latency, not by bandwidth.
@@ -104,7 +105,10 @@ class Arena:
 
 
 class LocalFabric:
-    """All ranks in this process (one GPU): a peer's arena is simply that rank's arena."""
+    """All ranks in this process (one GPU): a peer's arena is simply that rank's arena. Pushes and waits stay separate
+    launches: every rank's push is queued before any rank's wait."""
+
+    fused = False
 
     def __init__(self, world: int, nbytes: int, device):
         self.world = world
@@ -118,7 +122,10 @@ class LocalFabric:
 
 
 class IpcFabric:
-    """One process per GPU: the arenas are exchanged as CUDA IPC handles over the process group."""
+    """One process per GPU: the arenas are exchanged as CUDA IPC handles over the process group. An exchange is one
+    launch (lkc_shard_exchange: push, then wait for the own flags)."""
+
+    fused = True
 
     def __init__(self, nbytes: int, device, group=None):
         import torch.distributed as dist
@@ -199,6 +206,8 @@ class TimeShardedGenerator:
         self._lib.lkc_shard_wait.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p,
                                              ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_void_p]
         self._lib.lkc_shard_epoch_bump.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        self._lib.lkc_shard_exchange.argtypes = [ctypes.POINTER(_Push), ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+                                                 ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_void_p]
 
     @staticmethod
     def arena_bytes(t: int, world: int) -> int:
@@ -239,8 +248,9 @@ class TimeShardedGenerator:
 
     # ------------------------------------------------------------------ exchange
 
-    def _push(self, buf, stats):
-        """Boundary columns of buf -> the neighbours' margins; this rank's statistics slice -> every rank's row."""
+    def _push(self, buf, stats, wait_slots=None):
+        """Boundary columns of buf -> the neighbours' margins; this rank's statistics slice -> every rank's row.
+        wait_slots: flag slots of this exchange to wait for in the same launch (ranks on different GPUs only)."""
         k, n, sp = self.rank, self.world, self._sync
         ops.check(sp < self.max_sync, "too many exchanges in one forward")
         d = _Push()
@@ -277,19 +287,33 @@ class TimeShardedGenerator:
                 nf += 1
         d.num_copies, d.num_flags = nc, nf
         d.epoch, d.ticket = self.ctl[0:1].data_ptr(), self.tickets[sp: sp + 1].data_ptr()
+        if nf and wait_slots:
+            arr = (ctypes.c_void_p * len(wait_slots))(*[self.flags[sp, s].data_ptr() for s in wait_slots])
+            if self._lib.lkc_shard_exchange(ctypes.byref(d), arr, len(wait_slots), 0,
+                                            ctypes.c_uint64(self.wait_limit_ns),
+                                            ctypes.c_void_p(self.ctl[1:2].data_ptr()),
+                                            ctypes.c_void_p(ops._stream())) != 0:
+                raise _lib.LkcError(_lib.last_error())
+            return True
         if nf and self._lib.lkc_shard_push(ctypes.byref(d), ctypes.c_void_p(ops._stream())) != 0:
             raise _lib.LkcError(_lib.last_error())
+        return False
+
+    def _slots(self, halo: bool, stats: bool):
+        k, n = self.rank, self.world
+        slots = []
+        if halo and k > 0:
+            slots.append(n)
+        if halo and k < n - 1:
+            slots.append(n + 1)
+        if stats:
+            slots += [r for r in range(n) if r != k]
+        return slots
 
     def _wait(self, halo: bool, stats: bool, delta=0, slots=None):
-        k, n, sp = self.rank, self.world, self._sync
+        sp = self._sync
         if slots is None:
-            slots = []
-            if halo and k > 0:
-                slots.append(n)
-            if halo and k < n - 1:
-                slots.append(n + 1)
-            if stats:
-                slots += [r for r in range(n) if r != k]
+            slots = self._slots(halo, stats)
         if slots:
             arr = (ctypes.c_void_p * len(slots))(*[self.flags[sp, s].data_ptr() for s in slots])
             if self._lib.lkc_shard_wait(arr, len(slots), ctypes.c_void_p(self.ctl[0:1].data_ptr()), delta,
@@ -299,11 +323,14 @@ class TimeShardedGenerator:
                 raise _lib.LkcError(_lib.last_error())
 
     def _exchange(self, buf, stats):
-        """Generator step: push, then (after every rank has pushed, in the lock-step fabric) wait."""
-        self._push(buf, stats)
+        """Generator step: push, then (after every rank has pushed, in the lock-step fabric) wait; one launch for both
+        when every rank has its own GPU."""
+        fused = getattr(self.fabric, "fused", False)
+        waited = self._push(buf, stats, self._slots(buf is not None, stats is not None) if fused else None)
         yield
         torch.cuda.set_stream(self._stream)  # another rank of this process may have switched streams meanwhile
-        self._wait(buf is not None, stats is not None)
+        if not waited:
+            self._wait(buf is not None, stats is not None)
         self._sync += 1
 
     def _use(self, stream):
