@@ -576,23 +576,30 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         ++groupIt;
         return true;
       };
-      // The first four drains each carry one residual batch; with fewer drains than batches the rest follow unhidden.
+      // Four residual batches per tile. With four or more drains the first four each carry one (fetched before the
+      // wait for the group, added after the drain); with fewer drains the surplus batches get steps of their own
+      // where this warp would otherwise only wait for a group: right after the first drain (the second group's MMAs
+      // hide their fetch latency; before the first drain the warp is still busy with the previous tile's final
+      // phase), or before the only drain of a tile, instead of between the last drain and the final phase.
       // One copy of the fetch and of the drain in the code (this kernel is far larger than the instruction cache,
       // and straight-line code that runs once per tile is fetched at a fraction of the issue rate); only the add
       // needs static register indices.
-      const int nSteps = hasRes && nGroups < 4 ? 4 : nGroups;
+      const int nPre = hasRes && nGroups < 4 ? 4 - nGroups : 0;
+      const int nSteps = nPre + nGroups, preAt = nGroups == 1 ? 0 : 1;  // first step without a drain
+      int rb = 0;  // next residual batch
 #pragma unroll 1
       for (int c = 0; c < nSteps && !dead; ++c) {
-        const bool doRes = hasRes && c < 4;
-        if (doRes) fetchResidual(c);
-        if (c < nGroups) dead = !drainGroup();
+        const bool doRes = hasRes && rb < 4;
+        if (doRes) fetchResidual(rb);
+        if (c < preAt || c >= preAt + nPre) dead = !drainGroup();
         if (doRes && !dead) {
-          switch (c) {
+          switch (rb) {
             case 0: addResidual(0); break;
             case 1: addResidual(1); break;
             case 2: addResidual(2); break;
             default: addResidual(3); break;
           }
+          ++rb;
         }
       }
       if (dead) break;
@@ -1405,11 +1412,9 @@ static int finishArgs(TcArgs& a, TcMaps& m, bool f16, bool boxesOk, int* grid, s
   if (int rc = deviceInfo(&d)) return rc;
   a.status = d->status;
   a.prof = (kProf && gProfileOn) ? d->prof : nullptr;
-  // Dhi is drained into the f32 running sums after as many whole chunks as fit in MAX_CHAIN chained MMAs; with a
-  // residual, at least four drains per tile so that each hides one residual batch.
-  const int perChunk = a.k * (f16 ? 1 : 2), nChunks = a.ci / KC;
-  int n = MAX_CHAIN / perChunk;
-  if (a.residual && n > nChunks / 4) n = nChunks / 4;
+  // Dhi is drained into the f32 running sums after as many whole chunks as fit in MAX_CHAIN chained MMAs.
+  const int perChunk = a.k * (f16 ? 1 : 2);
+  const int n = MAX_CHAIN / perChunk;
   a.drainN = n < 1 ? 1 : n;
   const int tiles = a.numTTiles * a.numCoBlk;
   *grid = tiles < d->smCount ? tiles : d->smCount;
