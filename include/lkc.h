@@ -155,6 +155,9 @@ LKC_API int lkc_conv1d_tc_pack_f32_cuda(const LkcArgs* a, void* stream);
 LKC_API LkcConvState* lkc_conv1d_state_create(const void* wp, int64_t co, int64_t ci, int64_t k);
 LKC_API void lkc_conv1d_state_destroy(LkcConvState* st);
 LKC_API int lkc_conv1d_tc_status(int* status, int reset);
+/* Stream-ordered form for callers that keep several utterances in flight: queues a 4-byte copy of the status word
+ * into status_host (pinned host memory) behind the work already on `stream`; synchronises nothing, clears nothing. */
+LKC_API int lkc_conv1d_tc_status_async(int* status_host, void* stream);
 LKC_API int lkc_set_conv_path(int mode);
 LKC_API int lkc_set_conv_io(int mode);
 /* Role-level cycle counters of the tensor-core kernel (the counterpart of the reference's per-kernel profiler,

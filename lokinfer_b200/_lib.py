@@ -59,6 +59,8 @@ def lib():
         l.lkc_conv1d_state_destroy.argtypes = [ctypes.c_void_p]
         l.lkc_conv1d_tc_status.restype = ctypes.c_int
         l.lkc_conv1d_tc_status.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+        l.lkc_conv1d_tc_status_async.restype = ctypes.c_int
+        l.lkc_conv1d_tc_status_async.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         l.lkc_conv1d_tc_profile.restype = ctypes.c_int
         l.lkc_conv1d_tc_profile.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int64)]
         l.lkc_set_conv_io.restype = ctypes.c_int

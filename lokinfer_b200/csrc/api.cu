@@ -264,6 +264,11 @@ extern "C" LKC_API int lkc_conv1d_tc_status(int* status, int reset) {
   return convTcStatus(status, reset != 0);
 }
 
+extern "C" LKC_API int lkc_conv1d_tc_status_async(int* status_host, void* stream) {
+  LKC_REQUIRE(status_host, "conv1d_tc_status_async: null out pointer");
+  return convTcStatusAsync(status_host, S(stream));
+}
+
 extern "C" LKC_API int lkc_conv1d_tc_profile(int enable, int64_t* counters16) {
   return convTcProfile(enable, reinterpret_cast<long long*>(counters16));
 }

@@ -1525,4 +1525,14 @@ int convTcStatus(int* out, bool reset) {
   return 0;
 }
 
+// Stream-ordered read of the status word: queues a 4-byte copy into `hostOut` (pinned host memory) behind the work
+// already on `s`; nothing is synchronised and nothing is cleared. The caller looks at *hostOut after it has
+// synchronised with `s` (an event, a stream synchronise).
+int convTcStatusAsync(int* hostOut, cudaStream_t s) {
+  const DeviceInfo* d = nullptr;
+  if (int rc = deviceInfo(&d)) return rc;
+  const cudaError_t e = cudaMemcpyAsync(hostOut, d->status, sizeof(int), cudaMemcpyDeviceToHost, s);
+  return e == cudaSuccess ? 0 : failCuda("conv1d_tc_status_async: cudaMemcpyAsync", e);
+}
+
 }  // namespace lkc

@@ -99,6 +99,7 @@ int64_t convTcPackFloats(int64_t co, int64_t ci, int64_t k, bool f16);
 int convTcPack(const float* w, float* wp, int64_t co, int64_t ci, int64_t k, bool f16, cudaStream_t s);
 int convTc(const ConvFusedParams& p, const float* wp, bool f16, cudaStream_t s);
 int convTcStatus(int* out, bool reset);
+int convTcStatusAsync(int* hostOut, cudaStream_t s);
 int convTcSetIo(int mode);
 int convTcProfile(int enable, long long* out16);
 

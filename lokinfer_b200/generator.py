@@ -313,6 +313,10 @@ class Generator:
             raise RuntimeError(f"tensor-core conv kernels reported status {status:#x}")
         return audio_host
 
+    def pipeline(self, t: int, depth: int = 2):
+        """Host-buffer synthesis with `depth` utterances of `t` frames in flight (see SynthesisPipeline)."""
+        return SynthesisPipeline(self, t, depth)
+
     def synthesize(self, x_host, har_host, s_host, audio_host=None):
         """End-to-end call with HOST buffers (pinned torch tensors for async copies): host -> device copies, one
         graph replay, device -> host copy of the waveform. Returns the host waveform tensor. Raises if the tensor-core
@@ -333,3 +337,77 @@ class Generator:
             raise RuntimeError(f"tensor-core conv kernels reported status {status:#x} "
                                "(0x10000 = activation beyond the f16 range; else role << 8 | wait that gave up)")
         return audio_host
+
+
+class SynthesisPipeline:
+    """Throughput form of Generator.synthesize for a stream of utterances of one length: the host -> device copies of
+    utterance i + 1 and the device -> host copy of utterance i - 1 run on the two copy engines while the captured graph
+    computes utterance i. One graph and one arena; per slot a set of staging tensors (inputs and waveform), so the
+    graph's static buffers are only touched by device-side copies on the compute stream.
+
+        pipe = gen.pipeline(t)
+        tickets = [pipe.submit(x, har, s, out) for (x, har, s, out) in batch]   # pinned host tensors
+        for k in tickets: pipe.wait(k)                                          # out is complete after wait
+
+    submit() blocks only when all `depth` slots are in flight (it then waits for the oldest). wait() raises if the
+    tensor-core kernels reported a problem up to and including that utterance (the status word is read stream-ordered
+    after each utterance, not cleared)."""
+
+    def __init__(self, gen, t: int, depth: int = 2):
+        ops.check(depth >= 1, "depth must be >= 1")
+        self.gen, self.t, self.depth = gen, int(t), int(depth)
+        dev = gen.device
+        self.b = gen.capture(self.t)
+        self.h2d, self.d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        self.compute = torch.cuda.Stream(device=dev)
+        self.slots = []
+        for _ in range(self.depth):
+            self.slots.append({
+                "x": torch.empty_like(self.b["x"]), "har": torch.empty_like(self.b["har"]),
+                "s": torch.empty_like(self.b["s"]), "audio": torch.empty_like(self.b["audio"]),
+                "status": torch.zeros(1, dtype=torch.int32).pin_memory(),
+                "in_ready": torch.cuda.Event(), "in_free": None, "computed": torch.cuda.Event(),
+                "out_done": None, "ticket": -1})
+        self.n = 0
+        self.compute.wait_stream(torch.cuda.current_stream(dev))
+
+    def submit(self, x_host, har_host, s_host, audio_host):
+        slot = self.slots[self.n % self.depth]
+        if slot["ticket"] >= 0:
+            self.wait(slot["ticket"])  # the slot's previous utterance has left the device
+        b = self.b
+        with torch.cuda.stream(self.h2d):
+            if slot["in_free"] is not None:
+                self.h2d.wait_event(slot["in_free"])
+            slot["x"].copy_(x_host, non_blocking=True)
+            slot["har"].copy_(har_host, non_blocking=True)
+            slot["s"].copy_(s_host, non_blocking=True)
+            slot["in_ready"].record(self.h2d)
+        with torch.cuda.stream(self.compute):
+            self.compute.wait_event(slot["in_ready"])
+            b["x"].copy_(slot["x"]), b["har"].copy_(slot["har"]), b["s"].copy_(slot["s"])
+            slot["in_free"] = torch.cuda.Event()
+            slot["in_free"].record(self.compute)
+            b["graph"].replay()
+            slot["audio"].copy_(b["audio"])
+            ops.conv_tc_status_async(slot["status"])
+            slot["computed"].record(self.compute)
+        with torch.cuda.stream(self.d2h):
+            self.d2h.wait_event(slot["computed"])
+            audio_host.copy_(slot["audio"], non_blocking=True)
+            slot["out_done"] = torch.cuda.Event()
+            slot["out_done"].record(self.d2h)
+        slot["ticket"] = self.n
+        self.n += 1
+        return slot["ticket"]
+
+    def wait(self, ticket: int) -> None:
+        slot = self.slots[ticket % self.depth]
+        if slot["ticket"] != ticket:
+            return  # already waited for (its slot has been reused or released)
+        slot["out_done"].synchronize()
+        slot["ticket"] = -1
+        status = int(slot["status"].item())
+        if status != 0:
+            raise RuntimeError(f"tensor-core conv kernels reported status {status:#x} "
+                               "(0x10000 = activation beyond the f16 range; else role << 8 | wait that gave up)")

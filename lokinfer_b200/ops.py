@@ -688,6 +688,15 @@ TC_PROFILE_FIELDS = ("mma_wait_act", "mma_wait_drain", "mma_wait_weights", "mma_
                      "pro_wait_free", "pro_wait_raw", "pro_transform", "pro_total", "wpro_wait_free", "wpro_total")
 
 
+def conv_tc_status_async(status_host) -> None:
+    """Queues a copy of the status word into `status_host` (a pinned int32 host tensor with one element) behind the
+    work already on the current stream; synchronises nothing and clears nothing (see conv_tc_status)."""
+    check(status_host.dtype == torch.int32 and status_host.numel() == 1 and status_host.is_pinned(),
+          "status_host must be a pinned int32 tensor with one element")
+    if _lib.lib().lkc_conv1d_tc_status_async(status_host.data_ptr(), _stream()) != 0:
+        raise _lib.LkcError(_lib.last_error())
+
+
 def conv_tc_profile(enable: bool) -> dict:
     """Turns the tensor-core kernel's role-level cycle counters on / off and returns (then clears) what was recorded:
     cycles summed over CTAs and launches, one representative warp per role. Synchronises the device. Only in a

@@ -222,3 +222,23 @@ def test_full_size_properties(cuda, gen):
     finally:
         ops.set_conv_path("auto")
     assert (audio - simt).abs().max().item() <= WAVE_MAXABS
+
+
+def test_synthesis_pipeline_matches_synthesize(cuda, gen):
+    """Generator.pipeline (two utterances in flight, copies overlapping compute) returns, for every utterance of a
+    stream of different inputs, exactly what Generator.synthesize returns for it alone."""
+    t = 200
+    hosts, want = [], []
+    for i in range(5):
+        inp, _ = _inputs(cuda, t, seed=70 + i)
+        h = [torch.from_numpy(inp[k]).pin_memory() for k in ("x", "har", "s")]
+        hosts.append(h)
+        want.append(gen.synthesize(*h).numpy().copy())
+    pipe = gen.pipeline(t, depth=2)
+    outs = [torch.empty(want[0].shape, dtype=torch.float32).pin_memory() for _ in hosts]
+    tickets = [pipe.submit(*h, o) for h, o in zip(hosts, outs)]
+    for k in tickets:
+        pipe.wait(k)
+    for o, w in zip(outs, want):
+        np.testing.assert_array_equal(o.numpy(), w)
+    assert not np.array_equal(want[0], want[1])
