@@ -242,6 +242,22 @@ LKC_API int lkc_upsample_nearest1d_f32_cuda(const LkcArgs* a, void* stream);
  * f32[R_i, C]. ptrs x_0 .. x_{n-1} | out[sum R, C]; ints x_i(2) each, out(2). */
 LKC_API int lkc_concat_rows_f32_cuda(const LkcArgs* a, void* stream);
 
+/* ---- device-side test harness (the data path of the reference's RUN2 message, include/lokinfer/remote/server.h:30-47)
+ * lkc_generate_cuda fills a tensor from a seed with the reference's generator (src/remote/server.cpp:739-782;
+ * python/lokinfer/remote.py:96-119): splitmix64 of seed + (2 i + 1) golden and seed + (2 i + 2) golden, u = (mix >> 11)
+ * 2^-53, dist 0 normal(a, b) by Box-Muller, 1 uniform [a, b), 2 integers in [floor a, floor b), computed in double.
+ * ptrs seed | out, where ptrs[0] points at an 8-byte HOST slot holding the u64 seed; ints n dtype (0 f32, 1 i32,
+ * 2 i64) dist; floats a b. Uniform and integer draws are bit-exact against the reference's generator, f32 normals
+ * to an ulp (double log / cos of the device against the host's libm).
+ * lkc_compare_stats_cuda compares two tensors on the device (src/remote/server.cpp:686-736): ptrs got ref | stats
+ * workspace; ints n dtype; floats rtol atol. stats = 64 bytes: i64 count, nonfinite, mismatches (|got - ref| > atol +
+ * rtol |ref|), worst index (largest excess, first on a tie; -1 if none), then f64 max_abs_err, max_abs_ref, sum_sq_err,
+ * sum_sq_ref; workspace = LKC_COMPARE_WORKSPACE_BYTES bytes of device memory owned by the caller. Neither call
+ * synchronises; the caller reads stats after its own synchronisation. */
+#define LKC_COMPARE_WORKSPACE_BYTES 32768
+LKC_API int lkc_generate_cuda(const LkcArgs* a, void* stream);
+LKC_API int lkc_compare_stats_cuda(const LkcArgs* a, void* stream);
+
 /* ---- time sharding of one utterance across GPUs ------------------------------------------------------------
  * No counterpart in the reference (it has no multi-GPU path). One rank owns a contiguous time range of every
  * activation tensor, with a margin of halo columns on both sides, in memory that its peers have mapped (CUDA IPC).
