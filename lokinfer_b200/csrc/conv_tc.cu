@@ -31,7 +31,8 @@
 // against a layout with two producers on its scheduler):
 //   warps 0-7   accumulate + epilogue: 128 running sums per thread, started from the bias; the residual is added one
 //               32-column batch at a time (fetched into the warp's tile behind a Dhi drain); per drain group += Dhi
-//               (tcgen05.ld); per tile += Dlo, oscale, chunk statistics and the store
+//               (tcgen05.ld); per tile += Dlo (folded in before the tile's last drain: Dlo is complete one run of hi
+//               MMAs before Dhi is), oscale, chunk statistics and the store
 //   warps 8, 10, 11, 12, 14, 15, 16, 18
 //               activation producers: affine -> Snake / leaky -> hi / lo split of the current chunk's raw window into
 //               shared memory in the K-major no-swizzle UMMA layout [16-byte K chunk][time row][4 f32 or 8 f16
@@ -591,6 +592,32 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       for (int c = 0; c < nSteps && !dead; ++c) {
         const bool doRes = hasRes && rb < 4;
         if (doRes) fetchResidual(rb);
+        if (c == nSteps - 1) {
+          // Last step of the tile (always a drain): Dlo is complete before the last hi MMAs are, so it is folded in
+          // first and handed back, and the next tile's lo MMAs need not wait for the last drain and the final phase.
+          if (!waitT(loFull, tileIt & 1, wLo, SLEEP_EPI_NS)) {
+            giveUp(1, 2);
+            dead = true;
+            break;
+          }
+          tcFenceAfter();
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {  // two 16-column loads in flight per wait
+            uint32_t va[16], vb[16];
+            tmemLoad16Async(tmemLo + laneBase + g * 128 + b * 32, va);
+            tmemLoad16Async(tmemLo + laneBase + g * 128 + b * 32 + 16, vb);
+            tmemWaitLoads();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float x = __uint_as_float(va[j]), y = __uint_as_float(vb[j]);
+              S[b * 32 + j] = F16 ? fmaf(x, 1.f / kLoScale, S[b * 32 + j]) : S[b * 32 + j] + x;
+              S[b * 32 + 16 + j] = F16 ? fmaf(y, 1.f / kLoScale, S[b * 32 + 16 + j]) : S[b * 32 + 16 + j] + y;
+            }
+          }
+          tcFenceBefore();
+          __syncwarp();
+          if (lane == 0) mbarArrive(loEmpty);
+        }
         if (c < preAt || c >= preAt + nPre) dead = !drainGroup();
         if (doRes && !dead) {
           switch (rb) {
@@ -603,28 +630,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
       }
       if (dead) break;
-      if (!waitT(loFull, tileIt & 1, wLo, SLEEP_EPI_NS)) {
-        giveUp(1, 2);
-        break;
-      }
       const long long tFin = kProf ? clock64() : 0;
-      tcFenceAfter();
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {  // two 16-column loads in flight per wait
-        uint32_t va[16], vb[16];
-        tmemLoad16Async(tmemLo + laneBase + g * 128 + b * 32, va);
-        tmemLoad16Async(tmemLo + laneBase + g * 128 + b * 32 + 16, vb);
-        tmemWaitLoads();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float x = __uint_as_float(va[j]), y = __uint_as_float(vb[j]);
-          S[b * 32 + j] = F16 ? fmaf(x, 1.f / kLoScale, S[b * 32 + j]) : S[b * 32 + j] + x;
-          S[b * 32 + 16 + j] = F16 ? fmaf(y, 1.f / kLoScale, S[b * 32 + 16 + j]) : S[b * 32 + 16 + j] + y;
-        }
-      }
-      tcFenceBefore();
-      __syncwarp();
-      if (lane == 0) mbarArrive(loEmpty);
       if (a.residual && a.outScale != 1.f) {
 #pragma unroll
         for (int j = 0; j < 128; ++j) S[j] *= a.outScale;
@@ -1073,6 +1079,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             int nslot = slot + 1;
             uint32_t nph = slotPh;
             if (nslot == wStages) nslot = 0, nph ^= 1;
+            const bool lastRound = c == nChunks16 - 1 && gi == nTapGroups - 1;  // of the tile
             if (needLo) {  // first round of a tile: hi, then lo (Dhi is handed back before Dlo)
               if (needHi && !waitT(hiEmpty, groupPar ^ 1, wHe, SLEEP_MMA_NS)) {
                 giveUp(4, 1);
@@ -1088,8 +1095,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
               }
               tcFenceAfter();
               issueLo(accLo);
+              if (lastRound) mmaCommit(loFull);
             } else {
               issueLo(accLo);
+              // the tile's lo chain is complete: the epilogue folds Dlo under the hi MMAs of this last round
+              if (lastRound) mmaCommit(loFull);
               if (needHi) {
                 if (!waitT(hiEmpty, groupPar ^ 1, wHe, SLEEP_MMA_NS)) {
                   giveUp(4, 1);
@@ -1110,7 +1120,6 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           const bool lastChunk = c == nChunks16 - 1;
           // the hi chain of a drain group (drainN chunks, or what is left of the tile) is complete
           if (g == drainN - 1 || lastChunk) mmaCommit(hiFull);
-          if (lastChunk) mmaCommit(loFull);
           mmaCommit(&bEmpty[buf]);  // activation buffer free once the MMAs have read it
           if (++buf == NB) buf = 0, bufPh ^= 1;
           if (++g == drainN || lastChunk) g = 0, groupPar ^= 1;
