@@ -235,6 +235,12 @@ LKC_API int lkc_stft_magphase_f32_cuda(const LkcArgs* a, void* stream);
  * F.conv_transpose1d(groups = C). ptrs x[C,L] w[C,1,K] b[C] | out[C,(L-1)s-2p+K+op]; ints x(2) w(3) b(1) out(2)
  * output_padding padding stride. */
 LKC_API int lkc_conv_transpose1d_dw_f32_cuda(const LkcArgs* a, void* stream);
+/* No counterpart in the reference: the polyphase view of a strided conv's input, y[ci * s + r, t] = x[ci, s t + r -
+ * pad] (zero outside [0, L); rows from Ci * s on are zero), so that conv1d(x, w, stride s, padding pad) with K = taps *
+ * s becomes a stride-1 conv with `taps` taps over y with w'[co, ci * s + r, j] = w[co, ci, s j + r]: the shape the
+ * tensor-core conv takes (the generator's noise_convs, models/kokoro/model.py:736-739). ptrs x | y; ints x(2) y(2)
+ * pad stride [x_pitch y_pitch]. */
+LKC_API int lkc_space_to_depth_f32_cuda(const LkcArgs* a, void* stream);
 /* upsample_nearest1d_f32_cpu (kokoro_conv.cpp:231-247, adapter :310-312): F.interpolate(mode = 'nearest'), integer
  * scale. ptrs x[C,L] | out[C,L*scale]; ints x(2) out(2) scale. */
 LKC_API int lkc_upsample_nearest1d_f32_cuda(const LkcArgs* a, void* stream);

@@ -313,6 +313,7 @@ const Entry kEntries[] = {
     {"pad_reflect1d_f32_cuda", lkc_pad_reflect1d_f32_cuda},
     {"scale_f32_cuda", lkc_scale_f32_cuda},
     {"snake_f32_cuda", lkc_snake_f32_cuda},
+    {"space_to_depth_f32_cuda", lkc_space_to_depth_f32_cuda},
     {"stft_magphase_f32_cuda", lkc_stft_magphase_f32_cuda},
     {"upsample_nearest1d_f32_cuda", lkc_upsample_nearest1d_f32_cuda},
 };

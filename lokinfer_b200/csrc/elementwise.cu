@@ -293,6 +293,35 @@ extern "C" LKC_API int lkc_pad_reflect1d_f32_cuda(const LkcArgs* a, void* stream
   return launched("pad_reflect1d_f32_cuda");
 }
 
+// Polyphase view of a strided conv's input: y[ci * s + r, t] = x[ci, s t + r - pad] (zero outside [0, L)); rows from
+// Ci * s on are zero (channel padding up to the row count of y). A conv with stride s, K = taps * s and padding pad
+// over x equals a stride-1 conv with `taps` taps over y with the weights w'[co, ci * s + r, j] = w[co, ci, s j + r],
+// which is a shape the tensor-core conv takes. No counterpart in the reference (its strided conv is direct,
+// kernels/cpu/kokoro_conv.cpp:32-69).
+__global__ void spaceToDepthKernel(const float* __restrict__ x, float* __restrict__ y, int64_t ci, int64_t l,
+                                   int64_t rows, int64_t ly, int64_t xPitch, int64_t yPitch, int s, int64_t pad) {
+  const int64_t total = rows * ly;
+  for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < total; idx += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t row = idx / ly, t = idx - row * ly;
+    const int64_t c = row / s, r = row - c * s;
+    const int64_t pos = int64_t(s) * t + r - pad;
+    y[row * yPitch + t] = (c < ci && pos >= 0 && pos < l) ? x[c * xPitch + pos] : 0.f;
+  }
+}
+
+// ints: x(Ci, L) y(rows, Ly) pad stride [x_pitch y_pitch]
+extern "C" LKC_API int lkc_space_to_depth_f32_cuda(const LkcArgs* a, void* stream) {
+  LKC_REQUIRE(a && a->numPtrs == 2 && (a->numInts == 6 || a->numInts == 8), "space_to_depth_f32_cuda: expected x | y, pad, stride");
+  const int64_t ci = a->ints[0], l = a->ints[1], rows = a->ints[2], ly = a->ints[3], pad = a->ints[4], s = a->ints[5];
+  const int64_t xPitch = a->numInts == 8 ? a->ints[6] : l, yPitch = a->numInts == 8 ? a->ints[7] : ly;
+  LKC_REQUIRE(s >= 1 && s <= 64 && pad >= 0 && ci >= 1 && l >= 1, "space_to_depth_f32_cuda: invalid stride / padding");
+  LKC_REQUIRE(rows >= ci * s && ly >= 1 && yPitch >= ly && xPitch >= l,
+              "space_to_depth_f32_cuda: y must be f32[rows >= Ci * stride, Ly]");
+  spaceToDepthKernel<<<gridFor(rows * ly, 4), kThreads, 0, S(stream)>>>(F(a, 0), O(a, 1), ci, l, rows, ly, xPitch, yPitch,
+                                                                        int(s), pad);
+  return launched("space_to_depth_f32_cuda");
+}
+
 extern "C" LKC_API int lkc_adain1d_f32_cuda(const LkcArgs* a, void* stream) {
   LKC_REQUIRE(a && a->numPtrs == 3 && a->numInts == 5 && a->floats, "adain1d_f32_cuda: expected x, gb | out and eps");
   const int64_t c = a->ints[0], l = a->ints[1];

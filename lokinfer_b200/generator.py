@@ -58,10 +58,39 @@ class Generator:
                 st = ops.conv1d_prepare_f32_cuda(self.w[k])
                 if st is not None:
                     self.conv_state[k[: -len(".weight")]] = st
+        # The two noise convs (22 -> 256, k 12, stride 6, padding 3; 22 -> 128, k 1) as stride-1 convs over the
+        # polyphase view of `har` (ops.space_to_depth_f32_cuda), channels padded to a multiple of 16: the shape the
+        # tensor-core conv takes. Packed once, like every other weight.
+        self.noise_tc = {}
+        for i, (stride, pad) in enumerate(((6, 3), (1, 0))):
+            key = f"noise_convs.{i}"
+            if key + ".weight" not in sd:
+                continue
+            wn = np.ascontiguousarray(sd[key + ".weight"], dtype=np.float32)
+            rows = -(-wn.shape[1] * stride // 16) * 16
+            wp = ops.to_cuda(ops.polyphase_conv_weights(wn, stride, rows), self.device)
+            state = ops.conv1d_prepare_f32_cuda(wp)
+            if state is not None:
+                ident = torch.stack([torch.zeros(rows), torch.ones(rows), torch.zeros(rows)]).to(self.device).contiguous()
+                self.noise_tc[i] = (wp, state, ident, stride, pad, wn.shape[2] // stride, rows)
         self._graphs = {}
         self._streams = None
 
     # ------------------------------------------------------------------ building blocks
+
+    def _noise_conv(self, har, i, keep):
+        """noise_convs[i](har) -> (xs, chunk statistics of xs or None); temporaries go to `keep`. On the tensor cores when the polyphase pack
+        exists (and the conv path is not "simt"): space-to-depth of har, then a stride-1 conv with an identity
+        affine, whose epilogue also gives the statistics the following resblock needs."""
+        w = self.w
+        if i in self.noise_tc and ops._conv_path != "simt":
+            wp, state, ident, stride, pad, taps, rows = self.noise_tc[i]
+            y = ops.space_to_depth_f32_cuda(har, stride, pad, taps, rows)
+            keep.append(y)
+            return ops.conv1d_affine_f32_cuda(y, wp, w[f"noise_convs.{i}.bias"], ident, state=state)
+        if i == 0:
+            return ops.conv1d_f32_cuda(har, w["noise_convs.0.weight"], w["noise_convs.0.bias"], stride=6, padding=3), None
+        return ops.conv1d_f32_cuda(har, w["noise_convs.1.weight"], w["noise_convs.1.bias"]), None
 
     def style(self, s):
         """fc(style) of every AdaIN as views into one style-bank GEMV (model.py:135-144): name -> f32[2C]."""
@@ -152,13 +181,9 @@ class Generator:
             if not fused:
                 break
             with on(side[i] if par else None):
-                if i == 0:
-                    xs = ops.conv1d_f32_cuda(har, w["noise_convs.0.weight"], w["noise_convs.0.bias"], stride=6,
-                                             padding=3)
-                else:
-                    xs = ops.conv1d_f32_cuda(har, w["noise_convs.1.weight"], w["noise_convs.1.bias"])
-                noise[i], _ = self.adain_resblock1_fused(xs, gb, f"noise_res.{i}", k_noise)
-                keep.append(xs)
+                xs, xs_stats = self._noise_conv(har, i, keep)
+                noise[i], _ = self.adain_resblock1_fused(xs, gb, f"noise_res.{i}", k_noise, x_stats=xs_stats)
+                keep += [xs, xs_stats] if xs_stats is not None else [xs]
         for i, (k_up, u, k_noise) in enumerate(((20, 10, 7), (12, 6, 11))):
             if fused:
                 if par:

@@ -111,6 +111,7 @@ _PITCHED = {
     "conv1d_snake_f32_cuda": (0, 5), "conv1d_snake_res_f32_cuda": (0, 5, 6),
     "conv1d_leaky_f32_cuda": (0, 4), "conv1d_leaky_res_f32_cuda": (0, 4, 5), "conv1d_affine_f32_cuda": (0, 4),
     "conv_transpose1d_poly_f32_cuda": (0, 3, 4), "istft_logits_f32_cuda": (0,),
+    "space_to_depth_f32_cuda": (0, 1),
 }
 
 
@@ -479,6 +480,40 @@ def snake_f32_cuda(x, alpha):
     check(alpha.shape[0] == x.shape[0], "alpha must be f32[C]")
     out = _new(x, x.shape)
     _run("snake_f32_cuda", [x, alpha], [out])
+    return out
+
+
+def space_to_depth_f32_cuda(x, stride, padding, taps, rows=None):
+    """Polyphase view of the input of a strided conv (no counterpart in the reference): y[ci * stride + r, t] =
+    x[ci, stride * t + r - padding], zero outside x, t in [0, Lo + taps - 1) where Lo is the length of
+    conv1d(x, w[Co, Ci, taps * stride], stride, padding); rows beyond Ci * stride (up to `rows`) are zero. With
+    polyphase_conv_weights(w, stride, rows), conv1d(y, w') at stride 1 and no padding is that strided conv."""
+    stride, padding, taps = _int(stride, "stride"), _int(padding, "padding"), _int(taps, "taps")
+    _f32(x, rank=2)
+    check(stride >= 1 and padding >= 0 and taps >= 1, "invalid stride / padding / taps")
+    ci, l = int(x.shape[0]), int(x.shape[1])
+    lo = _conv_out(l, taps * stride, stride, padding, 1)
+    check(lo >= 1, "empty conv output")
+    rows = ci * stride if rows is None else _int(rows, "rows")
+    check(rows >= ci * stride, "rows must be >= Ci * stride")
+    y = _new(x, (rows, lo + taps - 1), rows=True)
+    _run("space_to_depth_f32_cuda", [x], [y], attrs_int=[padding, stride])
+    return y
+
+
+def polyphase_conv_weights(w, stride, rows=None):
+    """w f32[Co, Ci, taps * stride] (numpy) -> w' f32[Co, rows, taps] with w'[co, ci * stride + r, j] =
+    w[co, ci, stride * j + r] and zeros in the rows beyond Ci * stride: the weights of the stride-1 conv over
+    space_to_depth_f32_cuda(x, stride, ...)."""
+    import numpy as np
+    co, ci, k = w.shape
+    check(k % stride == 0, "K must be a multiple of the stride")
+    taps = k // stride
+    rows = ci * stride if rows is None else int(rows)
+    check(rows >= ci * stride, "rows must be >= Ci * stride")
+    out = np.zeros((co, rows, taps), dtype=np.float32)
+    out[:, : ci * stride, :] = np.asarray(w, dtype=np.float32).reshape(co, ci, taps, stride).transpose(0, 1, 3, 2).reshape(
+        co, ci * stride, taps)
     return out
 
 

@@ -571,3 +571,37 @@ def test_errors_come_back_as_exceptions(cuda):
                  torch.cuda.current_stream().cuda_stream)
     # the context is still usable
     assert ops.istft_logits_f32_cuda(x).shape == (35,)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ci,co,l,k,s,p", [(22, 256, 1201, 12, 6, 3), (22, 128, 999, 1, 1, 0), (5, 32, 500, 6, 3, 2),
+                                           (22, 256, 124801, 12, 6, 3)])
+def test_strided_conv_as_polyphase_conv_on_tensor_cores(cuda, ci, co, l, k, s, p):
+    """space_to_depth + the stride-1 tensor-core conv with polyphase weights equals the strided conv (the generator's
+    noise_convs, model.py:736-739): against the CUDA-core strided conv of the same library and, at the small sizes,
+    against the float64 oracle."""
+    from lokinfer_b200 import ops
+    rng = np.random.default_rng(ci * 7 + l)
+    x = rng.standard_normal((ci, l)).astype(np.float32)
+    w = (rng.standard_normal((co, ci, k)) / np.sqrt(ci * k)).astype(np.float32)
+    b = (rng.standard_normal(co) * 0.1).astype(np.float32)
+    rows = -(-ci * s // 16) * 16
+    dx, dw, db = dev(cuda, x, w, b)
+    want = ops.conv1d_f32_cuda(dx, dw, db, stride=s, padding=p).cpu().numpy()
+    wp = ops.to_cuda(ops.polyphase_conv_weights(w, s, rows), cuda)
+    state = ops.conv1d_prepare_f32_cuda(wp)
+    assert state is not None
+    ident = torch.stack([torch.zeros(rows), torch.ones(rows), torch.zeros(rows)]).to(cuda)
+    for padded in (False, True):
+        with ops.padded_rows(padded):
+            y = ops.space_to_depth_f32_cuda(dx, s, p, k // s, rows)
+            got, stats = ops.conv1d_affine_f32_cuda(y, wp, db, ident, state=state)
+        assert tuple(y.shape) == (rows, want.shape[1] + k // s - 1) and tuple(got.shape) == want.shape
+        got = got.cpu().numpy()
+        assert rel_l2(got, want) <= REL_L2
+        check_stats(stats.cpu().numpy(), got)
+    if l <= 2000:
+        ref64 = torch.nn.functional.conv1d(t64(x)[None], t64(w), t64(b), stride=s, padding=p)[0].numpy()
+        ref32 = torch.nn.functional.conv1d(t32(x)[None], t32(w), t32(b), stride=s, padding=p)[0].numpy()
+        assert rel_l2(got, ref64) <= 2 * rel_l2(ref32, ref64) + 2e-7
+    assert ops.conv_tc_status() == 0
