@@ -510,14 +510,24 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         } else {
           // channel cl: the 32 * TS output samples u = (tChunk + 32 b) * TS + idx are contiguous in memory; copy
           // i = cl * TS + f moves idx = 32 f + lane, which is column idx / TS of phase idx % TS
+          // The tile offsets of the TS copies of a channel depend on the lane only: computed once per batch, then a
+          // rolled loop over the channels with pointer increments (this runs four times per tile on every epilogue
+          // warp; the index arithmetic of the (channel, copy) pair per element cost more than the copies).
           const int64_t uEnd = a.lo * TS, u0 = (tChunk + b * 32) * TS;
-#pragma unroll 2
-          for (int i = 0; i < ROWS; ++i) {
-            const int cl = i / TS, idx = (i % TS) * 32 + lane;
-            float* dst = &tile[(cl * TS + idx % TS) * STAGE_PITCH + idx / TS];
-            if (cl < coValid && u0 + idx < uEnd)
-              cpAsync4(dst, a.residual + int64_t(coBase + cl) * a.resPitch + a.padLeft + u0 + idx);
-            else *dst = 0.f;
+          int off[TS ? TS : 1];
+#pragma unroll
+          for (int f = 0; f < TS; ++f) off[f] = ((f * 32 + lane) % TS) * STAGE_PITCH + (f * 32 + lane) / TS;
+          const int64_t left = uEnd - u0 - lane;  // copy f of this lane is inside the row iff f * 32 < left
+          const float* rp = a.residual + int64_t(coBase) * a.resPitch + a.padLeft + u0 + lane;
+          float* tp = tile;
+#pragma unroll 1
+          for (int cl = 0; cl < CQ; ++cl, rp += a.resPitch, tp += TS * STAGE_PITCH) {
+            const bool chOk = cl < coValid;
+#pragma unroll
+            for (int f = 0; f < TS; ++f) {
+              if (chOk && f * 32 < left) cpAsync4(tp + off[f], rp + f * 32);
+              else tp[off[f]] = 0.f;
+            }
           }
         }
         cpAsyncCommit();
@@ -752,13 +762,18 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 #pragma unroll
           for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
           __syncwarp();
-#pragma unroll 2
-          for (int i = 0; i < ROWS; ++i) {
-            const int cl = i / TS, idx = (i % TS) * 32 + lane;
-            const int64_t u = u0 + idx;
-            if (cl < coValid && u < uEnd)
-              a.out[int64_t(coBase + cl) * a.outPitch + a.padLeft + u] =
-                  tile[(cl * TS + idx % TS) * STAGE_PITCH + idx / TS];
+          int off[TS ? TS : 1];  // as in the residual fetch: lane-only tile offsets, then pointer increments
+#pragma unroll
+          for (int f = 0; f < TS; ++f) off[f] = ((f * 32 + lane) % TS) * STAGE_PITCH + (f * 32 + lane) / TS;
+          const int64_t left = uEnd - u0 - lane;
+          float* op = a.out + int64_t(coBase) * a.outPitch + a.padLeft + u0 + lane;
+          const float* tp = tile;
+#pragma unroll 1
+          for (int cl = 0; cl < CQ; ++cl, op += a.outPitch, tp += TS * STAGE_PITCH) {
+            if (cl >= coValid) break;
+#pragma unroll
+            for (int f = 0; f < TS; ++f)
+              if (f * 32 < left) op[f * 32] = tp[off[f]];
           }
           __syncwarp();
         }
