@@ -45,7 +45,7 @@ from lokinfer_b200 import synth  # noqa: E402
 
 # DRAM traffic of one launch of the dominant conv shape (ncu capture, summary under profiles/); algorithmic bytes =
 # x + residual read, out written = 3 * 4 * C * L.
-TRAFFIC = {"bytes": 129785856 + 35341056, "algorithmic": 3 * 4 * 128 * 124801,
+TRAFFIC = {"bytes": 129688576 + 29296384, "algorithmic": 3 * 4 * 128 * 124801,
            "kernel": "convTcKernel, conv1d_snake_res, Ci = Co = 128, L = 124801, K = 11, dilation 5 (one launch)",
            "source": "profiles/conv_tc_c128_k11_L124801.md"}
 
