@@ -384,7 +384,7 @@ class SynthesisPipeline:
         dev = gen.device
         self.b = gen.capture(self.t)
         self.h2d, self.d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-        self.compute = torch.cuda.Stream(device=dev)
+        self.compute = torch.cuda.current_stream(dev)  # the graph replays on the stream current at construction
         self.slots = []
         for _ in range(self.depth):
             self.slots.append({
@@ -394,7 +394,6 @@ class SynthesisPipeline:
                 "in_ready": torch.cuda.Event(), "in_free": None, "computed": torch.cuda.Event(),
                 "out_done": None, "ticket": -1})
         self.n = 0
-        self.compute.wait_stream(torch.cuda.current_stream(dev))
 
     def submit(self, x_host, har_host, s_host, audio_host):
         slot = self.slots[self.n % self.depth]
