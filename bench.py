@@ -79,7 +79,8 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons of one GPU every 200 ms while the timed region runs."""
+    """Samples nvidia-smi clocks / throttle reasons of one GPU every 50 ms while the timed regions run (the `value`
+    loop and the `e2e` loops that follow it)."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -91,7 +92,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -110,11 +111,13 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        pw = [float(r[2]) for r in self.rows if len(r) > 2 and r[2].replace(".", "").isdigit()]
         mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for j, n in enumerate(names) if any(len(r) > 3 + j and r[3 + j].lower() == "active" for r in self.rows)]
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "sm_min_mhz": min(sm) if sm else None, "power_w_median": float(np.median(pw)) if pw else None,
+                "reasons": reasons, "samples": len(sm), "covers": "the value loop and the e2e loops after it"}
 
 
 def cpu_generator_rate(t_sample: int, reps: int, warmup: int, threads: int | None):
@@ -473,7 +476,6 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     if sampler:
         sampler.start()
     ms_dev = timed(lambda: bufs["graph"].replay(), args.steps, args.warmup)
-    clocks = sampler.stop() if sampler else None
     ms_e2e_serial = timed(lambda: gen.synthesize(host[0], host[1], host[2], audio_host), args.steps,
                           max(1, args.warmup // 2))
     # throughput form: two utterances in flight, each step still copies its inputs in and its waveform out
@@ -501,6 +503,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         dist.all_reduce(ms_pipe, op=dist.ReduceOp.MAX)
     ms_e2e = float(ms_pipe.item())
     pipe_ok = bool(np.array_equal(outs[0].numpy(), outs[1].numpy()))  # same inputs -> same waveform in both slots
+    clocks = sampler.stop() if sampler else None
 
     # input option B: the `har` input computed on the device from the F0 curve (harmonic source with in-kernel noise +
     # STFT, the step before the generator in the reference graph); h2d carries x, f0 and s only
