@@ -192,7 +192,8 @@ def measure_cfg1(gen, dev, steps: int) -> dict:
 def measure_cfg0(dev, peak: float) -> dict:
     """BASELINE config 0: one AdaINResBlock1 (six fused convs + their AdaIN affines) per kernel size at C = 128,
     L = 19200 and L = 19201 (the generator's stage-1 length for T = 320), rows padded to 16 bytes as in the generator;
-    FLOPs = 6 * 2 * C^2 * k * L per block."""
+    FLOPs = 6 * 2 * C^2 * k * L per block. Each kernel size alone (`blocks`, `sum_L*`) and the three side by side on
+    three streams (`concurrent_L*`)."""
     from lokinfer_b200 import Generator, ops
 
     out = {"workload": "adain_resblock1 C=128 k in (3, 7, 11), dilations (1, 3, 5)", "blocks": []}
@@ -219,6 +220,37 @@ def measure_cfg0(dev, peak: float) -> dict:
             tot_fl += fl
         out[f"sum_L{l}"] = {"ms": tot_ms, "tflops": tot_fl / (tot_ms * 1e-3) / 1e12,
                             "frac": tot_fl / (tot_ms * 1e-3) / 1e12 / peak}
+        # The three branches of the config side by side, as the generator runs the resblocks of a stage: one captured
+        # graph, each kernel size on its own stream (75-76 tiles per conv leave half of the 148 SMs to the others).
+        gens, xs, gbs = [], [], []
+        with ops.padded_rows():
+            for k in (3, 7, 11):
+                sd, x, s = synth.resblock_case(128, l, k, 300 + k)
+                g = Generator(sd, dev)
+                gens.append(g), xs.append(ops.to_cuda(x, dev, rows=True)), gbs.append(g.style(ops.to_cuda(s, dev)))
+            lanes = [torch.cuda.Stream(device=dev) for _ in range(3)]
+
+            def three():
+                cur = torch.cuda.current_stream(dev)
+                keep = []
+                for ln, g, x, gb, k in zip(lanes, gens, xs, gbs, (3, 7, 11)):
+                    ln.wait_stream(cur)
+                    with torch.cuda.stream(ln):
+                        keep.append(g.adain_resblock1_fused(x, gb, "rb", k))
+                for ln in lanes:
+                    cur.wait_stream(ln)
+                return keep
+
+            for _ in range(2):
+                three()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                keep = three()
+            ms = _event_ms(graph.replay, 20, 3)
+            del keep
+        out[f"concurrent_L{l}"] = {"ms": ms, "tflops": tot_fl / (ms * 1e-3) / 1e12,
+                                   "frac": tot_fl / (ms * 1e-3) / 1e12 / peak}
     return out
 
 
