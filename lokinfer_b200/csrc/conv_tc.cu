@@ -33,6 +33,8 @@
 //               32-column batch at a time (fetched into the warp's tile behind a Dhi drain); per drain group += Dhi
 //               (tcgen05.ld); per tile += Dlo (folded in before the tile's last drain: Dlo is complete one run of hi
 //               MMAs before Dhi is), oscale, chunk statistics and the store
+//   (launches that are bound by the producers, few MMAs per chunk, use the plain layout instead: producers 8-15,
+//   two per scheduler, control warps 16-18)
 //   warps 8, 10, 11, 12, 14, 15, 16, 18
 //               activation producers: affine -> Snake / leaky -> hi / lo split of the current chunk's raw window into
 //               shared memory in the K-major no-swizzle UMMA layout [16-byte K chunk][time row][4 f32 or 8 f16
@@ -68,7 +70,7 @@ constexpr int KC = 16;          // input channels per staged chunk (one weight s
 constexpr int MAX_NB = 4;       // most activation (hi / lo) buffers
 constexpr int NRAW = 2;         // raw-input staging buffers, filled one chunk ahead
 constexpr int EPI_WARPS = 8, PRO_WARPS = 8;
-constexpr int W_WARP = 9, MMA_WARP = 13, RAW_WARP = 17, IDLE_WARP = 19;  // scheduler 1 = warp id % 4 == 1
+constexpr int IDLE_WARP = 19;
 constexpr int NWARPS = EPI_WARPS + PRO_WARPS + 4;
 constexpr int NTHREADS = NWARPS * 32;  // 640
 // warpgroups 2-4 mix producers and control warps, and setmaxnreg takes one value per warpgroup
@@ -141,6 +143,7 @@ struct TcArgs {
   int nb;          // activation buffers
   int wG;          // taps per weight slot: the k taps of a chunk go in ceil(k / wG) groups of near-equal size
   int drainN;      // 16-channel chunks accumulated in Dhi between two drains into the running sums
+  int balanced;    // warp-role layout (see the kernel)
   int tmaIn;       // 1: x rows are 16-byte aligned, the raw windows come by tiled TMA loads
   int tmaOut;      // 1: out (and residual) rows are 16-byte aligned, boxes go by TMA
   int numTTiles, numCoBlk;
@@ -391,6 +394,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     if (threadIdx.x == 0) atomicOr(a.status, (6 << 8) | 1);
     return;
   }
+  // Two warp-role layouts. Isolated (a.balanced == 0): the three control warps on scheduler 1 (warp id % 4 == 1), no
+  // producer next to the MMA issuer. Balanced: producers 8-15 (two per scheduler), control warps 16-18; for launches
+  // that are bound by the activation producers, where the issuer's pace does not matter.
+  const bool bal = a.balanced != 0;
+  const int W_WARP = bal ? 16 : 9, MMA_WARP = bal ? 17 : 13, RAW_WARP = bal ? 18 : 17;
   const int numTiles = a.numTTiles * a.numCoBlk;
   const int nChunks16 = a.ci / KC;
   const int nGroups = (nChunks16 + a.drainN - 1) / a.drainN;  // Dhi drains per tile
@@ -790,10 +798,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     if (tmaOut && lane == 0) bulkWaitAll();
     if (kProf && warp == 0)
       profAdd(5, wHi), profAdd(6, wLo), profAdd(7, cPre), profAdd(8, cFin), profAdd(9, clock64() - tStart);
-  } else if ((warp & 3) != 1 && warp != IDLE_WARP) {
+  } else if (bal ? warp < EPI_WARPS + PRO_WARPS : ((warp & 3) != 1 && warp != IDLE_WARP)) {
     // ------------------------------------------------------------------ activation producers
     regDec<PRO_REGS>();
-    const int pw = (warp - EPI_WARPS) - ((warp - EPI_WARPS + 2) >> 2);  // 8, 10, 11, 12, 14, 15, 16, 18 -> 0..7
+    const int pw = bal ? warp - EPI_WARPS
+                       : (warp - EPI_WARPS) - ((warp - EPI_WARPS + 2) >> 2);  // 8, 10, 11, 12, 14, 15, 16, 18 -> 0..7
     const int cg = pw & 3, hf = pw >> 2;  // channel group of 4 inside the 16-channel chunk; row half
     const int rowsHalf = (rows + 1) >> 1;
     const int r0 = hf * rowsHalf, r1 = (r0 + rowsHalf < rows) ? r0 + rowsHalf : rows;
@@ -1440,6 +1449,10 @@ static int finishArgs(TcArgs& a, TcMaps& m, bool f16, bool boxesOk, int* grid, s
   const int perChunk = a.k * (f16 ? 1 : 2);
   const int n = MAX_CHAIN / perChunk;
   a.drainN = n < 1 ? 1 : n;
+  // Launches with at most 15 MMAs per chunk (K <= 5 with f16 halves; the ConvTranspose launches: three taps) are
+  // bound by the activation producers: they take the balanced warp layout (measured at K = 3: the transform of a
+  // chunk 17 % faster, the launch 4-7 %; at K = 7 the isolated layout is 3 % ahead).
+  a.balanced = a.k * (f16 ? 3 : 6) <= 15 ? 1 : 0;
   const int tiles = a.numTTiles * a.numCoBlk;
   *grid = tiles < d->smCount ? tiles : d->smCount;
   // TMA routes: tensors whose rows are 16-byte aligned. A map that is not used still has to be a valid kernel
