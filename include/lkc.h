@@ -248,6 +248,17 @@ LKC_API int lkc_upsample_nearest1d_f32_cuda(const LkcArgs* a, void* stream);
  * f32[R_i, C]. ptrs x_0 .. x_{n-1} | out[sum R, C]; ints x_i(2) each, out(2). */
 LKC_API int lkc_concat_rows_f32_cuda(const LkcArgs* a, void* stream);
 
+/* ---- memory planner (host code) ----------------------------------------------------------------------------------
+ * Offsets of n tensors (in allocation order) inside one arena, for a program that forks into num_streams streams: the
+ * counterpart of the reference's planner (src/compiler/plan_memory.cpp; the arena of src/runtime/executable.cpp:
+ * 732-815). alloc_clock[i * S + s] = vector clock of the allocating stream at tensor i's allocation; last_use[i * S +
+ * s] = largest count of stream s at which tensor i was used (allocation included, 0 = never). A tensor's bytes are
+ * reused by a later allocation only if each of its uses happens-before that allocation (last_use <= alloc_clock on
+ * every stream) and it is not pinned. Greedy lowest-offset placement in program order; sizes rounded up to align. */
+LKC_API int lkc_plan_memory(int64_t n, int64_t num_streams, const int64_t* bytes, const int32_t* pinned,
+                            const int64_t* alloc_clock, const int64_t* last_use, int64_t align, int64_t* offsets,
+                            int64_t* total);
+
 /* ---- device-side test harness (the data path of the reference's RUN2 message, include/lokinfer/remote/server.h:30-47)
  * lkc_generate_cuda fills a tensor from a seed with the reference's generator (src/remote/server.cpp:739-782;
  * python/lokinfer/remote.py:96-119): splitmix64 of seed + (2 i + 1) golden and seed + (2 i + 2) golden, u = (mix >> 11)

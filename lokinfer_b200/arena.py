@@ -70,25 +70,38 @@ def happens_before(uses, clock) -> bool:
 
 
 def plan(allocs):
-    """Offsets for the traced allocations (same order) and the arena size. Greedy lowest-offset placement; a tensor
-    blocks its range for every later allocation that it does not happen-before (pinned tensors block forever)."""
-    placed = []  # (offset, end, alloc)
-    offsets, top = [], 0
-    for a in allocs:
-        size = -(-a["bytes"] // ALIGN) * ALIGN
-        busy = sorted((o, e) for o, e, p in placed
-                      if p["pinned"] or not happens_before(p["uses"] + [(p["stream"], p["clock"][p["stream"]])],
-                                                           a["clock"]))
-        off = 0
-        for o, e in busy:
-            if off + size <= o:
-                break
-            if e > off:
-                off = e
-        offsets.append(off)
-        placed.append((off, off + size, a))
-        top = max(top, off + size)
-    return offsets, top
+    """Offsets for the traced allocations (same order) and the arena size: the library's planner (lkc_plan_memory,
+    csrc/plan.cu). Greedy lowest-offset placement; a tensor blocks its range for every later allocation that it does
+    not happen-before (pinned tensors block forever)."""
+    import ctypes
+
+    from . import _lib
+
+    n = len(allocs)
+    streams = sorted({s for a in allocs for s in list(a["clock"]) + [u[0] for u in a["uses"]] + [a["stream"]]},
+                     key=repr)
+    col = {s: i for i, s in enumerate(streams)}
+    ns = max(1, len(streams))
+    size = (ctypes.c_int64 * n)(*[int(a["bytes"]) for a in allocs])
+    pinned = (ctypes.c_int32 * n)(*[1 if a["pinned"] else 0 for a in allocs])
+    clock = (ctypes.c_int64 * (n * ns))()
+    last = (ctypes.c_int64 * (n * ns))()
+    for i, a in enumerate(allocs):
+        for s, c in a["clock"].items():
+            clock[i * ns + col[s]] = int(c)
+        for s, c in a["uses"] + [(a["stream"], a["clock"][a["stream"]])]:
+            j = i * ns + col[s]
+            if last[j] < c:
+                last[j] = int(c)
+    offsets = (ctypes.c_int64 * n)()
+    total = ctypes.c_int64(0)
+    fn = _lib.lib().lkc_plan_memory
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                   ctypes.c_int64, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]
+    if fn(n, ns, size, pinned, clock, last, ALIGN, offsets, ctypes.byref(total)) != 0:
+        raise _lib.LkcError(_lib.last_error())
+    return [int(o) for o in offsets], int(total.value)
 
 
 class PlannedArena:

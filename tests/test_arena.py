@@ -66,3 +66,49 @@ def test_pinned_tensors_are_never_reused_and_sizes_are_aligned():
     tr.on_alloc(c, 1); tr.on_run([c], 1)
     off, total = plan(tr.allocs)
     assert off[0] == 0 and off[1] == ALIGN and off[2] == ALIGN and total == 2 * ALIGN
+
+
+def _plan_python(allocs):
+    """The planner restated in Python (greedy lowest offset, happens-before by vector clocks): the check of the
+    library's lkc_plan_memory on random traces."""
+    placed, offsets, top = [], [], 0
+    for a in allocs:
+        size = -(-a["bytes"] // ALIGN) * ALIGN
+        busy = sorted((o, e) for o, e, p in placed
+                      if p["pinned"] or not happens_before(p["uses"] + [(p["stream"], p["clock"][p["stream"]])],
+                                                           a["clock"]))
+        off = 0
+        for o, e in busy:
+            if off + size <= o:
+                break
+            if e > off:
+                off = e
+        offsets.append(off)
+        placed.append((off, off + size, a))
+        top = max(top, off + size)
+    return offsets, top
+
+
+def test_native_planner_matches_the_python_restatement_on_random_traces():
+    import random
+    rng = random.Random(7)
+    for trial in range(30):
+        tr = Tracer()
+        live = []
+        streams = [1, 2, 3, 4][: rng.randint(1, 4)]
+        for step in range(rng.randint(5, 60)):
+            s = rng.choice(streams)
+            kind = rng.random()
+            if kind < 0.15 and len(streams) > 1:
+                w = rng.choice([x for x in streams if x != s])
+                tr.on_join(s, w)
+                continue
+            t = _T(rng.choice([4, 100, 256, 1000, 4096, 70000]))
+            tr.on_alloc(t, s)
+            ins = rng.sample(live, min(len(live), rng.randint(0, 3)))
+            tr.on_run(ins + [t], s)
+            live.append(t)
+            if rng.random() < 0.1:
+                tr.pin(t)
+        assert plan(tr.allocs) == _plan_python(tr.allocs)
+    assert plan([]) == ([], 0)
