@@ -477,6 +477,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       // conv: the warp's rows are 32 consecutive output channels. ConvTranspose: rows are (channel, phase) pairs,
       // CQ channels x TS phases per warp (lane = cl * TS + r), the last 32 - CQ * TS rows are zero padding.
       constexpr int CQ = TS ? 32 / TS : 32, ROWS = TS ? CQ * TS : 32;
+      // Row pitch of the warp's transpose tile. ConvTranspose: 35 floats, so that both the row-wise accesses (lane =
+      // row: 3 * lane mod 32 is a permutation) and the interleaved ones (phase r, column q -> bank 3 r + q: at most
+      // two lanes per bank) stay cheap; its 30 rows still fit the tile (30 x 35 <= 32 x 33).
+      constexpr int TP = TS ? 35 : STAGE_PITCH;
+      static_assert(ROWS * TP <= STAGE_FLOATS, "transpose tile");
       const int coBase = TS ? (cb * 4 + q) * CQ : cb * MT + q * 32;
       const int co = TS ? coBase + lane / (TS ? TS : 1) : coBase + lane;
       const bool rowOk = TS ? (lane < ROWS && co < a.co) : (!PARTIAL || co < a.co);
@@ -524,12 +529,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           const int64_t uEnd = a.lo * TS, u0 = (tChunk + b * 32) * TS;
           int off[TS ? TS : 1];
 #pragma unroll
-          for (int f = 0; f < TS; ++f) off[f] = ((f * 32 + lane) % TS) * STAGE_PITCH + (f * 32 + lane) / TS;
+          for (int f = 0; f < TS; ++f) off[f] = ((f * 32 + lane) % TS) * TP + (f * 32 + lane) / TS;
           const int64_t left = uEnd - u0 - lane;  // copy f of this lane is inside the row iff f * 32 < left
           const float* rp = a.residual + int64_t(coBase) * a.resPitch + a.padLeft + u0 + lane;
           float* tp = tile;
 #pragma unroll 1
-          for (int cl = 0; cl < CQ; ++cl, rp += a.resPitch, tp += TS * STAGE_PITCH) {
+          for (int cl = 0; cl < CQ; ++cl, rp += a.resPitch, tp += TS * TP) {
             const bool chOk = cl < coValid;
 #pragma unroll
             for (int f = 0; f < TS; ++f) {
@@ -562,7 +567,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         if (TS == 0 || lane < ROWS) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const float r = tile[lane * STAGE_PITCH + j];
+            const float r = tile[lane * TP + j];
             if (TS != 0 && b == 0 && j == 0 && reflectLane) resHeld = r;
             else S[b * 32 + j] += r;
           }
@@ -767,17 +772,19 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           const int64_t u0 = (tChunk + b * 32) * TS;
+          if (lane < ROWS) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) tile[lane * STAGE_PITCH + j] = S[b * 32 + j];
+            for (int j = 0; j < 32; ++j) tile[lane * TP + j] = S[b * 32 + j];
+          }
           __syncwarp();
           int off[TS ? TS : 1];  // as in the residual fetch: lane-only tile offsets, then pointer increments
 #pragma unroll
-          for (int f = 0; f < TS; ++f) off[f] = ((f * 32 + lane) % TS) * STAGE_PITCH + (f * 32 + lane) / TS;
+          for (int f = 0; f < TS; ++f) off[f] = ((f * 32 + lane) % TS) * TP + (f * 32 + lane) / TS;
           const int64_t left = uEnd - u0 - lane;
           float* op = a.out + int64_t(coBase) * a.outPitch + a.padLeft + u0 + lane;
           const float* tp = tile;
 #pragma unroll 1
-          for (int cl = 0; cl < CQ; ++cl, op += a.outPitch, tp += TS * STAGE_PITCH) {
+          for (int cl = 0; cl < CQ; ++cl, op += a.outPitch, tp += TS * TP) {
             if (cl >= coValid) break;
 #pragma unroll
             for (int f = 0; f < TS; ++f)
